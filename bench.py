@@ -1,0 +1,551 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A32 quantized-linear path on B200.
+
+Headline workload ("qwen2-1.5b-decode-linears"): one decode token's worth of quantized linears of
+the Qwen2-1.5B architecture - 28 decoder layers x the seven linears q,k,v,o,gate,up,down at M=1 -
+every layer with its own weights (737 MB of int4+scales per step, larger than the 126 MB L2, so
+no flush is needed between steps).  A step is one pass over those 196 linears, launched through the
+C ABI (mllmb200_w4a32_linear_forward) and replayed as a CUDA graph.  The metric is algorithmic HBM
+bytes per second: nibbles + scales + bias + fp32 x + fp32 y of every linear, divided by the
+device time (CUDA events on the launching stream, max over ranks).
+
+Extra objects in the JSON line: `roofline` (GEMV kernel vs the measured HBM copy bandwidth),
+`prefill` (the same seven linears at M=512, TFLOP/s), `e2e` (host buffers in, host buffers out),
+`cpu_baseline` (the reference's X86 int4 kernels on the host cores), `per_shape`, `clocks`.
+
+With N > 1 ranks (torchrun) every rank serves its own token (independent replicas, weak scaling,
+no collective on the data path), and rank 0 adds a `tp` object: the column-sharded large linear of
+BASELINE config 4 with an NCCL all-gather of y.
+
+`--impl reference` times the reference's CPU path for the same workload on the host cores.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "mllm-advanced_b200"))
+
+LAYERS = 28
+# name, K, N, has_bias  (mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:38-44,86-93 of the reference project)
+LINEARS = [("q", 1536, 1536, True), ("k", 1536, 256, True), ("v", 1536, 256, True), ("o", 1536, 1536, False),
+           ("gate", 1536, 8960, False), ("up", 1536, 8960, False), ("down", 8960, 1536, False)]
+PREFILL_M = 512
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def algorithmic_bytes(m, k, n, has_bias):
+    return n * k // 2 + n * (k // 32) * 2 + m * k * 4 + m * n * 4 + (n * 4 if has_bias else 0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d.get("bf16_tflops"))), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.samples, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self, t0, t1):
+        sm, mx, reasons = [], 0.0, set()
+        for t, line in self.samples:
+            if t < t0 - 0.05 or t > t1 + 0.05:
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:  # region shorter than the sampling period: use every sample we have
+            for _, line in self.samples:
+                parts = [p.strip() for p in line.split(",")]
+                try:
+                    sm.append(float(parts[0]))
+                    mx = max(mx, float(parts[1]))
+                except (ValueError, IndexError):
+                    pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------ CPU baselines
+def cpu_has(flag):
+    try:
+        return flag in open("/proc/cpuinfo").read()
+    except Exception:
+        return False
+
+
+def load_x86_ref():
+    d = os.path.join(ROOT, "oracle", "_ref")
+    names = (["libx86q4k_ref_avx512.so"] if cpu_has("avx512f") and cpu_has("avx512bw") else []) + ["libx86q4k_ref_avx2.so"]
+    for n in names:
+        p = os.path.join(d, n)
+        if os.path.exists(p):
+            L = C.CDLL(p)
+            L.x86ref_q4k_row_bytes.restype = C.c_size_t
+            L.x86ref_q8k_row_bytes.restype = C.c_size_t
+            L.x86ref_quantize_weights.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+            L.x86ref_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                        C.c_int, C.c_void_p]
+            return L, n
+    return None, None
+
+
+def time_reference_cpu(budget_s=12.0, steps=None, warmup=1):
+    """One decoder layer's seven linears at M=1 on the reference's X86 int4 kernels (Q4_K x Q8_K -
+    a different int4 format from the Arm W4A32 path, same 0.5625 bytes per weight), all host threads.
+    Returns (GB/s over the algorithmic W4A32 bytes of those linears, info dict)."""
+    L, libname = load_x86_ref()
+    if L is None:
+        return None, {"why": "oracle/_ref/libx86q4k_ref_*.so not built"}
+    rng = np.random.default_rng(0)
+    threads = L.x86ref_max_threads()
+    variant = 1 if L.x86ref_has_avx512() else 0
+    mats = []
+    for name, k, n, hb in LINEARS:
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        wq = np.empty(n * L.x86ref_q4k_row_bytes(k), np.uint8)
+        L.x86ref_quantize_weights(w.ctypes.data, n, k, wq.ctypes.data)
+        x = rng.standard_normal((1, k)).astype(np.float32)
+        y = np.empty((1, n), np.float32)
+        ws = np.empty(L.x86ref_q8k_row_bytes(k) + 64, np.uint8)
+        mats.append((k, n, hb, wq, x, y, ws))
+
+    def one_pass():
+        for k, n, hb, wq, x, y, ws in mats:
+            L.x86ref_linear(x.ctypes.data, wq.ctypes.data, y.ctypes.data, 1, n, k, threads, variant, ws.ctypes.data)
+
+    for _ in range(max(1, warmup)):
+        one_pass()
+    t0 = time.perf_counter()
+    one_pass()
+    dt1 = time.perf_counter() - t0
+    reps = steps if steps else int(max(3, min(2000, budget_s / max(dt1, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        one_pass()
+    dt = (time.perf_counter() - t0) / reps
+    nbytes = sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
+    return nbytes / dt / 1e9, {"cores": threads, "lib": libname, "variant": "avx512f" if variant else "avx2",
+                              "ms_per_layer": dt * 1e3, "reps": reps,
+                              "sample": f"one decoder layer (7 linears, M=1) x {reps} passes, Q4_K x Q8_K kernels of the "
+                                        "reference X86 backend, OpenMP over output rows"}
+
+
+def time_oracle_port(budget_s=6.0):
+    """The same sample on the C restatement of the W4A32 arithmetic (same format as the GPU path)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import Oracle
+    o = Oracle()
+    rng = np.random.default_rng(0)
+    mats = []
+    for name, k, n, hb in LINEARS:
+        q = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+        s = ((np.abs(rng.standard_normal((n, k // 32))) * 0.02 / 7).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        x = rng.standard_normal((1, k)).astype(np.float32)
+        mats.append((x, q, s))
+    t0 = time.perf_counter()
+    for x, q, s in mats:
+        o.linear(x, q, s)
+    dt1 = time.perf_counter() - t0
+    reps = int(max(2, min(200, budget_s / max(dt1, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for x, q, s in mats:
+            o.linear(x, q, s)
+    dt = (time.perf_counter() - t0) / reps
+    nbytes = sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
+    return nbytes / dt / 1e9, o.lib.oracle_num_threads(), dt * 1e3
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    val, info = time_reference_cpu(budget_s=20.0, steps=None, warmup=max(1, args.warmup))
+    if val is None:
+        print(json.dumps({"impl": "reference", "unavailable": info["why"]}))
+        return
+    step_bytes = LAYERS * sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
+    ms_per_step = step_bytes / (val * 1e9) * 1e3
+    line = {"impl": "reference", "metric": "W4A32 decode-linear HBM GB/s", "value": val, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32 -> f32",
+            "data": "synthetic",
+            "config": {"workload": "qwen2-1.5b-decode-linears", "layers": LAYERS, "M": 1,
+                       "note": "each step of this arm is a bounded sample: one layer's 7 linears; ms_per_step scales it to 28 layers"},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": info["cores"], "kind": "reference",
+                             "sample": info["sample"], "variant": info["variant"]},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------ GPU side
+def make_random_weights(mb, torch, n, k, has_bias, gen, scale_mode=0):
+    """Random int4 + scales (BASELINE config 0 distributions), assembled as a blob on the device and
+    repacked there: no host quantization of 1.3 G weights."""
+    dev = "cuda"
+    total = mb.prepack_size(n, k, has_bias)
+    blob = torch.zeros(total, dtype=torch.uint8, device=dev)
+    # section offsets of a blob of this shape (the repack takes the shape as arguments, not from the header)
+    a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    mb.lib().mllmb200_w4a32_blob_offsets(n, k, int(has_bias), C.byref(a), C.byref(b), C.byref(c))
+    nib = torch.randint(0, 256, (n * (k // 2),), dtype=torch.uint8, device=dev, generator=gen)
+    sc = (torch.randn((n * (k // 32),), device=dev, generator=gen).abs() * (0.02 / 7.0))
+    sc16 = (sc.view(torch.int32) >> 16).to(torch.int16)
+    blob[a.value:a.value + nib.numel()] = nib
+    blob[b.value:b.value + sc16.numel() * 2] = sc16.view(torch.uint8)
+    if has_bias:
+        bias = torch.randn((n,), device=dev, generator=gen) * 0.02
+        blob[c.value:c.value + n * 4] = bias.view(torch.uint8)
+    tiled = torch.empty(mb.tiled_size(n, k), dtype=torch.uint8, device=dev)
+    st = mb.lib().mllmb200_w4a32_repack_device(blob.data_ptr(), n, k, scale_mode, int(has_bias), 0, n, tiled.data_ptr(),
+                                               C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0, mb.status_str(st)
+    torch.cuda.synchronize()
+    return mb.W4A32Weights(tiled, n, k, scale_mode, int(has_bias))
+
+
+def event_time_ms(torch, fn, iters):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_gpu(args):
+    import torch
+    import mllm_b200 as mb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    mb.lib()  # fails loudly when the CUDA library is missing
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+
+    # ---- weights: 28 layers x 7 linears, each its own tiled buffer
+    layers = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(LAYERS)]
+    xs = {k: torch.randn((1, k), device="cuda", generator=gen) for k in (1536, 8960)}
+    ys = {n: torch.empty((1, n), device="cuda") for n in (1536, 256, 8960)}
+    stream = torch.cuda.Stream()
+    pdl = not args.no_pdl
+    ws = torch.empty(mb.workspace_size(PREFILL_M, 8960), dtype=torch.uint8, device="cuda")
+
+    def decode_pass():
+        for lw in layers:
+            for w in lw:
+                mb.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream, pdl=pdl)
+
+    launches_per_step = LAYERS * len(LINEARS)
+    step_bytes = LAYERS * sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
+
+    with torch.cuda.stream(stream):
+        decode_pass()  # configures kernel attributes before capture
+    stream.synchronize()
+    mb.check_device_status(stream)
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            decode_pass()
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            with torch.cuda.stream(stream):
+                decode_pass()
+
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    # graph.replay() launches on torch's current stream: time on that stream
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    timing_stream = torch.cuda.current_stream() if graph is not None else stream
+    t_wall0 = time.time()
+    e0.record(timing_stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(timing_stream)
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms_total = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    mb.check_device_status()
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- everything below is extra reporting, outside the headline timed region
+    per_launch_us = ms_per_step * 1e3 / launches_per_step
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "frac_of_8TBs_spec": achieved / 8000.0, "peak_kind": f"of {peak_kind}", "traffic": None,
+                "kernel": "w4a32_gemv_kernel<1>", "avg_launch_us": per_launch_us,
+                "algorithmic_bytes_per_launch": step_bytes / launches_per_step}
+    tr = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+    if os.path.exists(tr):
+        try:
+            roofline["traffic"] = json.load(open(tr)).get("traffic_bytes_per_launch_avg")
+        except Exception:
+            pass
+
+    line = {"metric": "W4A32 decode-linear HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32 -> f32", "data": "synthetic",
+            "config": {"workload": "qwen2-1.5b-decode-linears", "layers": LAYERS, "linears_per_layer": len(LINEARS),
+                       "M": 1, "weight_bytes_per_step": LAYERS * 26320896, "algorithmic_bytes_per_step": step_bytes,
+                       "l2": "737 MB of weights per step > 126 MB L2: no flush between steps",
+                       "launch": ("cuda-graph replay" if graph is not None else "stream launches") + (", PDL" if pdl else ""),
+                       "parallelism": "replicas (one token per GPU)" if world > 1 else "single GPU"},
+            "roofline": roofline, "gpu_launches": args.steps * launches_per_step,
+            "tokens_per_s_linears_only": world * 1e3 / ms_per_step}
+
+    if rank == 0:
+        sampler.stop()
+        line["clocks"] = sampler.summary(t_wall0, t_wall1)
+
+    if rank == 0 and not args.quick:
+        # per-shape GEMV numbers, each over its 28 distinct weight copies
+        per_shape = {}
+        for idx, (name, k, n, hb) in enumerate(LINEARS):
+            def shape_pass(idx=idx, k=k, n=n):
+                for lw in layers:
+                    mb.linear_forward(xs[k], lw[idx], out=ys[n], workspace=ws, stream=stream, pdl=pdl)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                shape_pass()
+            for _ in range(3):
+                g.replay()
+            ms = event_time_ms(torch, g.replay, 10)
+            by = algorithmic_bytes(1, k, n, hb)
+            per_shape[f"{name}_{k}x{n}"] = {"us": ms * 1e3 / LAYERS, "GBs": by * LAYERS / (ms * 1e-3) / 1e9}
+            del g
+        line["per_shape"] = per_shape
+
+        # prefill: the same seven linears at M=512 (one layer after another, all 28 layers)
+        xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
+        yp = {n: torch.empty((PREFILL_M, n), device="cuda") for n in (1536, 256, 8960)}
+        n_pf_layers = LAYERS if not args.fast_prefill else 2
+
+        def prefill_pass():
+            for lw in layers[:n_pf_layers]:
+                for w in lw:
+                    mb.linear_forward(xp[w.k], w, out=yp[w.n], workspace=ws, stream=stream)
+        with torch.cuda.stream(stream):
+            prefill_pass()
+        stream.synchronize()
+        with torch.cuda.stream(stream):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                prefill_pass()
+            e1.record(stream)
+        stream.synchronize()
+        ms_pf = e0.elapsed_time(e1) / 3
+        flops = n_pf_layers * sum(2 * PREFILL_M * k * n for _, k, n, _ in LINEARS)
+        kern = {1: "gemv", 2: "simt-dp4a", 3: "tcgen05"}[mb.lib().mllmb200_w4a32_select_kernel(PREFILL_M, 1536, 8960)]
+        line["prefill"] = {"M": PREFILL_M, "layers": n_pf_layers, "ms": ms_pf, "tflops": flops / (ms_pf * 1e-3) / 1e12,
+                           "kernel": kern, "unit": "TOP/s (2*M*N*K int8 ops)",
+                           "frac_of_bf16_peak": flops / (ms_pf * 1e-3) / 1e12 / tensor_peak, "peak_kind": f"of {peak_kind}"}
+        mb.check_device_status()
+
+        # e2e: the same step with HOST buffers - per linear an H2D copy of x from pinned memory, the
+        # forward, and a D2H copy of y - replayed as one graph; one synchronize per step.
+        hx = {k: torch.randn((1, k)).pin_memory() for k in (1536, 8960)}
+        hy = {n: torch.empty((1, n)).pin_memory() for n in (1536, 256, 8960)}
+
+        def e2e_pass():
+            with torch.cuda.stream(stream):
+                for lw in layers:
+                    for w in lw:
+                        xs[w.k].copy_(hx[w.k], non_blocking=True)
+                        mb.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream)
+                        hy[w.n].copy_(ys[w.n], non_blocking=True)
+        e2e_pass()
+        stream.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=stream):
+            for lw in layers:
+                for w in lw:
+                    xs[w.k].copy_(hx[w.k], non_blocking=True)
+                    mb.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream)
+                    hy[w.n].copy_(ys[w.n], non_blocking=True)
+        for _ in range(3):
+            g2.replay()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        iters = max(5, args.steps)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            g2.replay()
+            torch.cuda.current_stream().synchronize()  # the host reads y after every step
+        e1.record()
+        torch.cuda.synchronize()
+        ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / iters
+        h2d = LAYERS * sum(k * 4 for _, k, n, _ in LINEARS)
+        d2h = LAYERS * sum(n * 4 for _, k, n, _ in LINEARS)
+        line["e2e"] = {"value": step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "how": "per linear: pinned H2D of x, C-ABI forward, D2H of y; one graph per step; host sync every step"}
+        line["gpu_launches"] += 0  # e2e launches are outside the headline region
+
+        # CPU baselines on this box's host cores
+        val, info = time_reference_cpu(budget_s=10.0)
+        if val is not None:
+            line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": info["cores"], "kind": "reference",
+                                    "sample": info["sample"], "variant": info["variant"],
+                                    "ms_per_layer": info["ms_per_layer"]}
+        try:
+            pv, pc, pms = time_oracle_port(budget_s=6.0)
+            line["cpu_port"] = {"value": pv, "unit": "GB/s", "cores": pc, "kind": "port", "ms_per_layer": pms,
+                                "sample": "same sample on oracle/w4a32_oracle.c (W4A32 format, OpenMP over output rows)"}
+            if "cpu_baseline" not in line:
+                line["cpu_baseline"] = dict(line["cpu_port"])
+        except Exception as ex:  # the oracle is optional for the bench
+            line["cpu_port"] = {"unavailable": str(ex)[:100]}
+    elif rank == 0:
+        line["e2e"] = None
+
+    if world > 1:
+        tp = run_tp(args, torch, mb, dist, rank, world, gen)
+        if rank == 0 and tp is not None:
+            line["tp"] = tp
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_tp(args, torch, mb, dist, rank, world, gen):
+    """BASELINE config 4: W [28672, 8192] column-sharded over the ranks, x replicated, NCCL all-gather of y.
+    M=1 (GEMV) and a reduced M for the GEMM; device time, max over ranks."""
+    n_total, k = 28672, 8192
+    if n_total % (world * 32) != 0:
+        return None
+    n_loc = n_total // world
+    g = torch.Generator(device="cuda").manual_seed(99)  # same on every rank: only the shard differs
+    w = make_random_weights(mb, torch, n_loc, k, False, gen)
+    out = {}
+    for m in (1, 256):
+        x = torch.randn((m, k), device="cuda", generator=g)
+        y_loc = torch.empty((m, n_loc), device="cuda")
+        y_all = torch.empty((world, m, n_loc), device="cuda")
+        ws = torch.empty(mb.workspace_size(m, k), dtype=torch.uint8, device="cuda")
+
+        def fwd():
+            mb.linear_forward(x, w, out=y_loc, workspace=ws)
+
+        def fwd_gather():
+            mb.linear_forward(x, w, out=y_loc, workspace=ws)
+            dist.all_gather_into_tensor(y_all, y_loc)
+        res = {}
+        for name, fn in (("compute_ms", fwd), ("compute_allgather_ms", fwd_gather)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            ms = event_time_ms(torch, fn, 10)
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = float(t.item())
+        by = algorithmic_bytes(m, k, n_total, False)
+        res["GBs_weights_alg"] = by / (res["compute_allgather_ms"] * 1e-3) / 1e9
+        res["tflops"] = 2.0 * m * k * n_total / (res["compute_allgather_ms"] * 1e-3) / 1e12
+        out[f"M{m}"] = res
+    out["workload"] = "config4: W[28672,8192] int4 g32, column-sharded, NCCL all-gather of y [world, M, N/world]"
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch on the stream instead of replaying a CUDA graph")
+    ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
+    ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
+    ap.add_argument("--fast-prefill", action="store_true", help="time the prefill linears on 2 layers instead of 28")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

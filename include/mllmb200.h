@@ -1,0 +1,151 @@
+/*
+ * mllmb200.h - C ABI of the B200 (sm_100a) W4A32 quantized-linear library.
+ *
+ * This is the whole boundary between host code (the mllm CUDA backend in
+ * mllm-advanced_b200/backend/, or any FFI binding) and the CUDA kernels: plain pointers and
+ * sizes, no C++ or framework types.  Every function returns an mllmb200_status (0 = ok) unless
+ * stated otherwise and never calls exit().  Pointers named *_dev are device pointers on the
+ * current CUDA device; all others are host pointers.  `stream` is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).  Device work is enqueued asynchronously on
+ * `stream`; nothing here synchronizes unless its comment says so.
+ *
+ * Each entry point names the interface of the reference project (mllm-advanced, paths relative
+ * to its root) that it stands in for.
+ */
+#ifndef MLLMB200_H_
+#define MLLMB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define MLLMB200_API
+#else
+#define MLLMB200_API __attribute__((visibility("default")))
+#endif
+
+typedef enum mllmb200_status {
+  MLLMB200_OK = 0,
+  MLLMB200_INVALID_ARG = 1,   /* null pointer, non-positive size, bad stride, misaligned pointer */
+  MLLMB200_UNSUPPORTED = 2,   /* a shape or mode this build has no kernel for */
+  MLLMB200_CUDA_ERROR = 3,    /* a CUDA runtime call failed; see mllmb200_last_cuda_error() */
+  MLLMB200_TIMEOUT = 4,       /* a bounded device-side wait ran out (reported by mllmb200_check_device_status) */
+  MLLMB200_BAD_BLOB = 5,      /* pre-pack blob header does not match (magic, version, sizes) */
+  MLLMB200_TOO_LARGE = 6      /* request exceeds a fixed capacity (static scratch entry point) */
+} mllmb200_status;
+
+/* How the 2-byte per-group scale is encoded.
+ * BF16_TRUNC is what the reference does (tests/Arm/KaiLinearTest.hpp:133-143 without
+ * __ARM_FEATURE_BF16; call site mllm/Backends/Arm/Kernels/kai_linear.cpp:258). */
+typedef enum mllmb200_scale_mode {
+  MLLMB200_SCALE_BF16_TRUNC = 0,
+  MLLMB200_SCALE_BF16_RNE = 1,
+  MLLMB200_SCALE_FP16 = 2
+} mllmb200_scale_mode;
+
+/* Text for a status code.  Replaces the reference's MLLM_ERROR_EXIT messages
+ * (mllm/Utils/Log.hpp:59-64): the library reports, the caller decides whether to exit. */
+MLLMB200_API const char* mllmb200_status_str(int status);
+
+/* cudaError_t (as int) of the last failed CUDA call made by this library on this thread. */
+MLLMB200_API int mllmb200_last_cuda_error(void);
+
+MLLMB200_API int mllmb200_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Offline side (host): quantize + pre-pack.  Stands in for
+ *   KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk::quant_pack_rhs_size     (mllm/Backends/Arm/Kernels/kai_linear.cpp:302-309)
+ *   KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk::quant_pack_rhs_offline  (mllm/Backends/Arm/Kernels/kai_linear.cpp:311-348)
+ * The blob is what the quantization pass stores as the 1-D int8 weight tensor
+ * (mllm/Backends/Arm/Passes/KaiQuantizationPass.cpp:104-187).  Layout:
+ *   64-byte header {magic 'MB2W', version, N, K, group=32, scale_mode, has_bias, layout=0, ...}
+ *   nibbles  u8  [N][ceil(K/2)]   q+8, even k in the low half-byte        (kai_linear.cpp:276-287)
+ *   scales   u16 [N][ceil(K/32)]                                          (kai_linear.cpp:254-258)
+ *   bias     f32 [N]              only when has_bias
+ * each section starting on a 16-byte boundary.  The nibble and scale sections are bit-identical
+ * to what the reference's quant_nxk_qs4c32_f32 (kai_linear.cpp:220-291) produces.
+ * ------------------------------------------------------------------------------------------ */
+MLLMB200_API int mllmb200_w4a32_prepack_size(int N, int K, int has_bias, size_t* bytes);
+
+/* W: fp32 [N,K] row-major; bias: fp32 [N] or NULL; blob: prepack_size bytes (host). */
+MLLMB200_API int mllmb200_w4a32_quant_prepack(const float* W, const float* bias, int N, int K,
+                                              int scale_mode, void* blob);
+
+/* Same blob from already-quantized data (nibbles [N][ceil(K/2)], scales [N][ceil(K/32)]),
+ * for checkpoints that ship int4 + scales. */
+MLLMB200_API int mllmb200_w4a32_prepack_from_quantized(const uint8_t* nibbles, const uint16_t* scales,
+                                                       const float* bias, int N, int K, int scale_mode,
+                                                       void* blob);
+
+/* Reads a blob header (host memory). Any out pointer may be NULL. */
+MLLMB200_API int mllmb200_w4a32_blob_info(const void* blob, size_t blob_bytes, int* N, int* K,
+                                          int* scale_mode, int* has_bias);
+
+/* Byte offsets of the sections inside a blob of the given shape. */
+MLLMB200_API int mllmb200_w4a32_blob_offsets(int N, int K, int has_bias, size_t* nibbles_off,
+                                             size_t* scales_off, size_t* bias_off);
+
+/* ------------------------------------------------------------------------------------------
+ * Load side (device): repack rows [row_begin, row_begin+row_count) of a blob that was copied to
+ * device memory into the tile layout the kernels stream.  Stands in for the KleidiAI packing
+ * step kai_run_rhs_pack_nxk_qsi4c32p_qsu4c32s1s0 (call site kai_linear.cpp:335-344), which in
+ * the reference runs offline on the CPU; here it runs once in LinearOp::load on the GPU.
+ * A row range gives a tensor-parallel rank its output-channel shard.
+ * blob_dev and tiled_dev must be 16-byte aligned (256 for tiled_dev recommended).
+ * ------------------------------------------------------------------------------------------ */
+MLLMB200_API int mllmb200_w4a32_tiled_size(int N_rows, int K, size_t* bytes);
+
+MLLMB200_API int mllmb200_w4a32_repack_device(const void* blob_dev, int N, int K, int scale_mode,
+                                              int has_bias, int row_begin, int row_count,
+                                              void* tiled_dev, void* stream);
+
+/* Inverse of the repack (tile layout -> nibbles/scales/bias sections of a blob of row_count rows),
+ * used to prove the repack loses nothing. out_blob_dev must hold prepack_size(row_count,K,has_bias). */
+MLLMB200_API int mllmb200_w4a32_unpack_device(const void* tiled_dev, int row_count, int K,
+                                              void* out_blob_dev, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Forward.  Stands in for
+ *   KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk::workspace_size  (kai_linear.cpp:293-300)
+ *   KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk::matmul          (kai_linear.cpp:350-398)
+ * as called by ArmLinearOp::forward (mllm/Backends/Arm/Ops/LinearOp.cpp:32-133).
+ *   y[m,n] = lhs_scale[m] * sum_b( (float)( sum_{k in b} (a_q[m,k]+a_off[m]) * (u[n,k]-8) ) * s[n,b] ) + bias[n]
+ * with the per-row dynamic int8 activation quantization of kai_run_lhs_quant_pack_qai8dxp_f32
+ * (call site kai_linear.cpp:358-362) done on the device inside the call.
+ * x_dev: fp32 [M, ldx] (ldx >= K, elements); y_dev: fp32 [M, ldy] (ldy >= N).
+ * ws_dev: workspace_size(M,K) bytes, 256-byte aligned; may be NULL when that size is 0.
+ * N must equal the row_count the tiled buffer was repacked with.
+ * ------------------------------------------------------------------------------------------ */
+MLLMB200_API int mllmb200_w4a32_workspace_size(int M, int K, size_t* bytes);
+
+MLLMB200_API int mllmb200_w4a32_linear_forward(const float* x_dev, const void* tiled_dev, float* y_dev,
+                                               void* ws_dev, int M, int K, int N, int ldx, int ldy,
+                                               void* stream);
+
+/* Same, with the kernel family forced (tests and benchmarks):
+ * 0 auto, 1 streaming GEMV (M <= 4), 2 SIMT dp4a GEMM, 3 tcgen05 GEMM. */
+MLLMB200_API int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, float* y_dev,
+                                                  void* ws_dev, int M, int K, int N, int ldx, int ldy,
+                                                  int kernel, void* stream);
+
+/* Which kernel family `kernel = 0` picks for a shape (1, 2 or 3 as above). */
+MLLMB200_API int mllmb200_w4a32_select_kernel(int M, int K, int N);
+
+/* Activation quantization alone (rows -> int8 + {recip scale, -zero point} headers in the
+ * reference's row layout of k + 8 bytes, tests/Arm/KaiLinearTest.hpp:163-230), for parity tests.
+ * out_dev: M * (K + 8) bytes. */
+MLLMB200_API int mllmb200_w4a32_quant_activations(const float* x_dev, int M, int K, int ldx,
+                                                  void* out_dev, void* stream);
+
+/* Device-side status word (bounded waits that ran out, bad tile headers).  Synchronizes `stream`,
+ * reads and clears the word.  0 = clean. */
+MLLMB200_API int mllmb200_check_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLLMB200_H_ */

@@ -1,0 +1,177 @@
+// Device side of the C ABI (include/mllmb200.h): argument checks, kernel selection, launches.
+#include <cuda_runtime.h>
+
+#include "../../include/mllmb200.h"
+#include "device_common.cuh"
+
+namespace mllmb200 {
+// repack.cu
+__global__ void repack_cells_kernel(const uint8_t*, const uint16_t*, int, int, int, int, int, uint8_t*);
+__global__ void repack_rowdata_kernel(const uint8_t*, const float*, int, int, int, int, uint32_t, float*, float*);
+__global__ void unpack_cells_kernel(const uint8_t*, int, int, int, int, uint8_t*, uint16_t*);
+__global__ void unpack_bias_kernel(const float*, int, float*);
+// act_quant.cu
+__global__ void act_quant_reflayout_kernel(const float*, int, int, uint8_t*);
+__global__ void act_quant_ws_kernel(const float*, int, int, int, int8_t*, float2*);
+// gemv.cu / gemm_simt.cu / gemm_tc.cu
+cudaError_t launch_w4a32_gemv(const float*, const void*, float*, int, int, int, int, int, int, cudaStream_t);
+bool w4a32_gemv_supported(int m, int k, int n);
+cudaError_t launch_w4a32_gemm_simt(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
+cudaError_t launch_w4a32_gemm_tc(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
+bool w4a32_gemm_tc_supported(int m, int k, int n);
+
+static thread_local int t_last_cuda_error = 0;
+static int cuda_fail(cudaError_t e) {
+  t_last_cuda_error = (int)e;
+  return MLLMB200_CUDA_ERROR;
+}
+static inline size_t ws_aq_bytes(int m, int k) {
+  return align_up((size_t)m * blob_num_blocks(k) * kGroup, 256);
+}
+}  // namespace mllmb200
+
+using namespace mllmb200;
+
+extern "C" {
+
+int mllmb200_last_cuda_error(void) { return t_last_cuda_error; }
+
+int mllmb200_w4a32_tiled_size(int N_rows, int K, size_t* bytes) {
+  if (!bytes || N_rows <= 0 || K <= 0) return MLLMB200_INVALID_ARG;
+  *bytes = make_tiled_header(N_rows, K, 0, 0).total_bytes;
+  return MLLMB200_OK;
+}
+
+int mllmb200_w4a32_repack_device(const void* blob_dev, int N, int K, int scale_mode, int has_bias, int row_begin,
+                                 int row_count, void* tiled_dev, void* stream) {
+  if (!blob_dev || !tiled_dev || N <= 0 || K <= 0 || row_count <= 0 || row_begin < 0 || row_begin + row_count > N)
+    return MLLMB200_INVALID_ARG;
+  if (scale_mode < 0 || scale_mode > 2) return MLLMB200_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(blob_dev) & 15u) || (reinterpret_cast<uintptr_t>(tiled_dev) & 15u))
+    return MLLMB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BlobHeader bh = make_blob_header(N, K, scale_mode, has_bias);
+  const TiledHeader th = make_tiled_header(row_count, K, scale_mode, has_bias);
+  const uint8_t* blob = static_cast<const uint8_t*>(blob_dev);
+  uint8_t* tiled = static_cast<uint8_t*>(tiled_dev);
+  cudaError_t e = cudaMemcpyAsync(tiled, &th, sizeof(th), cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const long long items = (long long)th.num_panels * th.num_groups * kPanelRows;
+  const int blocks = (int)std::min<long long>((items + 255) / 256, 148 * 16);
+  repack_cells_kernel<<<blocks, 256, 0, st>>>(blob + bh.nibbles_off,
+                                              reinterpret_cast<const uint16_t*>(blob + bh.scales_off), K, row_begin,
+                                              row_count, (int)th.num_groups, (int)th.num_panels, tiled + th.cells_off);
+  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
+  const int rows_pad = (int)th.num_panels * kPanelRows;
+  const int blocks2 = std::min((rows_pad + 7) / 8, 148 * 8);
+  repack_rowdata_kernel<<<blocks2, 256, 0, st>>>(
+      tiled + th.cells_off, has_bias ? reinterpret_cast<const float*>(blob + bh.bias_off) : nullptr, row_begin,
+      row_count, (int)th.num_groups, (int)th.num_panels, (uint32_t)scale_mode,
+      reinterpret_cast<float*>(tiled + th.zsum_off), reinterpret_cast<float*>(tiled + th.bias_off));
+  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
+  return MLLMB200_OK;
+}
+
+int mllmb200_w4a32_unpack_device(const void* tiled_dev, int row_count, int K, void* out_blob_dev, void* stream) {
+  if (!tiled_dev || !out_blob_dev || row_count <= 0 || K <= 0) return MLLMB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the header is small: read it back to learn scale_mode / has_bias (synchronizes the stream)
+  TiledHeader th;
+  cudaError_t e = cudaMemcpyAsync(&th, tiled_dev, sizeof(th), cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return cuda_fail(e);
+  if (th.magic != kTiledMagic || th.n != (uint32_t)row_count || th.k != (uint32_t)K) return MLLMB200_BAD_BLOB;
+  const BlobHeader bh = make_blob_header(row_count, K, (int)th.scale_mode, (int)th.has_bias);
+  uint8_t* out = static_cast<uint8_t*>(out_blob_dev);
+  const uint8_t* tiled = static_cast<const uint8_t*>(tiled_dev);
+  if ((e = cudaMemsetAsync(out, 0, bh.total_bytes, st)) != cudaSuccess) return cuda_fail(e);
+  if ((e = cudaMemcpyAsync(out, &bh, sizeof(bh), cudaMemcpyHostToDevice, st)) != cudaSuccess) return cuda_fail(e);
+  const long long items = (long long)th.num_panels * th.num_groups * kPanelRows;
+  const int blocks = (int)std::min<long long>((items + 255) / 256, 148 * 16);
+  unpack_cells_kernel<<<blocks, 256, 0, st>>>(tiled + th.cells_off, K, row_count, (int)th.num_groups,
+                                              (int)th.num_panels, out + bh.nibbles_off,
+                                              reinterpret_cast<uint16_t*>(out + bh.scales_off));
+  if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
+  if (th.has_bias) {
+    unpack_bias_kernel<<<std::min((row_count + 255) / 256, 1024), 256, 0, st>>>(
+        reinterpret_cast<const float*>(tiled + th.bias_off), row_count, reinterpret_cast<float*>(out + bh.bias_off));
+    if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
+  }
+  // the header copy above read from a stack variable: wait before it goes out of scope
+  if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return cuda_fail(e);
+  return MLLMB200_OK;
+}
+
+int mllmb200_w4a32_workspace_size(int M, int K, size_t* bytes) {
+  if (!bytes || M <= 0 || K <= 0) return MLLMB200_INVALID_ARG;
+  // M <= 4 runs the GEMV, which quantizes activations in shared memory and needs no workspace
+  // (unless the shape has no GEMV plan); the size is reported for every M so that one buffer
+  // sized for the largest M serves all calls.
+  *bytes = ws_aq_bytes(M, K) + align_up((size_t)M * sizeof(float2), 256);
+  return MLLMB200_OK;
+}
+
+int mllmb200_w4a32_quant_activations(const float* x_dev, int M, int K, int ldx, void* out_dev, void* stream) {
+  if (!x_dev || !out_dev || M <= 0 || K <= 0 || ldx < K) return MLLMB200_INVALID_ARG;
+  act_quant_reflayout_kernel<<<M, 256, 0, static_cast<cudaStream_t>(stream)>>>(x_dev, K, ldx,
+                                                                              static_cast<uint8_t*>(out_dev));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+}
+
+int mllmb200_w4a32_select_kernel(int M, int K, int N) {
+  if (w4a32_gemv_supported(M, K, N)) return 1;
+  if (w4a32_gemm_tc_supported(M, K, N)) return 3;
+  return 2;
+}
+
+int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, float* y_dev, void* ws_dev, int M,
+                                     int K, int N, int ldx, int ldy, int kernel, void* stream) {
+  if (!x_dev || !tiled_dev || !y_dev || M <= 0 || K <= 0 || N <= 0 || ldx < K || ldy < N) return MLLMB200_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(tiled_dev) & 15u) || (reinterpret_cast<uintptr_t>(x_dev) & 3u) ||
+      (reinterpret_cast<uintptr_t>(y_dev) & 3u))
+    return MLLMB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int use_pdl = (kernel >> 8) & 1;
+  kernel &= 0xFF;
+  if (kernel < 0 || kernel > 3) return MLLMB200_INVALID_ARG;
+  if (kernel == 0) kernel = mllmb200_w4a32_select_kernel(M, K, N);
+  if (kernel == 1) {
+    if (!w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
+    cudaError_t e = launch_w4a32_gemv(x_dev, tiled_dev, y_dev, M, K, N, ldx, ldy, use_pdl, st);
+    return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+  }
+  if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+  if (kernel == 3 && !w4a32_gemm_tc_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
+  int8_t* a_q = static_cast<int8_t*>(ws_dev);
+  float2* a_hdr = reinterpret_cast<float2*>(static_cast<uint8_t*>(ws_dev) + ws_aq_bytes(M, K));
+  const int k_pad = (int)blob_num_blocks(K) * kGroup;
+  act_quant_ws_kernel<<<M, 256, 0, st>>>(x_dev, K, ldx, k_pad, a_q, a_hdr);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = kernel == 3 ? launch_w4a32_gemm_tc(a_q, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st)
+                  : launch_w4a32_gemm_simt(a_q, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);
+  return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+}
+
+int mllmb200_w4a32_linear_forward(const float* x_dev, const void* tiled_dev, float* y_dev, void* ws_dev, int M, int K,
+                                  int N, int ldx, int ldy, void* stream) {
+  return mllmb200_w4a32_linear_forward_ex(x_dev, tiled_dev, y_dev, ws_dev, M, K, N, ldx, ldy, 0, stream);
+}
+
+int mllmb200_check_device_status(void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  unsigned int word = 0;
+  if ((e = cudaMemcpyFromSymbol(&word, g_device_status, sizeof(word))) != cudaSuccess) return cuda_fail(e);
+  if (word != 0) {
+    const unsigned int zero = 0;
+    if ((e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero))) != cudaSuccess) return cuda_fail(e);
+  }
+  if (word & kDevStatusTimeout) return MLLMB200_TIMEOUT;
+  if (word & kDevStatusBadHeader) return MLLMB200_BAD_BLOB;
+  return MLLMB200_OK;
+}
+
+}  // extern "C"

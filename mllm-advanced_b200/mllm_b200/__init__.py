@@ -1,0 +1,12 @@
+"""Python (ctypes) binding of the mllmb200 C ABI - used by the tests and bench.py.
+
+The product is the C ABI in include/mllmb200.h and the C++ backend under
+mllm-advanced_b200/backend/; this module only lets Python drive the same entry points.  torch is
+used for device memory and streams, nothing else: every computation goes through libmllm_b200.so,
+and importing this module fails loudly when that library has not been built.
+"""
+from .binding import (  # noqa: F401
+    SCALE_BF16_TRUNC, SCALE_BF16_RNE, SCALE_FP16, KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC,
+    MllmB200Error, lib, lib_path, status_str, prepack_size, quant_prepack, prepack_from_quantized, blob_info,
+    blob_sections, tiled_size, workspace_size, W4A32Weights, linear_forward, quant_activations, check_device_status,
+)

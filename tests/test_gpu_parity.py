@@ -1,0 +1,273 @@
+"""GPU parity tests: every result comes from libmllm_b200.so through the C ABI and is compared
+with the CPU oracle (oracle/w4a32_oracle.c) on the same seeded inputs.
+
+Bars: packing, repacking and activation quantization bit-exact; outputs max|diff| <= 1e-3 * rms(y)
+(the fp32-accumulate bar; the integer group sums are exact, only the order of the fp32 additions
+and the factored zero-point term differ from the scalar reference)."""
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import mllm_b200 as mb  # noqa: E402
+from oracle_lib import Oracle  # noqa: E402
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "kai_ref_golden.npz"))
+TOL = 1e-3  # times rms(y)
+
+
+@pytest.fixture(scope="module")
+def orc():
+    return Oracle()
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    mb.lib()
+    yield
+    mb.check_device_status()
+
+
+def make_case(rng, m, n, k, bias=True, x_scale=1.0, w_scale=0.02):
+    x = (rng.standard_normal((m, k)) * x_scale).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * w_scale).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32) * 0.1 if bias else None
+    return x, w, b
+
+
+def gpu_forward(x, blob, kernel=mb.KERNEL_AUTO, **kw):
+    wt = mb.W4A32Weights.from_blob(blob)
+    y = mb.linear_forward(torch.from_numpy(x).cuda(), wt, kernel=kernel, **kw)
+    torch.cuda.synchronize()
+    mb.check_device_status()
+    return y.cpu().numpy()
+
+
+def assert_close(y, ref, what=""):
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    err = float(np.max(np.abs(y.astype(np.float64) - ref)))
+    assert np.all(np.isfinite(y)), what
+    assert err <= TOL * max(rms, 1e-30), f"{what}: max|diff| {err:.3e} > {TOL} * rms {rms:.3e}"
+
+
+# ------------------------------------------------------------------ packing
+@pytest.mark.parametrize("n,k,mode,bias", [(8960, 1536, 0, False), (1536, 8960, 0, True), (256, 1536, 1, True),
+                                           (33, 257, 2, True), (5, 70, 0, False), (9, 71, 0, True), (64, 1176, 0, True),
+                                           (1, 32, 0, False), (31, 31, 0, True)])
+def test_repack_unpack_roundtrip_bit_exact(n, k, mode, bias):
+    rng = np.random.default_rng(n + k)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32) if bias else None
+    blob = mb.quant_prepack(w, b, mode)
+    wt = mb.W4A32Weights.from_blob(blob)
+    back = wt.unpack()
+    assert np.array_equal(back, blob)
+
+
+def test_repack_row_shards_roundtrip():
+    rng = np.random.default_rng(5)
+    n, k = 200, 160
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    blob = mb.quant_prepack(w, b)
+    nib, sc, bias = mb.blob_sections(blob)
+    for r0, cnt in [(0, 50), (50, 97), (147, 53)]:
+        wt = mb.W4A32Weights.from_blob(blob, row_begin=r0, row_count=cnt)
+        n2, s2, b2 = mb.blob_sections(wt.unpack())
+        assert np.array_equal(n2, nib[r0:r0 + cnt]) and np.array_equal(s2, sc[r0:r0 + cnt])
+        assert np.array_equal(b2, bias[r0:r0 + cnt])
+
+
+# ------------------------------------------------------------------ activation quantization
+@pytest.mark.parametrize("m,k", [(1, 1536), (4, 8960), (3, 71), (7, 1000), (2, 32), (5, 1176)])
+def test_activation_quant_bit_exact(orc, m, k):
+    rng = np.random.default_rng(m * 31 + k)
+    x = (rng.standard_normal((m, k)) * rng.uniform(0.05, 8.0)).astype(np.float32)
+    if m > 1:
+        x[1] = np.abs(x[1])          # all positive
+    if m > 2:
+        x[2] = 0.0                   # degenerate row
+    got = mb.quant_activations(torch.from_numpy(x).cuda())
+    assert np.array_equal(got, orc.quant_act(x))
+
+
+def test_activation_quant_fixture_golden():
+    x = Oracle().fill_uniform_random(1024, 4568).reshape(1, 1024)
+    got = mb.quant_activations(torch.from_numpy(x).cuda())
+    assert np.array_equal(got, GOLD["fixture_a"])
+
+
+# ------------------------------------------------------------------ forward: reference fixture + goldens
+def test_reference_fixture(orc):
+    """The reference's own test of this path: M=1, K=N=1024, srand 4568/4572, |ref-act| <= 1e-4
+    (tests/Arm/KaiLinearTest.hpp:387-463 of the reference project)."""
+    x = orc.fill_uniform_random(1024, 4568).reshape(1, 1024)
+    w = orc.fill_uniform_random(1024 * 1024, 4572).reshape(1024, 1024)
+    y = gpu_forward(x, mb.quant_prepack(w))
+    assert np.max(np.abs(y - GOLD["fixture_y"])) <= 1e-4
+    assert_close(y, GOLD["fixture_y"], "fixture")
+
+
+@pytest.mark.parametrize("name", sorted({k[:-2] for k in GOLD.files if k.startswith("r_") and k.endswith("_x")}))
+@pytest.mark.parametrize("kernel", [mb.KERNEL_AUTO, mb.KERNEL_SIMT])
+def test_ragged_goldens(name, kernel):
+    x, w = GOLD[name + "_x"], GOLD[name + "_w"]
+    y = gpu_forward(x, mb.quant_prepack(w), kernel)
+    ref = GOLD[name + "_y"]
+    assert_close(y, ref, name)
+
+
+# ------------------------------------------------------------------ forward: decode GEMV
+QWEN_SHAPES = [(1536, 1536), (1536, 256), (1536, 8960), (8960, 1536)]  # K -> N
+
+
+@pytest.mark.parametrize("k,n", QWEN_SHAPES + [(1024, 1024), (32, 32), (64, 40), (4096, 96), (1176, 1280)])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+def test_gemv_vs_oracle(orc, m, k, n):
+    rng = np.random.default_rng(k * 7 + n + m)
+    x, w, b = make_case(rng, m, n, k, bias=(n % 512 == 0))
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    y = gpu_forward(x, blob, mb.KERNEL_GEMV)
+    assert_close(y, ref, f"gemv m={m} k={k} n={n}")
+    y2 = gpu_forward(x, blob, mb.KERNEL_GEMV, pdl=True)
+    assert np.array_equal(y, y2)
+
+
+def test_cfg0_int4_uniform_fp16_scales(orc):
+    """BASELINE config 0: x ~ N(0,1) [1,1536]; q uniform in [-8,7]; scales |N(0,0.02)|/7 as fp16."""
+    g = torch.Generator().manual_seed(0)
+    n, k = 8960, 1536
+    x = torch.randn((1, k), generator=g).numpy()
+    qv = torch.randint(-8, 8, (n, k), generator=g).numpy()
+    sc = (torch.randn((n, k // 32), generator=g).abs() * 0.02 / 7)
+    u = (qv + 8).astype(np.uint8)
+    nib = (u[:, 0::2] | (u[:, 1::2] << 4)).astype(np.uint8)
+    for mode, s16 in ((mb.SCALE_FP16, sc.to(torch.float16).view(torch.int16).numpy().view(np.uint16)),
+                      (mb.SCALE_BF16_TRUNC, (sc.numpy().view(np.uint32) >> 16).astype(np.uint16))):
+        blob = mb.prepack_from_quantized(nib, s16, n, k, None, mode)
+        ref = orc.linear(x, nib, np.ascontiguousarray(s16), None, mode)
+        y = gpu_forward(x, blob)
+        assert_close(y, ref, f"cfg0 mode {mode}")
+
+
+def test_negative_zero_and_huge_activations(orc):
+    rng = np.random.default_rng(11)
+    m, n, k = 4, 96, 256
+    x, w, b = make_case(rng, m, n, k)
+    x[0] *= 1e4
+    x[1] = np.abs(x[1]) + 3.0      # zero point pinned at -128
+    x[2] = -np.abs(x[2]) - 3.0     # zero point pinned at 127
+    x[3] = 0.0
+    w[3] = 0.0                      # all scales -0.0
+    w[4, :32] = np.abs(w[4, :32])   # forces a negative scale in group 0
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    for kern in (mb.KERNEL_GEMV, mb.KERNEL_SIMT):
+        y = gpu_forward(x, blob, kern)
+        for r in range(m):  # per row: the rows have very different magnitudes
+            assert_close(y[r:r + 1], ref[r:r + 1], f"row {r} kernel {kern}")
+
+
+# ------------------------------------------------------------------ forward: GEMM paths
+@pytest.mark.parametrize("m,k,n", [(5, 1536, 256), (33, 1536, 1536), (64, 8960, 1536), (64, 1536, 8960),
+                                   (17, 1176, 1280), (100, 70, 45), (128, 1536, 256)])
+def test_simt_gemm_vs_oracle(orc, m, k, n):
+    rng = np.random.default_rng(m + k + n)
+    x, w, b = make_case(rng, m, n, k, x_scale=rng.uniform(0.2, 3.0))
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    y = gpu_forward(x, blob, mb.KERNEL_SIMT)
+    assert_close(y, ref, f"simt m={m} k={k} n={n}")
+
+
+def test_strided_input_and_output(orc):
+    rng = np.random.default_rng(21)
+    m, n, k = 3, 64, 128
+    x, w, b = make_case(rng, m, n, k)
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    wt = mb.W4A32Weights.from_blob(blob)
+    xb = torch.zeros((m, k + 24), device="cuda")
+    xb[:, :k] = torch.from_numpy(x).cuda()
+    yb = torch.full((m, n + 8), -7.0, device="cuda")
+    for kern in (mb.KERNEL_GEMV, mb.KERNEL_SIMT):
+        yb.fill_(-7.0)
+        mb.linear_forward(xb[:, :k], wt, out=yb[:, :n], kernel=kern)
+        torch.cuda.synchronize()
+        assert_close(yb[:, :n].cpu().numpy(), ref, f"strided kernel {kern}")
+        assert torch.all(yb[:, n:] == -7.0)
+
+
+# ------------------------------------------------------------------ size-independent properties at full size
+def test_row_shards_concatenate_to_full_result():
+    """Column (output-channel) sharding: each shard's output is bit-identical to that slice of the
+    unsharded output, for 2/4/8 shards - the tensor-parallel path needs no reduction."""
+    rng = np.random.default_rng(33)
+    n, k = 8960, 1536
+    x, w, b = make_case(rng, 1, n, k)
+    blob = mb.quant_prepack(w, b)
+    full = gpu_forward(x, blob)
+    xd = torch.from_numpy(x).cuda()
+    for g in (2, 4, 8):
+        per = n // g
+        parts = [mb.linear_forward(xd, mb.W4A32Weights.from_blob(blob, row_begin=r * per, row_count=per)).cpu().numpy()
+                 for r in range(g)]
+        assert np.array_equal(np.concatenate(parts, axis=1), full)
+
+
+def test_batch_rows_match_single_rows():
+    """Each activation row is quantized on its own: row r of an M=4 call equals the M=1 call on that row."""
+    rng = np.random.default_rng(34)
+    n, k = 1536, 8960
+    x, w, b = make_case(rng, 4, n, k)
+    blob = mb.quant_prepack(w, b)
+    y4 = gpu_forward(x, blob, mb.KERNEL_GEMV)
+    for r in range(4):
+        y1 = gpu_forward(x[r:r + 1], blob, mb.KERNEL_GEMV)
+        assert np.array_equal(y1[0], y4[r])
+    ys = gpu_forward(x, blob, mb.KERNEL_SIMT)
+    assert_close(ys, y4, "simt vs gemv")
+
+
+def test_zero_input_gives_bias():
+    rng = np.random.default_rng(35)
+    n, k = 512, 1536
+    _, w, b = make_case(rng, 2, n, k)
+    blob = mb.quant_prepack(w, b)
+    for kern in (mb.KERNEL_GEMV, mb.KERNEL_SIMT):
+        y = gpu_forward(np.zeros((2, k), np.float32), blob, kern)
+        assert np.array_equal(y, np.broadcast_to(b, (2, n)))
+
+
+def test_deterministic_repeat():
+    rng = np.random.default_rng(36)
+    x, w, b = make_case(rng, 1, 8960, 1536)
+    blob = mb.quant_prepack(w, b)
+    wt = mb.W4A32Weights.from_blob(blob)
+    xd = torch.from_numpy(x).cuda()
+    y0 = mb.linear_forward(xd, wt).clone()
+    for _ in range(5):
+        assert torch.equal(mb.linear_forward(xd, wt), y0)
+
+
+def test_bad_header_reports_status():
+    """Calling forward with N/K that do not match the tiled buffer is caught on the device and
+    reported as a status, not a fault."""
+    rng = np.random.default_rng(37)
+    x, w, b = make_case(rng, 1, 64, 64)
+    wt = mb.W4A32Weights.from_blob(mb.quant_prepack(w, b))
+    wt.n = 32  # lie about N (stays inside the buffer)
+    mb.linear_forward(torch.from_numpy(x).cuda(), wt, kernel=mb.KERNEL_GEMV)
+    with pytest.raises(mb.MllmB200Error) as e:
+        mb.check_device_status()
+    assert e.value.status == 5
+    mb.check_device_status()  # cleared
