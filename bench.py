@@ -394,6 +394,28 @@ def run_gpu(args):
             del g
         line["per_shape"] = per_shape
 
+        # the same step with the shared-activation linears grouped: (q,k,v) (o) (gate,up) (down) = 4 launches per layer
+        def grouped_pass():
+            for lw in layers:
+                mb.linear_forward_grouped(xs[1536], lw[0:3], outs=[ys[1536], ys[256], ys256b], workspace=ws, stream=stream, pdl=pdl)
+                mb.linear_forward(xs[1536], lw[3], out=ys[1536], workspace=ws, stream=stream, pdl=pdl)
+                mb.linear_forward_grouped(xs[1536], lw[4:6], outs=[ys[8960], ys8960b], workspace=ws, stream=stream, pdl=pdl)
+                mb.linear_forward(xs[8960], lw[6], out=ys[1536], workspace=ws, stream=stream, pdl=pdl)
+        ys256b, ys8960b = torch.empty((1, 256), device="cuda"), torch.empty((1, 8960), device="cuda")
+        with torch.cuda.stream(stream):
+            grouped_pass()
+        stream.synchronize()
+        gg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gg, stream=stream):
+            grouped_pass()
+        for _ in range(3):
+            gg.replay()
+        ms_g = event_time_ms(torch, gg.replay, max(5, args.steps))
+        line["grouped"] = {"launches_per_layer": 4, "ms_per_step": ms_g, "GBs": step_bytes / (ms_g * 1e-3) / 1e9,
+                           "frac": step_bytes / (ms_g * 1e-3) / 1e9 / hbm_peak,
+                           "how": "(q,k,v) and (gate,up) share their activations and run as one launch each"}
+        del gg
+
         # prefill: the same seven linears at M=512 (one layer after another, all 28 layers)
         xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
         yp = {n: torch.empty((PREFILL_M, n), device="cuda") for n in (1536, 256, 8960)}

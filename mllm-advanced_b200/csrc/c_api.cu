@@ -16,6 +16,8 @@ __global__ void act_quant_ws_kernel(const float*, int, int, int, int8_t*, float2
 // gemv.cu / gemm_simt.cu / gemm_tc.cu
 cudaError_t launch_w4a32_gemv(const float*, const void*, float*, int, int, int, int, int, int, cudaStream_t);
 bool w4a32_gemv_supported(int m, int k, int n);
+cudaError_t launch_w4a32_gemv_grouped(const float*, int, int, int, int, const void* const*, float* const*, const int*,
+                                      const int*, int, cudaStream_t);
 cudaError_t launch_w4a32_gemm_simt(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
 cudaError_t launch_w4a32_gemm_tc(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
 bool w4a32_gemm_tc_supported(int m, int k, int n);
@@ -157,6 +159,33 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
 int mllmb200_w4a32_linear_forward(const float* x_dev, const void* tiled_dev, float* y_dev, void* ws_dev, int M, int K,
                                   int N, int ldx, int ldy, void* stream) {
   return mllmb200_w4a32_linear_forward_ex(x_dev, tiled_dev, y_dev, ws_dev, M, K, N, ldx, ldy, 0, stream);
+}
+
+int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int ldx, int count,
+                                          const void* const* tiled_dev, float* const* y_dev, const int* N,
+                                          const int* ldy, void* ws_dev, int flags, void* stream) {
+  if (!x_dev || !tiled_dev || !y_dev || !N || !ldy || count < 1 || count > 4 || M <= 0 || K <= 0 || ldx < K)
+    return MLLMB200_INVALID_ARG;
+  bool gemv = true;
+  for (int i = 0; i < count; ++i) {
+    if (!tiled_dev[i] || !y_dev[i] || N[i] <= 0 || ldy[i] < N[i]) return MLLMB200_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(tiled_dev[i]) & 15u) || (reinterpret_cast<uintptr_t>(y_dev[i]) & 3u))
+      return MLLMB200_INVALID_ARG;
+    gemv = gemv && w4a32_gemv_supported(M, K, N[i]);
+  }
+  if (gemv) {
+    cudaError_t e = launch_w4a32_gemv_grouped(x_dev, M, K, ldx, count, tiled_dev, y_dev, N, ldy, (flags >> 8) & 1,
+                                              static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) return MLLMB200_OK;
+    if (e != cudaErrorInvalidValue) return cuda_fail(e);
+    // no joint plan (too much shared memory for the group): fall through to one call per matrix
+  }
+  for (int i = 0; i < count; ++i) {
+    const int st = mllmb200_w4a32_linear_forward_ex(x_dev, tiled_dev[i], y_dev[i], ws_dev, M, K, N[i], ldx, ldy[i],
+                                                    flags & 0x100, stream);
+    if (st != MLLMB200_OK) return st;
+  }
+  return MLLMB200_OK;
 }
 
 int mllmb200_check_device_status(void* stream) {

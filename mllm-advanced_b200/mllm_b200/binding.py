@@ -51,6 +51,8 @@ def lib():
         "mllmb200_w4a32_workspace_size": ([C.c_int, C.c_int, sz_p], C.c_int),
         "mllmb200_w4a32_linear_forward": ([vp, vp, vp, vp] + [C.c_int] * 5 + [vp], C.c_int),
         "mllmb200_w4a32_linear_forward_ex": ([vp, vp, vp, vp] + [C.c_int] * 6 + [vp], C.c_int),
+        "mllmb200_w4a32_linear_forward_grouped": ([vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp, C.c_int,
+                                                   vp], C.c_int),
         "mllmb200_w4a32_select_kernel": ([C.c_int, C.c_int, C.c_int], C.c_int),
         "mllmb200_w4a32_quant_activations": ([vp, C.c_int, C.c_int, C.c_int, vp, vp], C.c_int),
         "mllmb200_check_device_status": ([vp], C.c_int),
@@ -197,6 +199,27 @@ def linear_forward(x, weights, out=None, workspace=None, kernel=KERNEL_AUTO, str
                                                   kernel | (KERNEL_FLAG_PDL if pdl else 0), _stream_ptr(stream)),
            "linear_forward")
     return out
+
+
+def linear_forward_grouped(x, weights_list, outs=None, workspace=None, stream=None, pdl=False):
+    """Several linears on the same activations in one call (one launch for M <= 4)."""
+    import torch
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+    m, k = x.shape
+    cnt = len(weights_list)
+    assert 1 <= cnt <= 4 and all(w.k == k for w in weights_list)
+    if outs is None:
+        outs = [torch.empty((m, w.n), dtype=torch.float32, device=x.device) for w in weights_list]
+    if workspace is None:
+        workspace = _workspace_for(m, k, x.device)
+    tiled = (C.c_void_p * cnt)(*[w.tiled.data_ptr() for w in weights_list])
+    ys = (C.c_void_p * cnt)(*[o.data_ptr() for o in outs])
+    ns = (C.c_int * cnt)(*[w.n for w in weights_list])
+    ldy = (C.c_int * cnt)(*[o.stride(0) for o in outs])
+    _check(lib().mllmb200_w4a32_linear_forward_grouped(x.data_ptr(), m, k, x.stride(0), cnt, tiled, ys, ns, ldy,
+                                                       workspace.data_ptr(), KERNEL_FLAG_PDL if pdl else 0,
+                                                       _stream_ptr(stream)), "linear_forward_grouped")
+    return outs
 
 
 def quant_activations(x, stream=None):

@@ -238,6 +238,28 @@ def test_batch_rows_match_single_rows():
     assert_close(ys, y4, "simt vs gemv")
 
 
+@pytest.mark.parametrize("m", [1, 3, 4, 9])
+def test_grouped_equals_single_calls(m):
+    """q/k/v and gate/up style groups: one launch, results bit-identical to separate calls for the
+    same kernel family."""
+    rng = np.random.default_rng(40 + m)
+    k = 1536
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    for ns in ((1536, 256, 256), (8960, 8960), (40,), (64, 8960, 32, 1536)):
+        ws = [mb.W4A32Weights.from_blob(mb.quant_prepack(*make_case(rng, 1, n, k, bias=(i % 2 == 0))[1:]))
+              for i, n in enumerate(ns)]
+        outs = mb.linear_forward_grouped(xd, ws)
+        torch.cuda.synchronize()
+        mb.check_device_status()
+        for w, o in zip(ws, outs):
+            single = mb.linear_forward(xd, w)
+            if m <= 4:
+                assert_close(o.cpu().numpy(), single.cpu().numpy(), f"grouped m={m} n={w.n}")
+            else:
+                assert torch.equal(o, single)
+
+
 def test_zero_input_gives_bias():
     rng = np.random.default_rng(35)
     n, k = 512, 1536
