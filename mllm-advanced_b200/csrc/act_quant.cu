@@ -1,11 +1,131 @@
-// Dynamic per-row int8 activation quantization as stand-alone kernels:
-//  - act_quant_reflayout_kernel: the reference's row layout {float recip, int32 -zp, int8 q[k]}
-//    (tests/Arm/KaiLinearTest.hpp:163-230 of the reference project), used by parity tests.
-//  - act_quant_ws_kernel: the GEMM workspace: int8 [M][K_pad] in natural k order + row headers.
-// The M <= 4 GEMV path does this inside the GEMV kernel instead (see gemv.cu).
+// Dynamic per-row int8 activation quantization (reference project:
+// tests/Arm/KaiLinearTest.hpp:163-230; production call site
+// mllm/Backends/Arm/Kernels/kai_linear.cpp:358-362), as kernels of their own:
+//  - act_quant_records_kernel: what the GEMV and the SIMT GEMM consume - per row and K-group a
+//    48-byte record {4 words a_q for even k, 4 words a_q for odd k, -8 * sum(a_q), pad} (the byte
+//    order the nibble unpack produces, see layout.h) plus one {lhs_scale, a_off} header per row.
+//  - act_quant_reflayout_kernel: the reference's row layout {float recip, int32 -zp, int8 q[k]},
+//    used by the parity tests.
+// One CTA per activation row.  The row is read once from global memory and kept in registers
+// between the min/max pass and the quantization pass.
 #include "device_common.cuh"
 
 namespace mllmb200 {
+
+constexpr int kQuantThreads = 512;
+constexpr int kQuantItemsPerThread = 4;  // 8-value items kept in registers: covers K <= 16384
+
+// records: [M][num_groups] x 48 bytes; hdr: [M] {float lhs_scale, int32 a_off (bit pattern)}.
+__global__ void __launch_bounds__(kQuantThreads) act_quant_records_kernel(const float* __restrict__ x, int k, int ldx,
+                                                                          int num_groups, uint8_t* __restrict__ records,
+                                                                          float2* __restrict__ hdr, int use_pdl) {
+  __shared__ float scratch[64];
+  if (use_pdl) {
+    pdl_launch_dependents();  // the GEMV behind us may start fetching its weights
+    pdl_wait_prior();         // x may be the output of the kernel before us
+  }
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const float* row = x + (size_t)m * ldx;
+  const int num_items = num_groups * 4;  // item = 8 consecutive k
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+  float v[kQuantItemsPerThread][8];
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+#pragma unroll
+  for (int it = 0; it < kQuantItemsPerThread; ++it) {
+    const int item = tid + it * kQuantThreads;
+    const int k0 = item * 8;
+    if (item < num_items && k0 < k) {
+      if (vec && k0 + 8 <= k) {
+        const float4 a = *reinterpret_cast<const float4*>(row + k0);
+        const float4 b = *reinterpret_cast<const float4*>(row + k0 + 4);
+        v[it][0] = a.x; v[it][1] = a.y; v[it][2] = a.z; v[it][3] = a.w;
+        v[it][4] = b.x; v[it][5] = b.y; v[it][6] = b.z; v[it][7] = b.w;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          mn = fminf(mn, v[it][j]);
+          mx = fmaxf(mx, v[it][j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const bool in = k0 + j < k;
+          v[it][j] = in ? row[k0 + j] : 0.0f;
+          if (in) {
+            mn = fminf(mn, v[it][j]);
+            mx = fmaxf(mx, v[it][j]);
+          }
+        }
+      }
+    }
+  }
+  // rows longer than the register window: finish the min/max from memory
+  for (int kk = kQuantItemsPerThread * kQuantThreads * 8 + tid; kk < k; kk += kQuantThreads) {
+    mn = fminf(mn, row[kk]);
+    mx = fmaxf(mx, row[kk]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  const int warp = tid >> 5, lane = tid & 31;
+  if (lane == 0) {
+    scratch[warp] = mn;
+    scratch[32 + warp] = mx;
+  }
+  __syncthreads();
+  mn = lane < kQuantThreads / 32 ? scratch[lane] : 3.402823466e+38f;
+  mx = lane < kQuantThreads / 32 ? scratch[32 + lane] : -3.402823466e+38f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  const ActQuantParams p = act_quant_params(mn, mx);
+  if (tid == 0) hdr[m] = make_float2(p.recip_scale, __int_as_float(-p.nzp));
+
+  uint8_t* out = records + (size_t)m * num_groups * kActRecordBytes;
+  // Packs one 8-value item into its record.  Called by every thread of a warp together (the quad
+  // shuffles need full warps); `valid` masks the stores.
+  auto emit = [&](int item, bool valid, const int (&q8)[8]) {
+    const uint32_t lo = ((uint32_t)q8[0] & 0xFFu) | (((uint32_t)q8[2] & 0xFFu) << 8) |
+                        (((uint32_t)q8[4] & 0xFFu) << 16) | (((uint32_t)q8[6] & 0xFFu) << 24);
+    const uint32_t hi = ((uint32_t)q8[1] & 0xFFu) | (((uint32_t)q8[3] & 0xFFu) << 8) |
+                        (((uint32_t)q8[5] & 0xFFu) << 16) | (((uint32_t)q8[7] & 0xFFu) << 24);
+    int s = q8[0] + q8[1] + q8[2] + q8[3] + q8[4] + q8[5] + q8[6] + q8[7];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (valid) {
+      const int g = item >> 2, i = item & 3;
+      uint32_t* rec = reinterpret_cast<uint32_t*>(out + (size_t)g * kActRecordBytes);
+      rec[i] = lo;
+      rec[4 + i] = hi;
+      if (i == 0) *reinterpret_cast<uint4*>(rec + 8) = make_uint4((uint32_t)(-8 * s), 0u, 0u, 0u);
+    }
+  };
+  // items held in registers (trip count is a compile-time constant: full warps at the shuffles)
+#pragma unroll
+  for (int it = 0; it < kQuantItemsPerThread; ++it) {
+    const int item = tid + it * kQuantThreads;
+    if (it * kQuantThreads >= num_items) break;  // uniform over the CTA
+    const bool valid = item < num_items;
+    const int k0 = item * 8;
+    int q8[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q8[j] = (valid && k0 + j < k) ? act_quant_value(v[it][j], p) : 0;
+    emit(item, valid, q8);
+  }
+  // rows longer than the register window: the rest comes from memory (uniform trip count)
+  for (int base = kQuantItemsPerThread * kQuantThreads; base < num_items; base += kQuantThreads) {
+    const int item = base + tid;
+    const bool valid = item < num_items;
+    const int k0 = item * 8;
+    int q8[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q8[j] = (valid && k0 + j < k) ? act_quant_value(row[k0 + j], p) : 0;
+    emit(item, valid, q8);
+  }
+}
 
 // grid = M rows, block = 256
 __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* __restrict__ x, int k, int ldx,
@@ -29,28 +149,21 @@ __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* _
   for (int i = threadIdx.x; i < k; i += blockDim.x) dst[8 + i] = (uint8_t)(int8_t)act_quant_value(row[i], p);
 }
 
-// grid = M rows, block = 256.  a_q: int8 [M][k_pad] (k_pad = groups*32, padding = 0);
-// hdr: [M] {float lhs_scale, int32 a_off}.
-__global__ void __launch_bounds__(256) act_quant_ws_kernel(const float* __restrict__ x, int k, int ldx, int k_pad,
-                                                           int8_t* __restrict__ a_q, float2* __restrict__ hdr) {
-  __shared__ float scratch[64];
-  const int m = blockIdx.x;
-  const float* row = x + (size_t)m * ldx;
-  float mn, mx;
-  block_row_minmax(row, k, scratch, mn, mx);
-  const ActQuantParams p = act_quant_params(mn, mx);
-  if (threadIdx.x == 0) hdr[m] = make_float2(p.recip_scale, __int_as_float(-p.nzp));
-  uint32_t* dst = reinterpret_cast<uint32_t*>(a_q + (size_t)m * k_pad);
-  for (int w = threadIdx.x; w < (k_pad >> 2); w += blockDim.x) {
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int kk = 4 * w + j;
-      const int q = kk < k ? act_quant_value(row[kk], p) : 0;
-      packed |= ((uint32_t)q & 0xFFu) << (8 * j);
-    }
-    dst[w] = packed;
+cudaError_t launch_act_quant_records(const float* x, int m, int k, int ldx, uint8_t* records, float2* hdr, int use_pdl,
+                                     cudaStream_t stream) {
+  const int num_groups = (k + kGroup - 1) / kGroup;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)m, 1, 1);
+  cfg.blockDim = dim3(kQuantThreads, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  if (use_pdl) {
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
   }
+  return cudaLaunchKernelEx(&cfg, act_quant_records_kernel, x, k, ldx, num_groups, records, hdr, use_pdl);
 }
 
 }  // namespace mllmb200

@@ -12,14 +12,13 @@ __global__ void unpack_cells_kernel(const uint8_t*, int, int, int, int, uint8_t*
 __global__ void unpack_bias_kernel(const float*, int, float*);
 // act_quant.cu
 __global__ void act_quant_reflayout_kernel(const float*, int, int, uint8_t*);
-__global__ void act_quant_ws_kernel(const float*, int, int, int, int8_t*, float2*);
+cudaError_t launch_act_quant_records(const float*, int, int, int, uint8_t*, float2*, int, cudaStream_t);
 // gemv.cu / gemm_simt.cu / gemm_tc.cu
-cudaError_t launch_w4a32_gemv(const float*, const void*, float*, int, int, int, int, int, int, cudaStream_t);
 bool w4a32_gemv_supported(int m, int k, int n);
-cudaError_t launch_w4a32_gemv_grouped(const float*, int, int, int, int, const void* const*, float* const*, const int*,
-                                      const int*, int, cudaStream_t);
-cudaError_t launch_w4a32_gemm_simt(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
-cudaError_t launch_w4a32_gemm_tc(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
+cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
+                                      const int*, const int*, int, cudaStream_t);
+cudaError_t launch_w4a32_gemm_simt(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
+cudaError_t launch_w4a32_gemm_tc(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
 bool w4a32_gemm_tc_supported(int m, int k, int n);
 
 static thread_local int t_last_cuda_error = 0;
@@ -27,8 +26,9 @@ static int cuda_fail(cudaError_t e) {
   t_last_cuda_error = (int)e;
   return MLLMB200_CUDA_ERROR;
 }
-static inline size_t ws_aq_bytes(int m, int k) {
-  return align_up((size_t)m * blob_num_blocks(k) * kGroup, 256);
+// workspace = [activation records: M * groups * 48 bytes][row headers: M * 8 bytes], each 256-aligned
+static inline size_t ws_rec_bytes(int m, int k) {
+  return align_up((size_t)m * blob_num_blocks(k) * kActRecordBytes, 256);
 }
 }  // namespace mllmb200
 
@@ -106,10 +106,7 @@ int mllmb200_w4a32_unpack_device(const void* tiled_dev, int row_count, int K, vo
 
 int mllmb200_w4a32_workspace_size(int M, int K, size_t* bytes) {
   if (!bytes || M <= 0 || K <= 0) return MLLMB200_INVALID_ARG;
-  // M <= 4 runs the GEMV, which quantizes activations in shared memory and needs no workspace
-  // (unless the shape has no GEMV plan); the size is reported for every M so that one buffer
-  // sized for the largest M serves all calls.
-  *bytes = ws_aq_bytes(M, K) + align_up((size_t)M * sizeof(float2), 256);
+  *bytes = ws_rec_bytes(M, K) + align_up((size_t)M * sizeof(float2), 256);
   return MLLMB200_OK;
 }
 
@@ -127,6 +124,16 @@ int mllmb200_w4a32_select_kernel(int M, int K, int N) {
   return 2;
 }
 
+// Shared front half of every forward: validate, quantize the activations into the workspace.
+static int quantize_into_ws(const float* x_dev, void* ws_dev, int M, int K, int ldx, int use_pdl, cudaStream_t st,
+                            uint8_t** a_rec, float2** a_hdr) {
+  if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+  *a_rec = static_cast<uint8_t*>(ws_dev);
+  *a_hdr = reinterpret_cast<float2*>(static_cast<uint8_t*>(ws_dev) + ws_rec_bytes(M, K));
+  const cudaError_t e = launch_act_quant_records(x_dev, M, K, ldx, *a_rec, *a_hdr, use_pdl, st);
+  return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+}
+
 int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, float* y_dev, void* ws_dev, int M,
                                      int K, int N, int ldx, int ldy, int kernel, void* stream) {
   if (!x_dev || !tiled_dev || !y_dev || M <= 0 || K <= 0 || N <= 0 || ldx < K || ldy < N) return MLLMB200_INVALID_ARG;
@@ -138,21 +145,15 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
   kernel &= 0xFF;
   if (kernel < 0 || kernel > 3) return MLLMB200_INVALID_ARG;
   if (kernel == 0) kernel = mllmb200_w4a32_select_kernel(M, K, N);
-  if (kernel == 1) {
-    if (!w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
-    cudaError_t e = launch_w4a32_gemv(x_dev, tiled_dev, y_dev, M, K, N, ldx, ldy, use_pdl, st);
-    return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
-  }
-  if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+  if (kernel == 1 && !w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   if (kernel == 3 && !w4a32_gemm_tc_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
-  int8_t* a_q = static_cast<int8_t*>(ws_dev);
-  float2* a_hdr = reinterpret_cast<float2*>(static_cast<uint8_t*>(ws_dev) + ws_aq_bytes(M, K));
-  const int k_pad = (int)blob_num_blocks(K) * kGroup;
-  act_quant_ws_kernel<<<M, 256, 0, st>>>(x_dev, K, ldx, k_pad, a_q, a_hdr);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e);
-  e = kernel == 3 ? launch_w4a32_gemm_tc(a_q, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st)
-                  : launch_w4a32_gemm_simt(a_q, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);
+  uint8_t* a_rec;
+  float2* a_hdr;
+  if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, use_pdl & 1, st, &a_rec, &a_hdr)) return s;
+  cudaError_t e;
+  if (kernel == 1) e = launch_w4a32_gemv_grouped(a_rec, a_hdr, M, K, 1, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
+  else if (kernel == 3) e = launch_w4a32_gemm_tc(a_rec, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);
+  else e = launch_w4a32_gemm_simt(a_rec, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);
   return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
 }
 
@@ -174,8 +175,11 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
     gemv = gemv && w4a32_gemv_supported(M, K, N[i]);
   }
   if (gemv) {
-    cudaError_t e = launch_w4a32_gemv_grouped(x_dev, M, K, ldx, count, tiled_dev, y_dev, N, ldy, (flags >> 8) & 1,
-                                              static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* a_rec;
+    float2* a_hdr;
+    if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, (flags >> 8) & 1, st, &a_rec, &a_hdr)) return s;
+    cudaError_t e = launch_w4a32_gemv_grouped(a_rec, a_hdr, M, K, count, tiled_dev, y_dev, N, ldy, (flags >> 8) & 1, st);
     if (e == cudaSuccess) return MLLMB200_OK;
     if (e != cudaErrorInvalidValue) return cuda_fail(e);
     // no joint plan (too much shared memory for the group): fall through to one call per matrix

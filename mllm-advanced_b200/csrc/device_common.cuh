@@ -79,6 +79,11 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Split form: arrive early, wait later (hides the barrier latency behind independent work).
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // Address of `local_smem` in the shared memory of CTA `rank` of this cluster.
 __device__ __forceinline__ uint32_t map_to_cta(const void* local_smem, uint32_t rank) {
   uint32_t out;

@@ -1,5 +1,5 @@
 // SIMT (dp4a) W4A32 GEMM: the any-shape path (any M, K, N, including K not a multiple of 32).
-// It reads the quantized activations from the workspace written by act_quant_ws_kernel and the
+// It reads the quantized activation records written by act_quant_records_kernel and the
 // weights straight from the tile layout.  One CTA = one 32-row weight panel x 32 activation rows;
 // each of the 4 warps owns 8 activation rows, lane = weight row.  Every group sum is an exact
 // int32 and the fp32 accumulation runs over the K-groups in order, as in the reference's scalar
@@ -13,20 +13,9 @@ constexpr int kSimtRowsPerWarp = 8;
 constexpr int kSimtWarps = 4;
 constexpr int kSimtMTile = kSimtRowsPerWarp * kSimtWarps;
 
-// nibble word -> two words of signed int8 in natural k order
-__device__ __forceinline__ void unpack_word_signed(uint32_t w, int& k0123, int& k4567) {
-  const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-  uint32_t a = __byte_perm(lo, hi, 0x5140);  // k0 k1 k2 k3
-  uint32_t b = __byte_perm(lo, hi, 0x7362);  // k4 k5 k6 k7
-  // u - 8 per byte: flip bit 3 (4-bit two's complement) and sign-extend into the high half-byte
-  const uint32_t sa = (~a) & 0x08080808u, sb = (~b) & 0x08080808u;
-  k0123 = (int)((a ^ 0x08080808u) | (sa * 0x1Eu));
-  k4567 = (int)((b ^ 0x08080808u) | (sb * 0x1Eu));
-}
-
 __global__ void __launch_bounds__(kSimtWarps * 32) w4a32_gemm_simt_kernel(
-    const int8_t* __restrict__ a_q, const float2* __restrict__ a_hdr, const uint8_t* __restrict__ tiled,
-    float* __restrict__ y, int m, int k_pad, int n, int ldy, int num_groups, size_t zsum_off, size_t bias_off) {
+    const uint8_t* __restrict__ a_rec, const float2* __restrict__ a_hdr, const uint8_t* __restrict__ tiled,
+    float* __restrict__ y, int m, int n, int ldy, int num_groups, size_t zsum_off, size_t bias_off) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int panel = blockIdx.x;
   const int m0 = blockIdx.y * kSimtMTile + warp * kSimtRowsPerWarp;
@@ -41,26 +30,27 @@ __global__ void __launch_bounds__(kSimtWarps * 32) w4a32_gemm_simt_kernel(
     const uint8_t* cell = cells + (size_t)b * kCellBytes;
     const uint4 wq = *reinterpret_cast<const uint4*>(cell + lane * 16);
     const float s = decode_scale(*reinterpret_cast<const uint16_t*>(cell + kCellNibbleBytes + lane * 2), scale_mode);
-    int w[8];
-    unpack_word_signed(wq.x, w[0], w[1]);
-    unpack_word_signed(wq.y, w[2], w[3]);
-    unpack_word_signed(wq.z, w[4], w[5]);
-    unpack_word_signed(wq.w, w[6], w[7]);
+    const int lo0 = (int)(wq.x & 0x0F0F0F0Fu), hi0 = (int)((wq.x >> 4) & 0x0F0F0F0Fu);
+    const int lo1 = (int)(wq.y & 0x0F0F0F0Fu), hi1 = (int)((wq.y >> 4) & 0x0F0F0F0Fu);
+    const int lo2 = (int)(wq.z & 0x0F0F0F0Fu), hi2 = (int)((wq.z >> 4) & 0x0F0F0F0Fu);
+    const int lo3 = (int)(wq.w & 0x0F0F0F0Fu), hi3 = (int)((wq.w >> 4) & 0x0F0F0F0Fu);
 #pragma unroll
     for (int i = 0; i < kSimtRowsPerWarp; ++i) {
       const int mm = min(m0 + i, m - 1);
-      const int4* ap = reinterpret_cast<const int4*>(a_q + (size_t)mm * k_pad + b * kGroup);
-      const int4 a0 = __ldg(ap), a1 = __ldg(ap + 1);
-      int iacc = 0;
-      iacc = __dp4a(a0.x, w[0], iacc);
-      iacc = __dp4a(a0.y, w[1], iacc);
-      iacc = __dp4a(a0.z, w[2], iacc);
-      iacc = __dp4a(a0.w, w[3], iacc);
-      iacc = __dp4a(a1.x, w[4], iacc);
-      iacc = __dp4a(a1.y, w[5], iacc);
-      iacc = __dp4a(a1.z, w[6], iacc);
-      iacc = __dp4a(a1.w, w[7], iacc);
-      acc[i] = fmaf((float)iacc, s, acc[i]);
+      const uint8_t* rec = a_rec + ((size_t)mm * num_groups + b) * kActRecordBytes;
+      const int4 alo = __ldg(reinterpret_cast<const int4*>(rec));
+      const int4 ahi = __ldg(reinterpret_cast<const int4*>(rec + 16));
+      int ia = __ldg(reinterpret_cast<const int*>(rec + 32));
+      int ib = 0;
+      ia = __dp4a(alo.x, lo0, ia);
+      ib = __dp4a(ahi.x, hi0, ib);
+      ia = __dp4a(alo.y, lo1, ia);
+      ib = __dp4a(ahi.y, hi1, ib);
+      ia = __dp4a(alo.z, lo2, ia);
+      ib = __dp4a(ahi.z, hi2, ib);
+      ia = __dp4a(alo.w, lo3, ia);
+      ib = __dp4a(ahi.w, hi3, ib);
+      acc[i] = fmaf((float)(ia + ib), s, acc[i]);
     }
   }
   const int n_pad = panel * kPanelRows + lane;
@@ -80,7 +70,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) w4a32_gemm_simt_kernel(
   }
 }
 
-cudaError_t launch_w4a32_gemm_simt(const int8_t* a_q, const float2* a_hdr, const void* tiled, float* y, int m, int k,
+cudaError_t launch_w4a32_gemm_simt(const uint8_t* a_rec, const float2* a_hdr, const void* tiled, float* y, int m, int k,
                                    int n, int ldy, cudaStream_t stream) {
   const int num_groups = (k + kGroup - 1) / kGroup;
   const int num_panels = (n + kPanelRows - 1) / kPanelRows;
@@ -88,9 +78,8 @@ cudaError_t launch_w4a32_gemm_simt(const int8_t* a_q, const float2* a_hdr, const
   const int my = (m + kSimtMTile - 1) / kSimtMTile;
   if (my > 65535) return cudaErrorInvalidValue;
   dim3 grid((unsigned)num_panels, (unsigned)my, 1);
-  w4a32_gemm_simt_kernel<<<grid, kSimtWarps * 32, 0, stream>>>(a_q, a_hdr, static_cast<const uint8_t*>(tiled), y, m,
-                                                               num_groups * kGroup, n, ldy, num_groups, th.zsum_off,
-                                                               th.bias_off);
+  w4a32_gemm_simt_kernel<<<grid, kSimtWarps * 32, 0, stream>>>(a_rec, a_hdr, static_cast<const uint8_t*>(tiled), y, m, n,
+                                                               ldy, num_groups, th.zsum_off, th.bias_off);
   return cudaGetLastError();
 }
 

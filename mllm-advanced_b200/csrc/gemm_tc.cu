@@ -4,7 +4,7 @@
 
 namespace mllmb200 {
 bool w4a32_gemm_tc_supported(int, int, int) { return false; }
-cudaError_t launch_w4a32_gemm_tc(const int8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t) {
+cudaError_t launch_w4a32_gemm_tc(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t) {
   return cudaErrorNotSupported;
 }
 }  // namespace mllmb200
