@@ -4,6 +4,9 @@
 //  - act_quant_records_kernel: what the GEMV and the SIMT GEMM consume - per row and K-group a
 //    48-byte record {4 words a_q for even k, 4 words a_q for odd k, -8 * sum(a_q), pad} (the byte
 //    order the nibble unpack produces, see layout.h) plus one {lhs_scale, a_off} header per row.
+//    With `m8_pad > 0` the same kernel writes instead what the tcgen05 GEMM consumes as its B
+//    operand: [K-group][row/8][256-byte block], a block being 8 rows x 32 int8 in the canonical
+//    K-major core-matrix layout (two 128-byte core matrices, k in the same permuted order).
 //  - act_quant_reflayout_kernel: the reference's row layout {float recip, int32 -zp, int8 q[k]},
 //    used by the parity tests.
 // One CTA per activation row.  The row is read once from global memory and kept in registers
@@ -18,7 +21,8 @@ constexpr int kQuantItemsPerThread = 4;  // 8-value items kept in registers: cov
 // records: [M][num_groups] x 48 bytes; hdr: [M] {float lhs_scale, int32 a_off (bit pattern)}.
 __global__ void __launch_bounds__(kQuantThreads) act_quant_records_kernel(const float* __restrict__ x, int k, int ldx,
                                                                           int num_groups, uint8_t* __restrict__ records,
-                                                                          float2* __restrict__ hdr, int use_pdl) {
+                                                                          float2* __restrict__ hdr, int use_pdl,
+                                                                          int m8_pad) {
   __shared__ float scratch[64];
   if (use_pdl) {
     pdl_launch_dependents();  // the GEMV behind us may start fetching its weights
@@ -97,10 +101,15 @@ __global__ void __launch_bounds__(kQuantThreads) act_quant_records_kernel(const 
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     if (valid) {
       const int g = item >> 2, i = item & 3;
-      uint32_t* rec = reinterpret_cast<uint32_t*>(out + (size_t)g * kActRecordBytes);
-      rec[i] = lo;
-      rec[4 + i] = hi;
-      if (i == 0) *reinterpret_cast<uint4*>(rec + 8) = make_uint4((uint32_t)(-8 * s), 0u, 0u, 0u);
+      if (m8_pad > 0) {
+        uint8_t* blk = records + ((size_t)g * m8_pad + (m >> 3)) * 256;
+        *reinterpret_cast<uint2*>(blk + (i >> 1) * 128 + (m & 7) * 16 + (i & 1) * 8) = make_uint2(lo, hi);
+      } else {
+        uint32_t* rec = reinterpret_cast<uint32_t*>(out + (size_t)g * kActRecordBytes);
+        rec[i] = lo;
+        rec[4 + i] = hi;
+        if (i == 0) *reinterpret_cast<uint4*>(rec + 8) = make_uint4((uint32_t)(-8 * s), 0u, 0u, 0u);
+      }
     }
   };
   // items held in registers (trip count is a compile-time constant: full warps at the shuffles)
@@ -149,8 +158,9 @@ __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* _
   for (int i = threadIdx.x; i < k; i += blockDim.x) dst[8 + i] = (uint8_t)(int8_t)act_quant_value(row[i], p);
 }
 
+// m8_pad == 0: 48-byte records; m8_pad > 0: canonical 256-byte blocks with m8_pad blocks per K-group.
 cudaError_t launch_act_quant_records(const float* x, int m, int k, int ldx, uint8_t* records, float2* hdr, int use_pdl,
-                                     cudaStream_t stream) {
+                                     int m8_pad, cudaStream_t stream) {
   const int num_groups = (k + kGroup - 1) / kGroup;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)m, 1, 1);
@@ -163,7 +173,7 @@ cudaError_t launch_act_quant_records(const float* x, int m, int k, int ldx, uint
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  return cudaLaunchKernelEx(&cfg, act_quant_records_kernel, x, k, ldx, num_groups, records, hdr, use_pdl);
+  return cudaLaunchKernelEx(&cfg, act_quant_records_kernel, x, k, ldx, num_groups, records, hdr, use_pdl, m8_pad);
 }
 
 }  // namespace mllmb200

@@ -12,7 +12,8 @@ __global__ void unpack_cells_kernel(const uint8_t*, int, int, int, int, uint8_t*
 __global__ void unpack_bias_kernel(const float*, int, float*);
 // act_quant.cu
 __global__ void act_quant_reflayout_kernel(const float*, int, int, uint8_t*);
-cudaError_t launch_act_quant_records(const float*, int, int, int, uint8_t*, float2*, int, cudaStream_t);
+cudaError_t launch_act_quant_records(const float*, int, int, int, uint8_t*, float2*, int, int, cudaStream_t);
+int w4a32_gemm_tc_m_pad(int m);
 // gemv.cu / gemm_simt.cu / gemm_tc.cu
 bool w4a32_gemv_supported(int m, int k, int n);
 cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
@@ -26,9 +27,13 @@ static int cuda_fail(cudaError_t e) {
   t_last_cuda_error = (int)e;
   return MLLMB200_CUDA_ERROR;
 }
-// workspace = [activation records: M * groups * 48 bytes][row headers: M * 8 bytes], each 256-aligned
+// workspace = [quantized activations][row headers: M * 8 bytes], each 256-aligned.  The first part
+// holds either 48-byte records (GEMV, SIMT GEMM) or 256-byte operand blocks over rows padded to
+// the tcgen05 tile (tcgen05 GEMM); it is sized for the larger of the two.
 static inline size_t ws_rec_bytes(int m, int k) {
-  return align_up((size_t)m * blob_num_blocks(k) * kActRecordBytes, 256);
+  const size_t rec = (size_t)m * blob_num_blocks(k) * kActRecordBytes;
+  const size_t blk = (size_t)w4a32_gemm_tc_m_pad(m) * blob_num_blocks(k) * 32;
+  return align_up(rec > blk ? rec : blk, 256);
 }
 }  // namespace mllmb200
 
@@ -126,11 +131,12 @@ int mllmb200_w4a32_select_kernel(int M, int K, int N) {
 
 // Shared front half of every forward: validate, quantize the activations into the workspace.
 static int quantize_into_ws(const float* x_dev, void* ws_dev, int M, int K, int ldx, int use_pdl, cudaStream_t st,
-                            uint8_t** a_rec, float2** a_hdr) {
+                            uint8_t** a_rec, float2** a_hdr, bool tc_blocks = false) {
   if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
   *a_rec = static_cast<uint8_t*>(ws_dev);
   *a_hdr = reinterpret_cast<float2*>(static_cast<uint8_t*>(ws_dev) + ws_rec_bytes(M, K));
-  const cudaError_t e = launch_act_quant_records(x_dev, M, K, ldx, *a_rec, *a_hdr, use_pdl, st);
+  const cudaError_t e =
+      launch_act_quant_records(x_dev, M, K, ldx, *a_rec, *a_hdr, use_pdl, tc_blocks ? w4a32_gemm_tc_m_pad(M) / 8 : 0, st);
   return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
 }
 
@@ -149,7 +155,7 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
   if (kernel == 3 && !w4a32_gemm_tc_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   uint8_t* a_rec;
   float2* a_hdr;
-  if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, use_pdl & 1, st, &a_rec, &a_hdr)) return s;
+  if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, use_pdl & 1, st, &a_rec, &a_hdr, kernel == 3)) return s;
   cudaError_t e;
   if (kernel == 1) e = launch_w4a32_gemv_grouped(a_rec, a_hdr, M, K, 1, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
   else if (kernel == 3) e = launch_w4a32_gemm_tc(a_rec, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);

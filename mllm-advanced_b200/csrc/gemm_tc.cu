@@ -1,10 +1,345 @@
-// tcgen05 (5th-generation tensor core) W4A32 GEMM for large M.  Placeholder until the kernel lands:
-// reports "not supported" so that the dispatcher uses the SIMT path.
+// tcgen05 (5th-generation tensor core) W4A32 GEMM for prefill-sized M, sm_100a.
+//
+// The reference quantizes activations to int8 per row and accumulates every 32-wide K-group in
+// int32 before applying that group's weight scale (tests/Arm/KaiLinearTest.hpp:338-373 of the
+// reference project).  This kernel keeps exactly that arithmetic on the tensor cores:
+// tcgen05.mma kind::i8 (int8 x int8 -> int32 in tensor memory), one MMA per K-group (K = 32 is the
+// instruction's K for 8-bit types) with a fresh accumulator, and an epilogue that converts the
+// exact group sums to fp32 and applies s[n,b] with one FMA per element, in K order.
+//
+// Operand roles are swapped with respect to the usual GEMM so that the per-row weight scale is a
+// per-thread scalar in the epilogue:
+//   A (M_mma = 128) = 128 weight rows (4 panels of the tile layout), int8 = 16 * (nibble - 8),
+//                     written to shared memory by the dequant warps from the raw cells;
+//   B (N_mma = NT)  = NT activation rows, int8, pre-arranged by the quantization kernel in the
+//                     canonical K-major core-matrix layout, so one bulk copy per K-group delivers a
+//                     ready operand (no tensor map needed);
+//   D (tensor memory) = [128 lanes = weight rows] x [NT columns = activation rows], int32.
+// Both operands use the same permutation of k inside a K-group (the order the nibble masks
+// produce), which leaves every dot product unchanged.
+//
+// Warp roles (448 threads, one CTA per SM):
+//   warps 0-7   epilogue: warp w reads TMEM lanes 32*(w%4).. (its quadrant) and columns
+//               (w/4)*NT/2 ..; accumulators stay in registers for the whole K loop
+//   warps 8-11  dequant: thread j expands weight row j of the tile, 4 K-groups per stage
+//   warp 12     producer: bulk copies (cp.async.bulk) of raw weight cells and activation blocks
+//   warp 13     MMA issuer (one elected lane) and tensor-memory allocation
+// Shared memory: 4 stages of {raw cells 9 KB, B operand NT*128 B, A operand 16 KB}; tensor
+// memory: 4 accumulator stages of NT columns.  Every mbarrier wait is bounded (device_common.cuh).
 #include "device_common.cuh"
 
 namespace mllmb200 {
-bool w4a32_gemm_tc_supported(int, int, int) { return false; }
-cudaError_t launch_w4a32_gemm_tc(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t) {
-  return cudaErrorNotSupported;
+
+constexpr int kTcThreads = 448;
+constexpr int kTcStages = 4;        // shared-memory stages
+constexpr int kTcGroupsPerStage = 4;  // K-groups (of 32) per stage
+constexpr int kTcTileRows = 128;    // weight rows per CTA (= 4 panels)
+constexpr int kTcAccStages = 4;     // tensor-memory accumulator stages
+
+// ------------------------------------------------------------------ tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
 }
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// arrive on `bar` once every tcgen05 operation issued so far by this thread has completed
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D[tmem] = A[smem] * B[smem] (fresh accumulator), int8 x int8 -> int32
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+// 16 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, no-swizzle operand descriptor: core matrix = 8 rows x 16 bytes (128 contiguous bytes),
+// the two 16-byte K chunks of a row are `lbo` bytes apart, 8-row groups are `sbo` bytes apart.
+__device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+
+struct TcParams {
+  const uint8_t* a_blocks;  // activations, [num_groups][m8_pad][256 bytes] canonical blocks
+  const float2* a_hdr;      // [m] {lhs_scale, a_off bits}
+  const uint8_t* tiled;     // weights (TiledHeader at offset 0)
+  float* y;
+  int m, n, k, ldy;
+  int num_groups, num_panels, m8_pad;
+  size_t zsum_off, bias_off;
+};
+
+template <int NT>
+struct TcSmem {
+  static constexpr int kRawBytes = 4 * kTcGroupsPerStage * kCellBytes;  // 9216
+  static constexpr int kBBytes = kTcGroupsPerStage * NT * 32;
+  static constexpr int kABytes = kTcGroupsPerStage * kTcTileRows * 32;  // 16384
+  static constexpr int kStageBytes = kRawBytes + kBBytes + kABytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kTotal = kBarBytes + kTcStages * kStageBytes + 1024;  // + alignment slack
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcParams p) {
+  using S = TcSmem<NT>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [kTcStages]
+  uint64_t* stage_empty = raw_full + kTcStages;            // [kTcStages]
+  uint64_t* a_full = stage_empty + kTcStages;              // [kTcStages]
+  uint64_t* tmem_full = a_full + kTcStages;                // [kTcAccStages]
+  uint64_t* tmem_empty = tmem_full + kTcAccStages;         // [kTcAccStages]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + kTcAccStages);
+  uint8_t* stages = smem + S::kBarBytes;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile_n = blockIdx.x;  // 128 weight rows
+  const int tile_m = blockIdx.y;  // NT activation rows
+  const int panel0 = tile_n * 4;
+  const int m0 = tile_m * NT;
+  const int k_tiles = (p.num_groups + kTcGroupsPerStage - 1) / kTcGroupsPerStage;
+
+  if (tid == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&stage_empty[s], 1);
+      mbar_init(&a_full[s], 128);
+    }
+    for (int t = 0; t < kTcAccStages; ++t) {
+      mbar_init(&tmem_full[t], 1);
+      mbar_init(&tmem_empty[t], 8);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+  }
+  if (warp == 13) {
+    tmem_alloc(tmem_base_slot, (uint32_t)(kTcAccStages * NT));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 12) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      for (int it = 0; it < k_tiles; ++it) {
+        const int s = it % kTcStages;
+        const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
+        if (!mbar_wait_bounded(&stage_empty[s], ph ^ 1u)) break;
+        const int g0 = it * kTcGroupsPerStage;
+        const int ng = min(kTcGroupsPerStage, p.num_groups - g0);
+        const int np = min(4, p.num_panels - panel0);
+        uint8_t* st = stages + (size_t)s * S::kStageBytes;
+        mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCellBytes + ng * NT * 32));
+        for (int q = 0; q < np; ++q)
+          bulk_g2s(st + q * kTcGroupsPerStage * kCellBytes,
+                   p.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + q) * p.num_groups + g0) * kCellBytes,
+                   (uint32_t)(ng * kCellBytes), &raw_full[s]);
+        for (int g = 0; g < ng; ++g)
+          bulk_g2s(st + S::kRawBytes + g * NT * 32,
+                   p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 256, (uint32_t)(NT * 32), &raw_full[s]);
+      }
+    }
+  } else if (warp == 13) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = NT, M = 128
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
+      int cnt = 0;
+      bool ok = true;
+      for (int it = 0; it < k_tiles && ok; ++it) {
+        const int s = it % kTcStages;
+        const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
+        ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&a_full[s], ph);
+        if (!ok) break;
+        tc_fence_after();
+        const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
+        uint8_t* st = stages + (size_t)s * S::kStageBytes;
+        const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(st + S::kRawBytes + S::kBBytes);
+        for (int g = 0; g < ng; ++g, ++cnt) {
+          const int t = cnt % kTcAccStages;
+          ok = mbar_wait_bounded(&tmem_empty[t], ((uint32_t)(cnt / kTcAccStages) & 1u) ^ 1u);
+          if (!ok) break;
+          tc_fence_after();
+          tc_mma_i8(tmem_base + (uint32_t)(t * NT), make_kmajor_desc(a_addr + g * kTcTileRows * 32, 128, 256),
+                    make_kmajor_desc(b_addr + g * NT * 32, 128, 256), idesc);
+          tc_commit(&tmem_full[t]);
+        }
+        tc_commit(&stage_empty[s]);  // raw cells, A and B of this stage may be overwritten once these MMAs are done
+      }
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------ dequant: thread j = weight row j of the tile
+    const int j = tid - 8 * 32;
+    const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
+    const bool have_panel = panel0 + q < p.num_panels;
+    bool ok = true;
+    for (int it = 0; it < k_tiles && ok; ++it) {
+      const int s = it % kTcStages;
+      const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
+      ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&stage_empty[s], ph ^ 1u);
+      if (!ok) break;
+      const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
+      uint8_t* st = stages + (size_t)s * S::kStageBytes;
+      const uint8_t* raw = st + q * kTcGroupsPerStage * kCellBytes;
+      uint8_t* a_out = st + S::kRawBytes + S::kBBytes + (j >> 3) * 256 + (j & 7) * 16;
+      for (int g = 0; g < ng; ++g) {
+        uint4 w = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+        if (have_panel) w = *reinterpret_cast<const uint4*>(raw + g * kCellBytes + r * 16);
+        // byte = 16 * (nibble - 8) as signed int8: low nibbles shifted up, high nibbles in place, flip bit 7
+        uint4 c0, c1;
+        c0.x = ((w.x << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+        c0.y = (w.x & 0xF0F0F0F0u) ^ 0x80808080u;
+        c0.z = ((w.y << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+        c0.w = (w.y & 0xF0F0F0F0u) ^ 0x80808080u;
+        c1.x = ((w.z << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+        c1.y = (w.z & 0xF0F0F0F0u) ^ 0x80808080u;
+        c1.z = ((w.w << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
+        c1.w = (w.w & 0xF0F0F0F0u) ^ 0x80808080u;
+        *reinterpret_cast<uint4*>(a_out + g * kTcTileRows * 32) = c0;        // K chunk 0
+        *reinterpret_cast<uint4*>(a_out + g * kTcTileRows * 32 + 128) = c1;  // K chunk 1
+      }
+      fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
+      mbar_arrive(&a_full[s]);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    constexpr int CW = NT / 2;  // columns per warp
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;                // weight row inside the tile == TMEM lane
+    const int n = tile_n * kTcTileRows + row;
+    const bool have_panel = panel0 + quad < p.num_panels;
+    const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(p.tiled);
+    const uint32_t scale_mode = hdr->scale_mode;
+    const uint8_t* scale_ptr = p.tiled + sizeof(TiledHeader) + (size_t)(panel0 + quad) * p.num_groups * kCellBytes +
+                               kCellNibbleBytes + lane * 2;
+    float acc[CW];
+#pragma unroll
+    for (int c = 0; c < CW; ++c) acc[c] = 0.0f;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * CW);
+    bool ok = true;
+    for (int cnt = 0; cnt < p.num_groups && ok; ++cnt) {
+      const int t = cnt % kTcAccStages;
+      // group scale / 16 (the A operand carries 16 * weight); exact: a power-of-two factor
+      float s16 = 0.0f;
+      if (have_panel)
+        s16 = decode_scale(*reinterpret_cast<const uint16_t*>(scale_ptr + (size_t)cnt * kCellBytes), scale_mode) * 0.0625f;
+      ok = mbar_wait_bounded(&tmem_full[t], (uint32_t)(cnt / kTcAccStages) & 1u);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < CW; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(lane_addr + (uint32_t)(t * NT + c0), v);
+        tmem_ld_wait();
+        if (c0 + 16 >= CW) {  // last read of this accumulator stage: hand it back to the MMA issuer
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[t]);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          // exact int32 -> fp32 for |v| < 2^22: add 1.5 * 2^23 as an integer, subtract it as a float
+          const float f = __int_as_float((int)v[i] + 0x4B400000) - 12582912.0f;
+          acc[c0 + i] = fmaf(f, s16, acc[c0 + i]);
+        }
+      }
+    }
+    // y[m, n] = lhs_scale[m] * (acc + a_off[m] * zsum[n]) + bias[n]; lanes = consecutive n: coalesced per m
+    if (ok && n < p.n) {
+      const int n_pad = n;  // inside the padded per-row arrays
+      const float zs = reinterpret_cast<const float*>(p.tiled + p.zsum_off)[n_pad];
+      const float bs = reinterpret_cast<const float*>(p.tiled + p.bias_off)[n_pad];
+#pragma unroll
+      for (int c = 0; c < CW; ++c) {
+        const int m = m0 + half * CW + c;
+        if (m < p.m) {
+          const float2 h = p.a_hdr[m];
+          float v = fmaf((float)__float_as_int(h.y), zs, acc[c]);
+          v = fmaf(v, h.x, bs);
+          p.y[(size_t)m * p.ldy + n] = clamp_flt_max(v);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 13) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)(kTcAccStages * NT));
+  }
+}
+
+template <int NT>
+static cudaError_t launch_tc_t(const TcParams& prm, cudaStream_t stream) {
+  using S = TcSmem<NT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (!(dev >= 0 && dev < 64 && configured[dev])) {
+    e = cudaFuncSetAttribute(w4a32_gemm_tc_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  dim3 grid((unsigned)((prm.num_panels + 3) / 4), (unsigned)((prm.m + NT - 1) / NT), 1);
+  w4a32_gemm_tc_kernel<NT><<<grid, kTcThreads, S::kTotal, stream>>>(prm);
+  return cudaGetLastError();
+}
+
+// Rows of the activation block array are padded to a multiple of this (largest NT).
+int w4a32_gemm_tc_m_pad(int m) { return (m + 127) / 128 * 128; }
+
+bool w4a32_gemm_tc_supported(int m, int k, int n) {
+  // one CTA per SM holds 128 KB+ of shared memory and all tensor memory it allocates; any K, any N.
+  // Below ~17 rows the GEMV / SIMT paths are the better fit.
+  return m >= 17 && k >= 1 && n >= 1 && (size_t)((m + 127) / 128) <= 65535;
+}
+
+cudaError_t launch_w4a32_gemm_tc(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
+                                 int n, int ldy, cudaStream_t stream) {
+  TcParams prm;
+  prm.a_blocks = a_blocks;
+  prm.a_hdr = a_hdr;
+  prm.tiled = static_cast<const uint8_t*>(tiled);
+  prm.y = y;
+  prm.m = m;
+  prm.n = n;
+  prm.k = k;
+  prm.ldy = ldy;
+  prm.num_groups = (k + kGroup - 1) / kGroup;
+  prm.num_panels = (n + kPanelRows - 1) / kPanelRows;
+  prm.m8_pad = w4a32_gemm_tc_m_pad(m) / 8;
+  const TiledHeader th = make_tiled_header(n, k, 0, 0);
+  prm.zsum_off = th.zsum_off;
+  prm.bias_off = th.bias_off;
+  if (m <= 32) return launch_tc_t<32>(prm, stream);
+  if (m <= 64) return launch_tc_t<64>(prm, stream);
+  return launch_tc_t<128>(prm, stream);
+}
+
 }  // namespace mllmb200

@@ -188,6 +188,36 @@ def test_simt_gemm_vs_oracle(orc, m, k, n):
     assert_close(y, ref, f"simt m={m} k={k} n={n}")
 
 
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (17, 1536, 256), (33, 1536, 1536), (64, 8960, 1536),
+                                   (128, 1536, 8960), (100, 70, 45), (200, 1176, 1280), (512, 1536, 256),
+                                   (300, 4096, 96), (129, 32, 33)])
+def test_tcgen05_gemm_vs_oracle(orc, m, k, n):
+    """tcgen05 kind::i8 path: exact int32 group sums on the tensor cores, fp32 scale-accumulate in K order."""
+    rng = np.random.default_rng(m * 3 + k + n)
+    x, w, b = make_case(rng, m, n, k, x_scale=rng.uniform(0.2, 3.0))
+    if m > 40:
+        x[7] = np.abs(x[7]) + 1.0   # zero point -128
+        x[8] = 0.0
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    y = gpu_forward(x, blob, mb.KERNEL_TC)
+    assert_close(y, ref, f"tcgen05 m={m} k={k} n={n}")
+    y2 = gpu_forward(x, blob, mb.KERNEL_SIMT)
+    assert_close(y, y2, "tcgen05 vs simt")
+
+
+def test_tcgen05_prefill_layer_shapes_full_size():
+    """All seven linears of a decoder layer at M=512 (BASELINE config 1): tcgen05 vs SIMT path."""
+    rng = np.random.default_rng(77)
+    for k, n in QWEN_SHAPES:
+        x, w, b = make_case(rng, 512, n, k)
+        blob = mb.quant_prepack(w, b)
+        y = gpu_forward(x, blob, mb.KERNEL_TC)
+        y2 = gpu_forward(x, blob, mb.KERNEL_SIMT)
+        assert_close(y, y2, f"prefill k={k} n={n}")
+
+
 def test_strided_input_and_output(orc):
     rng = np.random.default_rng(21)
     m, n, k = 3, 64, 128
