@@ -32,7 +32,8 @@ static int cuda_fail(cudaError_t e) {
 // the tcgen05 tile (tcgen05 GEMM); it is sized for the larger of the two.
 static inline size_t ws_rec_bytes(int m, int k) {
   const size_t rec = (size_t)m * blob_num_blocks(k) * kActRecordBytes;
-  const size_t blk = (size_t)w4a32_gemm_tc_m_pad(m) * blob_num_blocks(k) * 32;
+  // operand blocks are only written when the tcgen05 path can be chosen for this M
+  const size_t blk = w4a32_gemm_tc_supported(m, k, 1) ? (size_t)w4a32_gemm_tc_m_pad(m) * blob_num_blocks(k) * 32 : 0;
   return align_up(rec > blk ? rec : blk, 256);
 }
 }  // namespace mllmb200
