@@ -151,6 +151,22 @@ MLLMB200_API int mllmb200_w4a32_select_kernel(int M, int K, int N);
 MLLMB200_API int mllmb200_w4a32_quant_activations(const float* x_dev, int M, int K, int ldx,
                                                   void* out_dev, void* stream);
 
+/* Forward that allocates nothing.  (No counterpart in the reference project: its linear op
+ * allocates a workspace tensor on every call, mllm/Backends/Arm/Ops/LinearOp.cpp:41-43.)
+ * For callers that cannot obtain device memory at call time - a host that owns all device memory
+ * through its own pool, a fixed-budget serving loop, a step that must not trigger cudaMalloc's
+ * device synchronization.  The activation workspace lives in a 1 MiB array inside the library's
+ * device image (held by every GPU that loads the library until exit); a call needing more
+ * (see mllmb200_w4a32_workspace_size) returns MLLMB200_TOO_LARGE.  All calls on a device share that
+ * array: calls that overlap on the GPU race, so keep them on one stream or order them.  The first
+ * call on each device resolves the array's address (cudaGetSymbolAddress) - make it before any
+ * stream capture.  Same arguments and results as mllmb200_w4a32_linear_forward, minus ws_dev. */
+MLLMB200_API int mllmb200_w4a32_linear_forward_static(const float* x_dev, const void* tiled_dev, float* y_dev,
+                                                      int M, int K, int N, int ldx, int ldy, void* stream);
+
+/* Capacity of that array in bytes. */
+MLLMB200_API int mllmb200_w4a32_static_scratch_bytes(size_t* bytes);
+
 /* Device-side status word (bounded waits that ran out, bad tile headers).  Synchronizes `stream`,
  * reads and clears the word.  0 = clean. */
 MLLMB200_API int mllmb200_check_device_status(void* stream);
