@@ -1,0 +1,139 @@
+#include "CUDALinearOp.hpp"
+
+#include <cuda_runtime.h>
+
+#include <vector>
+
+#include "CUDAW4A32Backend.hpp"
+#include "mllm/Utils/Common.hpp"
+#include "mllm/Utils/Log.hpp"
+#include "mllmb200.h"
+
+#define MLLMB200_CHECK_CUDA(expr)                                                                         \
+  do {                                                                                                    \
+    cudaError_t err__ = (expr);                                                                           \
+    if (err__ != cudaSuccess) {                                                                           \
+      MLLM_ERROR_EXIT(kCudaError, "CUDA error code {}: {}", int(err__), cudaGetErrorString(err__));       \
+    }                                                                                                     \
+  } while (0)
+
+#define MLLMB200_CHECK(expr)                                                                              \
+  do {                                                                                                    \
+    int st__ = (expr);                                                                                    \
+    if (st__ != MLLMB200_OK) {                                                                            \
+      MLLM_ERROR_EXIT(kCudaError, "mllmb200: {} (status {}, cuda error {})", mllmb200_status_str(st__),   \
+                      st__, mllmb200_last_cuda_error());                                                  \
+    }                                                                                                     \
+  } while (0)
+
+namespace mllm::cuda {
+
+bool isW4A32ImplType(LinearOpImplType t) {
+  switch (t) {
+    case LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp1x8_qsi4c32p4x8_1x4x32:
+    case LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp1x8_qsi4c32p8x8_1x8x32:
+    case LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp4x8_qsi4c32p4x8_8x4x32:
+    case LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp4x8_qsi4c32p4x8_16x4x32:
+    case LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp4x8_qsi4c32p8x8_4x8x32:
+    case LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp1x4_qsi4c32p4x4_1x4: return true;
+    default: return false;
+  }
+}
+
+CUDAW4A32LinearOp::CUDAW4A32LinearOp(const LinearOpCargo& cargo) : LinearOp(cargo) {}
+
+CUDAW4A32LinearOp::~CUDAW4A32LinearOp() { releaseDevice(); }
+
+void CUDAW4A32LinearOp::releaseDevice() {
+  if (tiled_dev_) cudaFree(tiled_dev_);
+  if (workspace_dev_) cudaFree(workspace_dev_);
+  tiled_dev_ = workspace_dev_ = nullptr;
+  workspace_bytes_ = 0;
+}
+
+void CUDAW4A32LinearOp::load(const std::shared_ptr<ParameterLoader>& ploader) {
+  LinearOp::load(ploader);  // weight_ / bias_ by name (mllm/Core/AOps/LinearOp.cpp:60-63)
+  if (!isW4A32ImplType(cargo_.impl_type_)) {
+    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: impl type {} is not a W4A32 type; this backend implements only those",
+                    name(), int(cargo_.impl_type_));
+  }
+  releaseDevice();
+  k_ = cargo_.in_channels;
+  n_ = cargo_.out_channels;
+
+  std::vector<unsigned char> owned;  // holds the blob when it is produced here
+  const void* blob = nullptr;
+  size_t blob_bytes = 0;
+  if (weight_.dtype() == kInt8) {
+    // the quantization pass's output: an opaque 1-D int8 tensor (KaiQuantizationPass.cpp:167-184 convention)
+    blob = weight_.ptr<unsigned char>();
+    blob_bytes = weight_.numel();
+  } else if (weight_.dtype() == kFp32) {
+    // unquantized checkpoint: quantize at load time with the same routine the pass uses
+    auto shape = weight_.shape();
+    MLLM_RT_ASSERT_EQ(shape.size(), 2);
+    MLLM_RT_ASSERT_EQ(shape[0], n_);
+    MLLM_RT_ASSERT_EQ(shape[1], k_);
+    const bool has_bias = cargo_.bias && bias_.dtype() == kFp32 && (int)bias_.numel() == n_;
+    MLLMB200_CHECK(mllmb200_w4a32_prepack_size(n_, k_, has_bias, &blob_bytes));
+    owned.resize(blob_bytes);
+    MLLMB200_CHECK(mllmb200_w4a32_quant_prepack(weight_.ptr<float>(), has_bias ? bias_.ptr<float>() : nullptr, n_, k_,
+                                                MLLMB200_SCALE_BF16_TRUNC, owned.data()));
+    blob = owned.data();
+  } else {
+    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: weight dtype must be int8 (pre-packed) or fp32", name());
+  }
+
+  int bn = 0, bk = 0, scale_mode = 0, has_bias = 0;
+  MLLMB200_CHECK(mllmb200_w4a32_blob_info(blob, blob_bytes, &bn, &bk, &scale_mode, &has_bias));
+  if (bn != n_ || bk != k_) {
+    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: blob is {}x{} but the layer is {}x{}", name(), bn, bk, n_, k_);
+  }
+
+  auto stream = static_cast<cudaStream_t>(currentW4A32Stream());
+  void* blob_dev = nullptr;
+  size_t tiled_bytes = 0;
+  MLLMB200_CHECK(mllmb200_w4a32_tiled_size(n_, k_, &tiled_bytes));
+  MLLMB200_CHECK_CUDA(cudaMalloc(&blob_dev, blob_bytes));
+  MLLMB200_CHECK_CUDA(cudaMalloc(&tiled_dev_, tiled_bytes));
+  MLLMB200_CHECK_CUDA(cudaMemcpyAsync(blob_dev, blob, blob_bytes, cudaMemcpyHostToDevice, stream));
+  MLLMB200_CHECK(mllmb200_w4a32_repack_device(blob_dev, n_, k_, scale_mode, has_bias, 0, n_, tiled_dev_, stream));
+  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` and blob_dev go away below
+  MLLMB200_CHECK_CUDA(cudaFree(blob_dev));
+}
+
+void CUDAW4A32LinearOp::reshape(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) {
+  const auto& i = inputs[0];
+  auto o_shape = i.shape();
+  MLLM_RT_ASSERT_EQ(o_shape[o_shape.size() - 1], cargo_.in_channels);
+  o_shape[o_shape.size() - 1] = cargo_.out_channels;
+  // W4A32: fp32 out whatever the tile (ArmLinearOp::reshape, LinearOp.cpp:252-259)
+  outputs.emplace_back(Tensor::empty(o_shape, kFp32, i.device()));
+}
+
+void CUDAW4A32LinearOp::forward(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) {
+  const auto& x = inputs[0];
+  auto& y = outputs[0];
+  if (!tiled_dev_) { MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: forward before load", name()); }
+  if (x.dtype() != kFp32 || x.device() != kCUDA) {
+    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: input must be fp32 on the CUDA device", name());
+  }
+  // every leading dimension is a row of the matrix product (the Arm kai path takes shape[-2] only,
+  // LinearOp.cpp:34, which silently drops batches; here a [B,S,K] input is B*S rows)
+  const int m = (int)(x.numel() / (size_t)k_);
+  size_t need = 0;
+  MLLMB200_CHECK(mllmb200_w4a32_workspace_size(m, k_, &need));
+  if (need > workspace_bytes_) {
+    // grow once and keep: the reference allocates a workspace tensor on every call (LinearOp.cpp:41-43)
+    if (workspace_dev_) {
+      MLLMB200_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(currentW4A32Stream())));
+      MLLMB200_CHECK_CUDA(cudaFree(workspace_dev_));
+    }
+    MLLMB200_CHECK_CUDA(cudaMalloc(&workspace_dev_, need));
+    workspace_bytes_ = need;
+  }
+  MLLMB200_CHECK(mllmb200_w4a32_linear_forward(x.ptr<float>(), tiled_dev_, y.ptr<float>(), workspace_dev_, m, k_, n_, k_,
+                                               n_, currentW4A32Stream()));
+}
+
+}  // namespace mllm::cuda

@@ -1,0 +1,46 @@
+// The W4A32 quantized linear as an mllm op: drop-in for ArmLinearOp on the Kai W4A32 impl types
+// (reference project: mllm/Backends/Arm/Ops/LinearOp.hpp:15-29, LinearOp.cpp:21-264).
+// All device work goes through the C ABI in include/mllmb200.h.
+#pragma once
+
+#include <cstddef>
+#include <memory>
+
+#include "mllm/Core/AOps/LinearOp.hpp"
+
+namespace mllm::cuda {
+
+class CUDAW4A32LinearOp final : public LinearOp {
+ public:
+  explicit CUDAW4A32LinearOp(const LinearOpCargo& cargo);
+  ~CUDAW4A32LinearOp();
+
+  // Binds "<name>.weight" (the 1-D int8 pre-pack blob written by the quantization pass, or an
+  // fp32 [N,K] tensor that is then quantized on the fly) and uploads + repacks it once.
+  void load(const std::shared_ptr<ParameterLoader>& ploader) override;
+
+  void reshape(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) override;
+
+  void forward(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) override;
+
+ private:
+  void releaseDevice();
+
+  void* tiled_dev_ = nullptr;      // weights in the tile layout
+  void* workspace_dev_ = nullptr;  // quantized activations, grown on demand, reused across calls
+  size_t workspace_bytes_ = 0;
+  int n_ = 0, k_ = 0;
+};
+
+class CUDALinearOpFactory : public TypedOpFactory<OpType::kLinear, LinearOpCargo> {
+ public:
+  std::shared_ptr<BaseOp> createOpImpl(const LinearOpCargo& cargo) override {
+    return std::make_shared<CUDAW4A32LinearOp>(cargo);
+  }
+};
+
+// True for the impl types this op implements (the six f32 W4 Kai tiles; the tile choice is an
+// Arm micro-kernel detail and is ignored here).
+bool isW4A32ImplType(LinearOpImplType t);
+
+}  // namespace mllm::cuda

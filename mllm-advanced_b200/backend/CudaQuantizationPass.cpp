@@ -1,0 +1,95 @@
+#include "CudaQuantizationPass.hpp"
+
+#include <string>
+
+#include "mllm/Core/AOps/LinearOp.hpp"
+#include "mllm/IR/Builtin/Op.hpp"
+#include "mllm/IR/Graph/Op.hpp"
+#include "mllm/IR/Linalg/Op.hpp"
+#include "mllm/Utils/Common.hpp"
+#include "mllm/Utils/Log.hpp"
+#include "mllmb200.h"
+
+namespace mllm::cuda {
+
+namespace {
+constexpr const char* kFamily = "KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk";
+
+// "family:tile" -> family
+std::string implFamily(const std::string& impl) {
+  const auto pos = impl.find(':');
+  return pos == std::string::npos ? impl : impl.substr(0, pos);
+}
+}  // namespace
+
+bool CudaQuantizationPass::quantizeLinear(const ir::op_ptr_t& op) {
+  auto* linear = (LinearOp*)(op->cast_<ir::linalg::LinearOp>()->getAOp());
+  if (implFamily(cfg_.opImplType(linear->name())) != kFamily) return false;
+
+  const Tensor weight = linear->weight();
+  const Tensor bias = linear->bias();
+  const int n = linear->cargo().out_channels, k = linear->cargo().in_channels;
+  const bool has_bias = linear->cargo().bias;
+  if (weight.dtype() != kFp32 || (has_bias && bias.dtype() != kFp32)) {
+    MLLM_WARN("CudaQuantizationPass: {} needs an fp32 weight (and bias); left unquantized", linear->name());
+    return false;
+  }
+  const auto shape = weight.shape();
+  if (shape.size() != 2 || shape[0] != n || shape[1] != k) {
+    MLLM_WARN("CudaQuantizationPass: {} weight must be [out_channels, in_channels]; left unquantized", linear->name());
+    return false;
+  }
+
+  size_t bytes = 0;
+  int st = mllmb200_w4a32_prepack_size(n, k, has_bias ? 1 : 0, &bytes);
+  if (st != MLLMB200_OK) {
+    MLLM_WARN("CudaQuantizationPass: {}: {}", linear->name(), mllmb200_status_str(st));
+    return false;
+  }
+  // a flat int8 buffer stands for the packed weight; it cannot be read as an ordinary tensor
+  Tensor packed = Tensor::empty({(int32_t)bytes}, kInt8, kCPU).alloc();
+  st = mllmb200_w4a32_quant_prepack(weight.ptr<float>(), has_bias ? bias.ptr<float>() : nullptr, n, k,
+                                    MLLMB200_SCALE_BF16_TRUNC, packed.ptr<uint8_t>());
+  if (st != MLLMB200_OK) {
+    MLLM_WARN("CudaQuantizationPass: {}: {}", linear->name(), mllmb200_status_str(st));
+    return false;
+  }
+  packed.setName(weight.name());
+  linear->weight() = packed;
+  // the bias now lives inside the blob; a 1-byte tensor keeps its slot in the parameter file
+  linear->bias() = Tensor::empty({1}, kInt8, kCPU).alloc();
+  ++quantized_;
+  return true;
+}
+
+void CudaQuantizationPass::visitGraph(const ir::op_ptr_t& subgraph) {
+  auto region = subgraph->cast_<ir::graph::SubGraphOp>()->getTopRegion();
+  for (auto& node : region->ops()) {
+    if (node->isa_<ir::graph::CallGraphOp>()) {
+      auto callee = getCtx()->lookupSymbolTable(node->cast_<ir::graph::CallGraphOp>()->getSymbolAttr()->str());
+      visitGraph(callee->cast_<ir::graph::SubGraphOp>());
+    } else if (node->isa_<ir::linalg::LinearOp>()) {
+      if (!quantizeLinear(node)) {
+        MLLM_WARN("CudaQuantizationPass: linear {} not quantized (no matching impl type in the config)",
+                  node->cast_<ir::linalg::LinalgIROp>()->getAOp()->name());
+      }
+    }
+  }
+}
+
+uint8_t CudaQuantizationPass::run(const ir::node_ptr_t& op) {
+  MLLM_RT_ASSERT(op->isa_<ir::ModuleOp>());
+  // entry point: the single CallGraphOp of the module
+  ir::graph::CallGraphOp::self_ptr_t entry = nullptr;
+  for (auto& node : op->cast_<ir::ModuleOp>()->getTopRegion()->ops()) {
+    if (node->isa_<ir::graph::CallGraphOp>()) {
+      MLLM_RT_ASSERT_EQ(entry, nullptr);
+      entry = node->cast_<ir::graph::CallGraphOp>();
+    }
+  }
+  if (entry == nullptr) return ir::PASS_RET_FAILURE;
+  visitGraph(getCtx()->lookupSymbolTable(entry->getSymbolAttr()->str())->cast_<ir::graph::SubGraphOp>());
+  return ir::PASS_RET_SUCCESS;
+}
+
+}  // namespace mllm::cuda

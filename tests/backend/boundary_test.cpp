@@ -1,0 +1,201 @@
+// Boundary test: the B200 W4A32 linear driven through the reference's OWN plugin API
+// (MllmEngineCtx / BackendBase / nn::Module / nn::Linear / ParameterLoader / ir::PassManager),
+// compiled against the reference's real classes.  Follows the shape of the reference's
+// op-through-plugin test (tests/Arm/SingleConv3DTest.cpp:88-120): build a one-layer module, hand it
+// a ParameterLoader, call it, compare with a scalar reference - here the CPU oracle.
+//
+//   1. CudaQuantizationPass on a flat IR module (as tools/Quantizer/FlatModuleBuilder.cpp builds it):
+//      the int8 blob's nibble and scale sections must equal the oracle's quantizer bit for bit.
+//   2. model.load(blob) -> model.to(kCUDA) -> y = model(x): outputs within 1e-3 * rms of the oracle,
+//      for M = 1 (GEMV), a [2,3,K] batch (M = 6) and M = 64 (tcgen05 path).
+// Exit code 0 = all passed.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "CUDALinearOp.hpp"
+#include "CUDAW4A32Backend.hpp"
+#include "CudaQuantizationPass.hpp"
+#include "HostShimBackend.hpp"
+#include "mllm/Engine/Context.hpp"
+#include "mllm/Engine/ParameterReader.hpp"
+#include "mllm/IR/Builtin/Op.hpp"
+#include "mllm/IR/Graph/Op.hpp"
+#include "mllm/IR/Linalg/Op.hpp"
+#include "mllm/IR/Passes/PassManager.hpp"
+#include "mllm/Nn/HierarchyBase.hpp"
+#include "mllm/Nn/Layers/Linear.hpp"
+#include "mllm/Nn/Module.hpp"
+#include "mllmb200.h"
+
+extern "C" {  // oracle/w4a32_oracle.c
+void oracle_quant_nxk_qs4c32_f32(size_t n, size_t k, size_t bl, const float* rhs, uint8_t* q, uint16_t* s, int mode);
+void oracle_linear_w4a32(size_t m, size_t n, size_t k, const float* x, const uint8_t* q, const uint16_t* s, int mode,
+                         const float* bias, float* y, void* workspace);
+}
+
+using namespace mllm;
+
+namespace {
+
+constexpr auto kImpl = LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp4x8_qsi4c32p4x8_8x4x32;
+
+class SingleLinear final : public nn::Module {
+ public:
+  nn::Linear fc_;
+  SingleLinear() = default;
+  SingleLinear(const std::string& name, int k, int n, bool bias) {
+    selfAssignName(name);
+    fc_ = reg<nn::Linear>("fc", k, n, bias, false, kImpl);
+  }
+  std::vector<Tensor> forward(const std::vector<Tensor>& inputs) override { return {fc_(inputs[0])}; }
+};
+
+uint32_t g_rng = 12345u;
+float frand() {  // uniform in [-1, 1)
+  g_rng = g_rng * 1664525u + 1013904223u;
+  return (float)((g_rng >> 8) & 0xFFFFFF) / 8388608.0f - 1.0f;
+}
+
+// Flat IR module holding one linalg LinearOp, the way the quantizer tool builds it.
+std::shared_ptr<ir::IRContext> flatModule(const std::shared_ptr<BaseOp>& op) {
+  auto ir_ctx = std::make_shared<ir::IRContext>();
+  ir_ctx->createAndSetModuleOp<ir::ModuleOp>(ir_ctx->create<ir::SymbolAttr>("main"));
+  ir_ctx->create<ir::graph::CallGraphOp>(ir_ctx->create<ir::SymbolAttr>("flat"));
+  std::shared_ptr<ir::graph::SubGraphOp> graph = nullptr;
+  {
+    auto guard = ir::IRWriterGuard(ir_ctx, ir_ctx->topLevelOp()->cast_<ir::ModuleOp>()->getTopRegion());
+    graph = ir_ctx->create<ir::graph::SubGraphOp>(ir_ctx->create<ir::SymbolAttr>("flat"),
+                                                  std::make_shared<HierarchyBase>(HierarchyTypes::kModule));
+  }
+  graph->setDevice(kCPU);
+  {
+    auto guard = ir::IRWriterGuard(ir_ctx, graph->getTopRegion());
+    ir_ctx->create<ir::linalg::LinearOp>(op, std::vector<ir::tensor::TensorValue::self_ptr_t>{},
+                                         std::vector<ir::tensor::TensorValue::self_ptr_t>{});
+  }
+  return ir_ctx;
+}
+
+int g_failures = 0;
+bool g_host_only = false;  // --host-only: quantization pass only (no CUDA device needed)
+void check(bool ok, const char* what) {
+  std::printf("[%s] %s\n", ok ? " ok " : "FAIL", what);
+  if (!ok) ++g_failures;
+}
+
+void runCase(const std::string& model, int k, int n, bool with_bias, const std::vector<std::vector<int32_t>>& x_shapes) {
+  const std::string layer = model + ".fc";
+  auto& ctx = MllmEngineCtx::instance();
+  char label[256];
+
+  // ---- fp32 parameters
+  Tensor w = Tensor::empty({n, k}, kFp32, kCPU).alloc();
+  Tensor b = Tensor::empty({n}, kFp32, kCPU).alloc();
+  for (int i = 0; i < n * k; ++i) w.ptr<float>()[i] = frand() * 0.05f;
+  for (int i = 0; i < n; ++i) b.ptr<float>()[i] = frand() * 0.1f;
+  w.setName(layer + ".weight");
+  b.setName(layer + ".bias");
+
+  // ---- 1. the quantization pass, through the reference's PassManager
+  auto host_op = ctx.getBackend(kCPU)->createOp(
+      OpType::kLinear, LinearOpCargo{.in_channels = k, .out_channels = n, .bias = with_bias, .transpose = false});
+  host_op->setName(layer);
+  auto* host_linear = (LinearOp*)host_op.get();
+  host_linear->weight() = w;
+  if (with_bias) host_linear->bias() = b;
+  MllmModelCfg cfg;
+  cfg.rawJson()["Ops"][layer] = {{"type", "Linear"},
+                                 {"implType", "KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk:qai8dxp4x8_qsi4c32p4x8_8x4x32"}};
+  auto ir_ctx = flatModule(host_op);
+  auto pass = cuda::createCudaQuantizationPass(cfg);
+  ir::PassManager pm(ir_ctx);
+  pm.reg(pass);
+  const bool pm_ok = pm.run();
+  std::snprintf(label, sizeof(label), "K=%d N=%d bias=%d: pass ran and quantized one linear", k, n, (int)with_bias);
+  check(pm_ok && pass->quantizedCount() == 1, label);
+  Tensor blob = host_linear->weight();
+  check(blob.dtype() == kInt8 && blob.shape().size() == 1 && blob.name() == layer + ".weight",
+        "  weight replaced by a 1-D int8 tensor of the same name");
+  check(host_linear->bias().dtype() == kInt8 && host_linear->bias().numel() == 1, "  bias replaced by the 1-byte placeholder");
+
+  // blob sections vs the oracle's quantizer, bit for bit
+  const size_t ns = (size_t)(k + 1) / 2, nb = (size_t)(k + 31) / 32;
+  std::vector<uint8_t> q_ref(n * ns);
+  std::vector<uint16_t> s_ref(n * nb);
+  oracle_quant_nxk_qs4c32_f32(n, k, 32, w.ptr<float>(), q_ref.data(), s_ref.data(), 0);
+  size_t off_q = 0, off_s = 0, off_b = 0;
+  mllmb200_w4a32_blob_offsets(n, k, with_bias, &off_q, &off_s, &off_b);
+  const uint8_t* blob_bytes = blob.ptr<uint8_t>();
+  check(std::memcmp(blob_bytes + off_q, q_ref.data(), q_ref.size()) == 0, "  nibbles bit-identical to the oracle");
+  check(std::memcmp(blob_bytes + off_s, s_ref.data(), s_ref.size() * 2) == 0, "  scales bit-identical to the oracle");
+  if (with_bias) check(std::memcmp(blob_bytes + off_b, b.ptr<float>(), n * 4) == 0, "  bias carried inside the blob");
+
+  if (g_host_only) return;
+  // ---- 2. one-layer module: load on the host, move to the GPU, run
+  auto net = SingleLinear(model, k, n, with_bias);
+  auto ploader = std::make_shared<ParameterLoader>();
+  blob.setMemType(kParams);
+  Tensor bias_placeholder = host_linear->bias();
+  ploader->params().insert({layer + ".weight", blob.impl()});
+  if (with_bias) ploader->params().insert({layer + ".bias", bias_placeholder.impl()});
+  net.load(ploader);
+  net.to(kCUDA);
+  auto stream = static_cast<cudaStream_t>(cuda::currentW4A32Stream());
+
+  for (const auto& shape : x_shapes) {
+    size_t numel = 1;
+    for (auto d : shape) numel *= (size_t)d;
+    const int m = (int)(numel / (size_t)k);
+    std::vector<float> x_host(numel), y_host((size_t)m * n), y_ref((size_t)m * n);
+    for (auto& v : x_host) v = frand() * 2.0f;
+    Tensor x = Tensor::empty(shape, kFp32, kCUDA).alloc();
+    cudaMemcpyAsync(x.ptr<float>(), x_host.data(), numel * 4, cudaMemcpyHostToDevice, stream);
+    Tensor y = net(x)[0];
+    cudaMemcpyAsync(y_host.data(), y.ptr<float>(), y_host.size() * 4, cudaMemcpyDeviceToHost, stream);
+    const cudaError_t e = cudaStreamSynchronize(stream);
+    const int dev_status = mllmb200_check_device_status(stream);
+    std::vector<uint8_t> ws((size_t)m * (k + 8));
+    oracle_linear_w4a32(m, n, k, x_host.data(), q_ref.data(), s_ref.data(), 0, with_bias ? b.ptr<float>() : nullptr,
+                        y_ref.data(), ws.data());
+    double sq = 0, err = 0;
+    for (size_t i = 0; i < y_ref.size(); ++i) {
+      sq += (double)y_ref[i] * y_ref[i];
+      err = std::fmax(err, std::fabs((double)y_host[i] - y_ref[i]));
+    }
+    const double rms = std::sqrt(sq / y_ref.size());
+    auto y_shape = y.shape();
+    bool shape_ok = y_shape.size() == shape.size() && y_shape.back() == n && y.dtype() == kFp32 && y.device() == kCUDA;
+    for (size_t d = 0; d + 1 < shape.size(); ++d) shape_ok = shape_ok && y_shape[d] == shape[d];
+    std::snprintf(label, sizeof(label), "  forward M=%d: max|diff| %.3e <= 1e-3 * rms %.3e, shape/dtype/device ok", m, err, rms);
+    check(e == cudaSuccess && dev_status == 0 && shape_ok && err <= 1e-3 * rms, label);
+  }
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  g_host_only = argc > 1 && std::strcmp(argv[1], "--host-only") == 0;
+  std::setvbuf(stdout, nullptr, _IOLBF, 0);
+  auto& ctx = MllmEngineCtx::instance();
+  ctx.registerBackend(std::make_shared<shim::HostShimBackend>());
+  ctx.mem()->initBuddyCtx(kCPU);
+  ctx.mem()->initOC(kCPU);
+  if (!g_host_only) {
+    ctx.registerBackend(cuda::createCUDAW4A32Backend());
+    ctx.mem()->initBuddyCtx(kCUDA);
+    ctx.mem()->initOC(kCUDA);
+  }
+
+  runCase("model", 1536, 256, true, {{1, 1, 1536}, {2, 3, 1536}, {1, 64, 1536}});
+  runCase("vit", 1176, 160, false, {{1, 1176}, {40, 1176}});  // K not a multiple of 32 (Qwen2VL patch embed width)
+
+  std::printf("%s (%d failures)\n", g_failures == 0 ? "BOUNDARY TEST PASSED" : "BOUNDARY TEST FAILED", g_failures);
+  std::fflush(stdout);
+  // leave without running the engine's static destructors after the CUDA context may be gone
+  std::_Exit(g_failures == 0 ? 0 : 1);
+}

@@ -1,0 +1,31 @@
+"""Runs the C++ boundary test: the W4A32 op behind the reference's own plugin API
+(MllmEngineCtx, BackendBase, nn::Module / nn::Linear, ParameterLoader, ir::PassManager), built by
+mllm-advanced_b200/backend/Makefile against the reference's real classes.  The binary is built where
+the reference tree exists and travels as a prebuilt file; its source is tests/backend/boundary_test.cpp."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BIN = os.path.join(ROOT, "oracle", "_ref", "backend_boundary_test")
+
+
+@pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/backend_boundary_test not built (needs the reference tree)")
+def test_quantization_pass_through_reference_pass_manager_host_only():
+    """CudaQuantizationPass run by the reference's ir::PassManager on a flat IR module: the blob's
+    nibble and scale sections equal the oracle's quantizer bit for bit.  No GPU involved."""
+    r = subprocess.run([BIN, "--host-only"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "BOUNDARY TEST PASSED" in r.stdout and r.stdout.count("[ ok ]") >= 10
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/backend_boundary_test not built (needs the reference tree)")
+def test_linear_op_through_reference_plugin_api():
+    r = subprocess.run([BIN], capture_output=True, text=True, timeout=300)
+    print(r.stdout[-4000:])
+    print(r.stderr[-2000:])
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "BOUNDARY TEST PASSED" in r.stdout
+    assert "FAIL" not in r.stdout.replace("0 failures", "")
