@@ -515,6 +515,7 @@ def run_gpu(args):
 def run_tp(args, torch, mb, dist, rank, world, gen):
     """BASELINE config 4: W [28672, 8192] column-sharded over the ranks, x replicated, NCCL all-gather of y.
     M=1 (GEMV) and a reduced M for the GEMM; device time, max over ranks."""
+    from mllm_b200 import tp
     n_total, k = 28672, 8192
     if n_total % (world * 32) != 0:
         return None
@@ -525,7 +526,6 @@ def run_tp(args, torch, mb, dist, rank, world, gen):
     for m in (1, 256):
         x = torch.randn((m, k), device="cuda", generator=g)
         y_loc = torch.empty((m, n_loc), device="cuda")
-        y_all = torch.empty((world, m, n_loc), device="cuda")
         ws = torch.empty(mb.workspace_size(m, k), dtype=torch.uint8, device="cuda")
 
         def fwd():
@@ -533,7 +533,7 @@ def run_tp(args, torch, mb, dist, rank, world, gen):
 
         def fwd_gather():
             mb.linear_forward(x, w, out=y_loc, workspace=ws)
-            dist.all_gather_into_tensor(y_all, y_loc)
+            tp.gather_columns(y_loc, n_total, n_loc)  # all-gather + [world, M, N/world] -> [M, N]
         res = {}
         for name, fn in (("compute_ms", fwd), ("compute_allgather_ms", fwd_gather)):
             for _ in range(3):
