@@ -282,6 +282,18 @@ def run_gpu(args):
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
 
+    if args.prefill_only:
+        lw = [make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS]
+        ws = torch.empty(mb.workspace_size(PREFILL_M, 8960), dtype=torch.uint8, device="cuda")
+        xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
+        for _ in range(max(1, args.steps)):
+            for w in lw:
+                mb.linear_forward(xp[w.k], w, workspace=ws)
+        torch.cuda.synchronize()
+        mb.check_device_status()
+        print(json.dumps({"prefill_only": True, "M": PREFILL_M, "passes": max(1, args.steps)}))
+        return
+
     # ---- weights: 28 layers x 7 linears, each its own tiled buffer
     layers = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(LAYERS)]
     xs = {k: torch.randn((1, k), device="cuda", generator=gen) for k in (1536, 8960)}
@@ -506,7 +518,7 @@ def run_gpu(args):
         if rank == 0 and tp is not None:
             line["tp"] = tp
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -561,6 +573,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch on the stream instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="run one decoder layer's seven linears at M=512 once and exit (small target for ncu)")
     ap.add_argument("--fast-prefill", action="store_true", help="time the prefill linears on 2 layers instead of 28")
     args = ap.parse_args()
     if args.impl == "reference":

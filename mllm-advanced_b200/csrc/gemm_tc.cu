@@ -24,8 +24,11 @@
 //   warps 8-11  dequant: thread j expands weight row j of the tile, 4 K-groups per stage
 //   warp 12     producer: bulk copies (cp.async.bulk) of raw weight cells and activation blocks
 //   warp 13     MMA issuer (one elected lane) and tensor-memory allocation
-// Shared memory: 4 stages of {raw cells 9 KB, B operand NT*128 B, A operand 16 KB}; tensor
-// memory: 4 accumulator stages of NT columns.  Every mbarrier wait is bounded (device_common.cuh).
+// Shared memory: 4 stages of {raw cells 9 KB, B operand NT*128 B, A operand 16 KB}.  Tensor memory:
+// all 512 columns, as 512/(4*NT) batches of 4 accumulators (one per K-group of a stage); a batch
+// is handed to the epilogue with one commit and handed back with one arrive per warp, so the
+// MMA -> epilogue -> MMA round trip (thousands of cycles) is paid once per 4 K-groups and several
+// batches are in flight.  NT is 64 or 32.  Every mbarrier wait is bounded (device_common.cuh).
 #include "device_common.cuh"
 
 namespace mllmb200 {
@@ -34,7 +37,7 @@ constexpr int kTcThreads = 448;
 constexpr int kTcStages = 4;        // shared-memory stages
 constexpr int kTcGroupsPerStage = 4;  // K-groups (of 32) per stage
 constexpr int kTcTileRows = 128;    // weight rows per CTA (= 4 panels)
-constexpr int kTcAccStages = 4;     // tensor-memory accumulator stages
+constexpr int kTcTmemCols = 512;    // all of tensor memory: accumulator batches of 4 K-groups x NT columns
 
 // ------------------------------------------------------------------ tcgen05 wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -109,9 +112,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [kTcStages]
   uint64_t* stage_empty = raw_full + kTcStages;            // [kTcStages]
   uint64_t* a_full = stage_empty + kTcStages;              // [kTcStages]
-  uint64_t* tmem_full = a_full + kTcStages;                // [kTcAccStages]
-  uint64_t* tmem_empty = tmem_full + kTcAccStages;         // [kTcAccStages]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + kTcAccStages);
+  // accumulators are handed over in batches of one shared-memory stage (4 K-groups): one barrier
+  // round trip per 4 MMAs instead of per MMA, and kSlots batches in flight
+  constexpr int kSlots = kTcTmemCols / (kTcGroupsPerStage * NT);
+  uint64_t* acc_full = a_full + kTcStages;                 // [kSlots]
+  uint64_t* acc_empty = acc_full + kSlots;                 // [kSlots]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + kSlots);
   uint8_t* stages = smem + S::kBarBytes;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -127,14 +133,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
       mbar_init(&stage_empty[s], 1);
       mbar_init(&a_full[s], 128);
     }
-    for (int t = 0; t < kTcAccStages; ++t) {
-      mbar_init(&tmem_full[t], 1);
-      mbar_init(&tmem_empty[t], 8);  // one arrival per epilogue warp
+    for (int t = 0; t < kSlots; ++t) {
+      mbar_init(&acc_full[t], 1);
+      mbar_init(&acc_empty[t], 8);  // one arrival per epilogue warp
     }
     mbar_fence_init();
   }
   if (warp == 13) {
-    tmem_alloc(tmem_base_slot, (uint32_t)(kTcAccStages * NT));
+    tmem_alloc(tmem_base_slot, (uint32_t)kTcTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -168,27 +174,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
     if (lane == 0) {
       // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = NT, M = 128
       const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
-      int cnt = 0;
       bool ok = true;
       for (int it = 0; it < k_tiles && ok; ++it) {
         const int s = it % kTcStages;
         const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
-        ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&a_full[s], ph);
+        const int slot = it % kSlots;
+        ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&a_full[s], ph) &&
+             mbar_wait_bounded(&acc_empty[slot], ((uint32_t)(it / kSlots) & 1u) ^ 1u);
         if (!ok) break;
         tc_fence_after();
         const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
         uint8_t* st = stages + (size_t)s * S::kStageBytes;
         const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(st + S::kRawBytes + S::kBBytes);
-        for (int g = 0; g < ng; ++g, ++cnt) {
-          const int t = cnt % kTcAccStages;
-          ok = mbar_wait_bounded(&tmem_empty[t], ((uint32_t)(cnt / kTcAccStages) & 1u) ^ 1u);
-          if (!ok) break;
-          tc_fence_after();
-          tc_mma_i8(tmem_base + (uint32_t)(t * NT), make_kmajor_desc(a_addr + g * kTcTileRows * 32, 128, 256),
+        for (int g = 0; g < ng; ++g)
+          tc_mma_i8(tmem_base + (uint32_t)((slot * kTcGroupsPerStage + g) * NT),
+                    make_kmajor_desc(a_addr + g * kTcTileRows * 32, 128, 256),
                     make_kmajor_desc(b_addr + g * NT * 32, 128, 256), idesc);
-          tc_commit(&tmem_full[t]);
-        }
-        tc_commit(&stage_empty[s]);  // raw cells, A and B of this stage may be overwritten once these MMAs are done
+        tc_commit(&acc_full[slot]);    // the batch's accumulators are complete
+        tc_commit(&stage_empty[s]);    // raw cells, A and B of this stage may be overwritten
       }
     }
   } else if (warp >= 8) {
@@ -240,31 +243,56 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
 #pragma unroll
     for (int c = 0; c < CW; ++c) acc[c] = 0.0f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * CW);
+    // Group scales come from global memory (L2: the producer just fetched the same cells).  They are
+    // requested kScaleAhead groups early so that their latency never sits in front of the math.
+    constexpr int kScaleAhead = 8;
+    uint32_t sraw[kScaleAhead];
+#pragma unroll
+    for (int i = 0; i < kScaleAhead; ++i)
+      sraw[i] = (have_panel && i < p.num_groups) ? *reinterpret_cast<const uint16_t*>(scale_ptr + (size_t)i * kCellBytes) : 0u;
     bool ok = true;
-    for (int cnt = 0; cnt < p.num_groups && ok; ++cnt) {
-      const int t = cnt % kTcAccStages;
-      // group scale / 16 (the A operand carries 16 * weight); exact: a power-of-two factor
-      float s16 = 0.0f;
-      if (have_panel)
-        s16 = decode_scale(*reinterpret_cast<const uint16_t*>(scale_ptr + (size_t)cnt * kCellBytes), scale_mode) * 0.0625f;
-      ok = mbar_wait_bounded(&tmem_full[t], (uint32_t)(cnt / kTcAccStages) & 1u);
-      if (!ok) break;
-      tc_fence_after();
+    static_assert(kScaleAhead == 2 * kTcGroupsPerStage, "the scale ring covers two batches");
+    for (int it2 = 0; it2 < k_tiles && ok; it2 += 2) {
 #pragma unroll
-      for (int c0 = 0; c0 < CW; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(lane_addr + (uint32_t)(t * NT + c0), v);
-        tmem_ld_wait();
-        if (c0 + 16 >= CW) {  // last read of this accumulator stage: hand it back to the MMA issuer
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[t]);
-        }
+      for (int h = 0; h < 2; ++h) {
+        const int it = it2 + h;
+        if (it >= k_tiles || !ok) break;
+        const int slot = it % kSlots;
+        ok = mbar_wait_bounded(&acc_full[slot], (uint32_t)(it / kSlots) & 1u);
+        if (!ok) break;
+        tc_fence_after();
+        const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          // exact int32 -> fp32 for |v| < 2^22: add 1.5 * 2^23 as an integer, subtract it as a float
-          const float f = __int_as_float((int)v[i] + 0x4B400000) - 12582912.0f;
-          acc[c0 + i] = fmaf(f, s16, acc[c0 + i]);
+        for (int g = 0; g < kTcGroupsPerStage; ++g) {
+          if (g >= ng) break;
+          const int u = h * kTcGroupsPerStage + g;
+          const int cnt = it * kTcGroupsPerStage + g;
+          // group scale / 16 (the A operand carries 16 * weight); exact: a power-of-two factor
+          const float s16 = decode_scale(sraw[u], scale_mode) * 0.0625f;
+          const int nxt = cnt + kScaleAhead;
+          sraw[u] = (have_panel && nxt < p.num_groups) ? *reinterpret_cast<const uint16_t*>(scale_ptr + (size_t)nxt * kCellBytes) : 0u;
+          const uint32_t col = lane_addr + (uint32_t)((slot * kTcGroupsPerStage + g) * NT);
+          // software pipeline over 16-column chunks: the next chunk's TMEM load is in flight during the math
+          uint32_t v[2][16];
+          tmem_ld16(col, v[0]);
+#pragma unroll
+          for (int c0 = 0; c0 < CW; c0 += 16) {
+            const int cur = (c0 >> 4) & 1;
+            tmem_ld_wait();
+            if (c0 + 16 < CW) {
+              tmem_ld16(col + (uint32_t)(c0 + 16), v[cur ^ 1]);
+            } else if (g == ng - 1) {  // the whole batch is in registers: hand its slot back to the MMA issuer
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[slot]);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              // exact int32 -> fp32 for |v| < 2^22: add 1.5 * 2^23 as an integer, subtract it as a float
+              const float f = __int_as_float((int)v[cur][i] + 0x4B400000) - 12582912.0f;
+              acc[c0 + i] = fmaf(f, s16, acc[c0 + i]);
+            }
+          }
         }
       }
     }
@@ -290,7 +318,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
   __syncthreads();
   if (warp == 13) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, (uint32_t)(kTcAccStages * NT));
+    tmem_dealloc(tmem_base, (uint32_t)kTcTmemCols);
   }
 }
 
@@ -311,8 +339,8 @@ static cudaError_t launch_tc_t(const TcParams& prm, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-// Rows of the activation block array are padded to a multiple of this (largest NT).
-int w4a32_gemm_tc_m_pad(int m) { return (m + 127) / 128 * 128; }
+// Rows of the activation block array are padded to a multiple of the largest NT.
+int w4a32_gemm_tc_m_pad(int m) { return (m + 63) / 64 * 64; }
 
 bool w4a32_gemm_tc_supported(int m, int k, int n) {
   // one CTA per SM holds 128 KB+ of shared memory and all tensor memory it allocates; any K, any N.
@@ -337,9 +365,23 @@ cudaError_t launch_w4a32_gemm_tc(const uint8_t* a_blocks, const float2* a_hdr, c
   const TiledHeader th = make_tiled_header(n, k, 0, 0);
   prm.zsum_off = th.zsum_off;
   prm.bias_off = th.bias_off;
-  if (m <= 32) return launch_tc_t<32>(prm, stream);
-  if (m <= 64) return launch_tc_t<64>(prm, stream);
-  return launch_tc_t<128>(prm, stream);
+  // Tile width along the activation rows: the wider of 64/32 that fills the 148 SMs best
+  // (CTAs run one per SM; a tile's cost is proportional to its width, so only the fill matters).
+  const int n_tiles = (prm.num_panels + 3) / 4;
+  int best_nt = 32;
+  double best_fill = -1.0;
+  for (int nt : {64, 32}) {
+    if (nt > 32 && m <= nt / 2) continue;  // would be mostly padding
+    const long long tiles = (long long)n_tiles * ((m + nt - 1) / nt);
+    const double waves = (double)((tiles + 147) / 148);
+    const double fill = (double)tiles / (waves * 148.0) * ((double)m / (double)(((m + nt - 1) / nt) * nt));
+    if (fill > best_fill + 1e-9) {
+      best_fill = fill;
+      best_nt = nt;
+    }
+  }
+  if (best_nt == 32) return launch_tc_t<32>(prm, stream);
+  return launch_tc_t<64>(prm, stream);
 }
 
 }  // namespace mllmb200
