@@ -18,12 +18,12 @@
 // Both operands use the same permutation of k inside a K-group (the order the nibble masks
 // produce), which leaves every dot product unchanged.
 //
-// Warp roles (448 threads, one CTA per SM):
-//   warps 0-7   epilogue: warp w reads TMEM lanes 32*(w%4).. (its quadrant) and columns
-//               (w/4)*NT/2 ..; accumulators stay in registers for the whole K loop
-//   warps 8-11  dequant: thread j expands weight row j of the tile, 4 K-groups per stage
-//   warp 12     producer: bulk copies (cp.async.bulk) of raw weight cells and activation blocks
-//   warp 13     MMA issuer (one elected lane) and tensor-memory allocation
+// Warp roles (704 threads, one CTA per SM):
+//   warps 0-15  epilogue: warp w reads TMEM lanes 32*(w%4).. (its quadrant) and columns
+//               (w/4)*NT/4 ..; accumulators stay in registers for the whole K loop
+//   warps 16-19 dequant: thread j expands weight row j of the tile, 4 K-groups per stage
+//   warp 20     producer: bulk copies (cp.async.bulk) of raw weight cells and activation blocks
+//   warp 21     MMA issuer (one elected lane) and tensor-memory allocation
 // Shared memory: 4 stages of {raw cells 9 KB, B operand NT*128 B, A operand 16 KB}.  Tensor memory:
 // all 512 columns, as 512/(4*NT) batches of 4 accumulators (one per K-group of a stage); a batch
 // is handed to the epilogue with one commit and handed back with one arrive per warp, so the
@@ -33,7 +33,8 @@
 
 namespace mllmb200 {
 
-constexpr int kTcThreads = 448;
+constexpr int kTcEpiWarps = 16;     // 4 per TMEM lane quadrant, each a quarter of the columns
+constexpr int kTcThreads = (kTcEpiWarps + 6) * 32;  // + 4 dequant warps + producer + MMA issuer
 constexpr int kTcStages = 4;        // shared-memory stages
 constexpr int kTcGroupsPerStage = 4;  // K-groups (of 32) per stage
 constexpr int kTcTileRows = 128;    // weight rows per CTA (= 4 panels)
@@ -75,6 +76,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(addr));
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(addr));
+}
+template <int CW>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[CW]) {
+  static_assert(CW == 8 || CW == 16, "column chunk");
+  if constexpr (CW == 8) tmem_ld8(addr, v);
+  else tmem_ld16(addr, v);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major, no-swizzle operand descriptor: core matrix = 8 rows x 16 bytes (128 contiguous bytes),
@@ -110,13 +122,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
   extern __shared__ __align__(128) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [kTcStages]
-  uint64_t* stage_empty = raw_full + kTcStages;            // [kTcStages]
-  uint64_t* a_full = stage_empty + kTcStages;              // [kTcStages]
+  uint64_t* mma_done = raw_full + kTcStages;               // [kTcStages] the MMAs of a stage completed
+  uint64_t* a_full = mma_done + kTcStages;                 // [kTcStages]
   // accumulators are handed over in batches of one shared-memory stage (4 K-groups): one barrier
   // round trip per 4 MMAs instead of per MMA, and kSlots batches in flight
   constexpr int kSlots = kTcTmemCols / (kTcGroupsPerStage * NT);
-  uint64_t* acc_full = a_full + kTcStages;                 // [kSlots]
-  uint64_t* acc_empty = acc_full + kSlots;                 // [kSlots]
+  uint64_t* acc_empty = a_full + kTcStages;                // [kSlots]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + kSlots);
   uint8_t* stages = smem + S::kBarBytes;
 
@@ -130,16 +141,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
   if (tid == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&stage_empty[s], 1);
+      mbar_init(&mma_done[s], 1);
       mbar_init(&a_full[s], 128);
     }
     for (int t = 0; t < kSlots; ++t) {
-      mbar_init(&acc_full[t], 1);
-      mbar_init(&acc_empty[t], 8);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[t], kTcEpiWarps);  // one arrival per epilogue warp
     }
     mbar_fence_init();
   }
-  if (warp == 13) {
+  if (warp == kTcEpiWarps + 5) {
     tmem_alloc(tmem_base_slot, (uint32_t)kTcTmemCols);
     tmem_relinquish();
   }
@@ -148,28 +158,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  if (warp == 12) {
+  if (warp == kTcEpiWarps + 4) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      for (int it = 0; it < k_tiles; ++it) {
-        const int s = it % kTcStages;
-        const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
-        if (!mbar_wait_bounded(&stage_empty[s], ph ^ 1u)) break;
-        const int g0 = it * kTcGroupsPerStage;
-        const int ng = min(kTcGroupsPerStage, p.num_groups - g0);
-        const int np = min(4, p.num_panels - panel0);
-        uint8_t* st = stages + (size_t)s * S::kStageBytes;
-        mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCellBytes + ng * NT * 32));
-        for (int q = 0; q < np; ++q)
-          bulk_g2s(st + q * kTcGroupsPerStage * kCellBytes,
-                   p.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + q) * p.num_groups + g0) * kCellBytes,
-                   (uint32_t)(ng * kCellBytes), &raw_full[s]);
-        for (int g = 0; g < ng; ++g)
-          bulk_g2s(st + S::kRawBytes + g * NT * 32,
-                   p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 256, (uint32_t)(NT * 32), &raw_full[s]);
+    // lanes 0-3 copy one panel's cells each, lanes 4-7 one K-group's activation block each: the eight
+    // copies of a stage are issued side by side (one thread issuing them all was the kernel's bottleneck)
+    const int np = min(4, p.num_panels - panel0);
+    for (int it = 0; it < k_tiles; ++it) {
+      const int s = it % kTcStages;
+      const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
+      // warp-uniform outcome: a timed-out lane must not leave the others at the __syncwarp below
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&mma_done[s], ph ^ 1u))) break;
+      const int g0 = it * kTcGroupsPerStage;
+      const int ng = min(kTcGroupsPerStage, p.num_groups - g0);
+      uint8_t* st = stages + (size_t)s * S::kStageBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCellBytes + ng * NT * 32));
+      __syncwarp();
+      if (lane < np) {
+        bulk_g2s(st + lane * kTcGroupsPerStage * kCellBytes,
+                 p.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCellBytes,
+                 (uint32_t)(ng * kCellBytes), &raw_full[s]);
+      } else if (lane >= 4 && lane < 4 + ng) {
+        const int g = lane - 4;
+        bulk_g2s(st + S::kRawBytes + g * NT * 32, p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 256,
+                 (uint32_t)(NT * 32), &raw_full[s]);
       }
     }
-  } else if (warp == 13) {
+  } else if (warp == kTcEpiWarps + 5) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = NT, M = 128
@@ -186,30 +200,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
         const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
         uint8_t* st = stages + (size_t)s * S::kStageBytes;
         const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(st + S::kRawBytes + S::kBBytes);
-        for (int g = 0; g < ng; ++g)
+        const uint64_t a_desc = make_kmajor_desc(a_addr, 128, 256), b_desc = make_kmajor_desc(b_addr, 128, 256);
+#pragma unroll
+        for (int g = 0; g < kTcGroupsPerStage; ++g) {
+          if (g >= ng) break;
+          // the start-address field counts 16-byte units: the next K-group is a constant further on
           tc_mma_i8(tmem_base + (uint32_t)((slot * kTcGroupsPerStage + g) * NT),
-                    make_kmajor_desc(a_addr + g * kTcTileRows * 32, 128, 256),
-                    make_kmajor_desc(b_addr + g * NT * 32, 128, 256), idesc);
-        tc_commit(&acc_full[slot]);    // the batch's accumulators are complete
-        tc_commit(&stage_empty[s]);    // raw cells, A and B of this stage may be overwritten
+                    a_desc + (uint64_t)(g * (kTcTileRows * 32 / 16)), b_desc + (uint64_t)(g * (NT * 32 / 16)), idesc);
+        }
+        // one commit per stage: the batch's accumulators are complete (epilogue) and the stage's raw
+        // cells, A and B may be overwritten (producer, dequant)
+        tc_commit(&mma_done[s]);
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= kTcEpiWarps) {
     // ------------------------------------------------------------ dequant: thread j = weight row j of the tile
-    const int j = tid - 8 * 32;
+    const int j = tid - kTcEpiWarps * 32;
     const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
     const bool have_panel = panel0 + q < p.num_panels;
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
       const int s = it % kTcStages;
       const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
-      ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&stage_empty[s], ph ^ 1u);
+      ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&mma_done[s], ph ^ 1u);
       if (!ok) break;
       const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
       uint8_t* st = stages + (size_t)s * S::kStageBytes;
       const uint8_t* raw = st + q * kTcGroupsPerStage * kCellBytes;
       uint8_t* a_out = st + S::kRawBytes + S::kBBytes + (j >> 3) * 256 + (j & 7) * 16;
-      for (int g = 0; g < ng; ++g) {
+#pragma unroll
+      for (int g = 0; g < kTcGroupsPerStage; ++g) {
+        if (g >= ng) break;
         uint4 w = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
         if (have_panel) w = *reinterpret_cast<const uint4*>(raw + g * kCellBytes + r * 16);
         // byte = 16 * (nibble - 8) as signed int8: low nibbles shifted up, high nibbles in place, flip bit 7
@@ -230,8 +251,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    constexpr int CW = NT / 2;  // columns per warp
-    const int quad = warp & 3, half = warp >> 2;
+    constexpr int CW = NT / 4;  // columns per warp
+    const int quad = warp & 3, half = warp >> 2;  // half = which quarter of the columns
     const int row = quad * 32 + lane;                // weight row inside the tile == TMEM lane
     const int n = tile_n * kTcTileRows + row;
     const bool have_panel = panel0 + quad < p.num_panels;
@@ -258,40 +279,39 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
         const int it = it2 + h;
         if (it >= k_tiles || !ok) break;
         const int slot = it % kSlots;
-        ok = mbar_wait_bounded(&acc_full[slot], (uint32_t)(it / kSlots) & 1u);
+        ok = mbar_wait_bounded(&mma_done[it % kTcStages], (uint32_t)(it / kTcStages) & 1u);
         if (!ok) break;
         tc_fence_after();
         const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
+        // kLoadGroups accumulators into registers per wait (register budget: 704 threads share the
+        // file); after the batch's last load its slot goes back to the MMA issuer
+        constexpr int kLoadGroups = CW == 16 ? 2 : 4;
 #pragma unroll
-        for (int g = 0; g < kTcGroupsPerStage; ++g) {
-          if (g >= ng) break;
-          const int u = h * kTcGroupsPerStage + g;
-          const int cnt = it * kTcGroupsPerStage + g;
-          // group scale / 16 (the A operand carries 16 * weight); exact: a power-of-two factor
-          const float s16 = decode_scale(sraw[u], scale_mode) * 0.0625f;
-          const int nxt = cnt + kScaleAhead;
-          sraw[u] = (have_panel && nxt < p.num_groups) ? *reinterpret_cast<const uint16_t*>(scale_ptr + (size_t)nxt * kCellBytes) : 0u;
-          const uint32_t col = lane_addr + (uint32_t)((slot * kTcGroupsPerStage + g) * NT);
-          // software pipeline over 16-column chunks: the next chunk's TMEM load is in flight during the math
-          uint32_t v[2][16];
-          tmem_ld16(col, v[0]);
+        for (int g0 = 0; g0 < kTcGroupsPerStage; g0 += kLoadGroups) {
+          if (g0 >= ng) break;
+          uint32_t v[kLoadGroups][CW];
 #pragma unroll
-          for (int c0 = 0; c0 < CW; c0 += 16) {
-            const int cur = (c0 >> 4) & 1;
-            tmem_ld_wait();
-            if (c0 + 16 < CW) {
-              tmem_ld16(col + (uint32_t)(c0 + 16), v[cur ^ 1]);
-            } else if (g == ng - 1) {  // the whole batch is in registers: hand its slot back to the MMA issuer
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&acc_empty[slot]);
-            }
+          for (int j = 0; j < kLoadGroups; ++j)
+            if (g0 + j < ng) tmem_ld_cols<CW>(lane_addr + (uint32_t)((slot * kTcGroupsPerStage + g0 + j) * NT), v[j]);
+          tmem_ld_wait();
+          if (g0 + kLoadGroups >= ng) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[slot]);
+          }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              // exact int32 -> fp32 for |v| < 2^22: add 1.5 * 2^23 as an integer, subtract it as a float
-              const float f = __int_as_float((int)v[cur][i] + 0x4B400000) - 12582912.0f;
-              acc[c0 + i] = fmaf(f, s16, acc[c0 + i]);
-            }
+          for (int j = 0; j < kLoadGroups; ++j) {
+            const int g = g0 + j;
+            if (g >= ng) break;
+            const int u = h * kTcGroupsPerStage + g;
+            const int cnt = it * kTcGroupsPerStage + g;
+            // group scale / 16 (the A operand carries 16 * weight); exact: a power-of-two factor
+            const float s16 = decode_scale(sraw[u], scale_mode) * 0.0625f;
+            const int nxt = cnt + kScaleAhead;
+            sraw[u] = (have_panel && nxt < p.num_groups) ? *reinterpret_cast<const uint16_t*>(scale_ptr + (size_t)nxt * kCellBytes) : 0u;
+            // |group sum| <= 16 * 32 * 128 * 8 < 2^24: the int32 -> fp32 conversion is exact
+#pragma unroll
+            for (int i = 0; i < CW; ++i) acc[i] = fmaf((float)(int)v[j][i], s16, acc[i]);
           }
         }
       }
@@ -316,7 +336,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == kTcEpiWarps + 5) {
     tc_fence_after();
     tmem_dealloc(tmem_base, (uint32_t)kTcTmemCols);
   }
