@@ -136,6 +136,93 @@ __global__ void __launch_bounds__(kQuantThreads) act_quant_records_kernel(const 
   }
 }
 
+// The tcgen05 GEMM's B operand: [K-group][row/8][256-byte block], a block = 8 rows x 32 int8 as two
+// 128-byte core matrices (row r at byte r*16 of each).  One CTA quantizes 8 consecutive rows, one
+// warp per row, so that every 256-byte block is written whole by one CTA (a one-row-per-CTA kernel
+// scatters 8-byte pieces 16 KB apart and was measured at 545 us for M=512, K=8192).
+// Pass 1: coalesced read of the row for min/max; pass 2: lane = K-group, 32 consecutive floats each.
+// Four warps share a row (each scans a quarter of it; the partial min/max meet in shared memory).
+// grid = ceil(M/8), block = 1024 (8 rows x 4 warps).
+constexpr int kBlocksWarpsPerRow = 4;
+__global__ void __launch_bounds__(8 * kBlocksWarpsPerRow * 32) act_quant_blocks_kernel(
+    const float* __restrict__ x, int m_total, int k, int ldx, int num_groups, int m8_pad, uint8_t* __restrict__ blocks,
+    float2* __restrict__ hdr) {
+  __shared__ float s_mm[8][kBlocksWarpsPerRow][2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = warp & 7, part = warp >> 3;
+  const int m = blockIdx.x * 8 + r;
+  const bool live = m < m_total;  // padding rows are never read back
+  const float* row = x + (size_t)(live ? m : 0) * ldx;
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  if (live) {
+    const int stride = 32 * kBlocksWarpsPerRow, first = part * 32 + lane;
+    if (vec) {
+      const float4* r4 = reinterpret_cast<const float4*>(row);
+      for (int i = first; i < (k >> 2); i += stride) {
+        const float4 v = r4[i];
+        mn = fminf(mn, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
+        mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+      }
+      for (int i = (k & ~3) + first; i < k; i += stride) {
+        mn = fminf(mn, row[i]);
+        mx = fmaxf(mx, row[i]);
+      }
+    } else {
+      for (int i = first; i < k; i += stride) {
+        mn = fminf(mn, row[i]);
+        mx = fmaxf(mx, row[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) {
+    s_mm[r][part][0] = mn;
+    s_mm[r][part][1] = mx;
+  }
+  __syncthreads();
+  if (!live) return;
+#pragma unroll
+  for (int q = 0; q < kBlocksWarpsPerRow; ++q) {
+    mn = fminf(mn, s_mm[r][q][0]);
+    mx = fmaxf(mx, s_mm[r][q][1]);
+  }
+  const ActQuantParams p = act_quant_params(mn, mx);
+  if (lane == 0 && part == 0) hdr[m] = make_float2(p.recip_scale, __int_as_float(-p.nzp));
+  for (int g = part * 32 + lane; g < num_groups; g += 32 * kBlocksWarpsPerRow) {
+    const int k0 = g * kGroup;
+    uint32_t w[8];  // lo0 hi0 lo1 hi1 | lo2 hi2 lo3 hi3 : the two 16-byte K chunks of this row
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+      if (vec && k0 + i * 8 + 8 <= k) {
+        const float4 a = *reinterpret_cast<const float4*>(row + k0 + i * 8);
+        const float4 b = *reinterpret_cast<const float4*>(row + k0 + i * 8 + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = (k0 + i * 8 + j < k) ? row[k0 + i * 8 + j] : 0.0f;
+      }
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t q = (k0 + i * 8 + j < k) ? ((uint32_t)act_quant_value(f[j], p) & 0xFFu) : 0u;
+        if (j & 1) hi |= q << (8 * (j >> 1));
+        else lo |= q << (8 * (j >> 1));
+      }
+      w[2 * i] = lo;
+      w[2 * i + 1] = hi;
+    }
+    uint8_t* blk = blocks + ((size_t)g * m8_pad + (m >> 3)) * 256 + (m & 7) * 16;
+    *reinterpret_cast<uint4*>(blk) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(blk + 128) = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 // grid = M rows, block = 256
 __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* __restrict__ x, int k, int ldx,
                                                                   uint8_t* __restrict__ out) {
@@ -162,6 +249,10 @@ __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* _
 cudaError_t launch_act_quant_records(const float* x, int m, int k, int ldx, uint8_t* records, float2* hdr, int use_pdl,
                                      int m8_pad, cudaStream_t stream) {
   const int num_groups = (k + kGroup - 1) / kGroup;
+  if (m8_pad > 0) {
+    act_quant_blocks_kernel<<<(m + 7) / 8, 8 * kBlocksWarpsPerRow * 32, 0, stream>>>(x, m, k, ldx, num_groups, m8_pad, records, hdr);
+    return cudaGetLastError();
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)m, 1, 1);
   cfg.blockDim = dim3(kQuantThreads, 1, 1);

@@ -24,7 +24,8 @@
 //   warps 16-19 dequant: thread j expands weight row j of the tile, 4 K-groups per stage
 //   warp 20     producer: bulk copies (cp.async.bulk) of raw weight cells and activation blocks
 //   warp 21     MMA issuer (one elected lane) and tensor-memory allocation
-// Shared memory: 4 stages of {raw cells 9 KB, B operand NT*128 B, A operand 16 KB}.  Tensor memory:
+// Shared memory: 8 stages of loaded data {raw cells 9 KB, B operand NT*128 B} and 3 stages of the
+// dequantized A operand (16 KB each).  Tensor memory:
 // all 512 columns, as 512/(4*NT) batches of 4 accumulators (one per K-group of a stage); a batch
 // is handed to the epilogue with one commit and handed back with one arrive per warp, so the
 // MMA -> epilogue -> MMA round trip (thousands of cycles) is paid once per 4 K-groups and several
@@ -35,7 +36,8 @@ namespace mllmb200 {
 
 constexpr int kTcEpiWarps = 16;     // 4 per TMEM lane quadrant, each a quarter of the columns
 constexpr int kTcThreads = (kTcEpiWarps + 6) * 32;  // + 4 dequant warps + producer + MMA issuer
-constexpr int kTcStages = 4;        // shared-memory stages
+constexpr int kTcStages = 8;        // shared-memory stages of loaded data (raw weight cells + B operand): deep, to cover HBM latency
+constexpr int kTcAStages = 3;       // shared-memory stages of the dequantized A operand (produced on chip: shallow)
 constexpr int kTcGroupsPerStage = 4;  // K-groups (of 32) per stage
 constexpr int kTcTileRows = 128;    // weight rows per CTA (= 4 panels)
 constexpr int kTcTmemCols = 512;    // all of tensor memory: accumulator batches of 4 K-groups x NT columns
@@ -111,9 +113,10 @@ struct TcSmem {
   static constexpr int kRawBytes = 4 * kTcGroupsPerStage * kCellBytes;  // 9216
   static constexpr int kBBytes = kTcGroupsPerStage * NT * 32;
   static constexpr int kABytes = kTcGroupsPerStage * kTcTileRows * 32;  // 16384
-  static constexpr int kStageBytes = kRawBytes + kBBytes + kABytes;
+  static constexpr int kStageBytes = kRawBytes + kBBytes;  // one loaded stage
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kBarBytes + kTcStages * kStageBytes + 1024;  // + alignment slack
+  static constexpr int kAOffset = kBarBytes + kTcStages * kStageBytes;
+  static constexpr int kTotal = kAOffset + kTcAStages * kABytes + 1024;  // + alignment slack
 };
 
 template <int NT>
@@ -123,13 +126,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [kTcStages]
   uint64_t* mma_done = raw_full + kTcStages;               // [kTcStages] the MMAs of a stage completed
-  uint64_t* a_full = mma_done + kTcStages;                 // [kTcStages]
+  uint64_t* a_full = mma_done + kTcStages;                 // [kTcAStages]
   // accumulators are handed over in batches of one shared-memory stage (4 K-groups): one barrier
   // round trip per 4 MMAs instead of per MMA, and kSlots batches in flight
   constexpr int kSlots = kTcTmemCols / (kTcGroupsPerStage * NT);
-  uint64_t* acc_empty = a_full + kTcStages;                // [kSlots]
+  uint64_t* acc_empty = a_full + kTcAStages;               // [kSlots]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_empty + kSlots);
   uint8_t* stages = smem + S::kBarBytes;
+  uint8_t* a_stages = smem + S::kAOffset;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile_n = blockIdx.x;  // 128 weight rows
@@ -142,8 +146,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&raw_full[s], 1);
       mbar_init(&mma_done[s], 1);
-      mbar_init(&a_full[s], 128);
     }
+    for (int s = 0; s < kTcAStages; ++s) mbar_init(&a_full[s], 128);
     for (int t = 0; t < kSlots; ++t) {
       mbar_init(&acc_empty[t], kTcEpiWarps);  // one arrival per epilogue warp
     }
@@ -193,13 +197,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
         const int s = it % kTcStages;
         const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
         const int slot = it % kSlots;
-        ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&a_full[s], ph) &&
+        const int sa = it % kTcAStages;
+        ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&a_full[sa], (uint32_t)(it / kTcAStages) & 1u) &&
              mbar_wait_bounded(&acc_empty[slot], ((uint32_t)(it / kSlots) & 1u) ^ 1u);
         if (!ok) break;
         tc_fence_after();
         const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
         uint8_t* st = stages + (size_t)s * S::kStageBytes;
-        const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(st + S::kRawBytes + S::kBBytes);
+        const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(a_stages + (size_t)sa * S::kABytes);
         const uint64_t a_desc = make_kmajor_desc(a_addr, 128, 256), b_desc = make_kmajor_desc(b_addr, 128, 256);
 #pragma unroll
         for (int g = 0; g < kTcGroupsPerStage; ++g) {
@@ -208,8 +213,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
           tc_mma_i8(tmem_base + (uint32_t)((slot * kTcGroupsPerStage + g) * NT),
                     a_desc + (uint64_t)(g * (kTcTileRows * 32 / 16)), b_desc + (uint64_t)(g * (NT * 32 / 16)), idesc);
         }
-        // one commit per stage: the batch's accumulators are complete (epilogue) and the stage's raw
-        // cells, A and B may be overwritten (producer, dequant)
+        // one commit per K-tile: its accumulators are complete (epilogue), its loaded stage may be
+        // refilled (producer) and its A stage rewritten (dequant); waiters pick the phase they need
         tc_commit(&mma_done[s]);
       }
     }
@@ -222,12 +227,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
     for (int it = 0; it < k_tiles && ok; ++it) {
       const int s = it % kTcStages;
       const uint32_t ph = (uint32_t)(it / kTcStages) & 1u;
-      ok = mbar_wait_bounded(&raw_full[s], ph) && mbar_wait_bounded(&mma_done[s], ph ^ 1u);
+      ok = mbar_wait_bounded(&raw_full[s], ph);
+      const int sa = it % kTcAStages;
+      if (ok && it >= kTcAStages) {  // the A stage is free once the MMAs of K-tile it - kTcAStages are done
+        const int prev = it - kTcAStages;
+        ok = mbar_wait_bounded(&mma_done[prev % kTcStages], (uint32_t)(prev / kTcStages) & 1u);
+      }
       if (!ok) break;
       const int ng = min(kTcGroupsPerStage, p.num_groups - it * kTcGroupsPerStage);
       uint8_t* st = stages + (size_t)s * S::kStageBytes;
       const uint8_t* raw = st + q * kTcGroupsPerStage * kCellBytes;
-      uint8_t* a_out = st + S::kRawBytes + S::kBBytes + (j >> 3) * 256 + (j & 7) * 16;
+      uint8_t* a_out = a_stages + (size_t)sa * S::kABytes + (j >> 3) * 256 + (j & 7) * 16;
 #pragma unroll
       for (int g = 0; g < kTcGroupsPerStage; ++g) {
         if (g >= ng) break;
@@ -247,7 +257,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcPa
         *reinterpret_cast<uint4*>(a_out + g * kTcTileRows * 32 + 128) = c1;  // K chunk 1
       }
       fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
-      mbar_arrive(&a_full[s]);
+      mbar_arrive(&a_full[sa]);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -385,21 +395,10 @@ cudaError_t launch_w4a32_gemm_tc(const uint8_t* a_blocks, const float2* a_hdr, c
   const TiledHeader th = make_tiled_header(n, k, 0, 0);
   prm.zsum_off = th.zsum_off;
   prm.bias_off = th.bias_off;
-  // Tile width along the activation rows: the wider of 64/32 that fills the 148 SMs best
-  // (CTAs run one per SM; a tile's cost is proportional to its width, so only the fill matters).
-  const int n_tiles = (prm.num_panels + 3) / 4;
-  int best_nt = 32;
-  double best_fill = -1.0;
-  for (int nt : {64, 32}) {
-    if (nt > 32 && m <= nt / 2) continue;  // would be mostly padding
-    const long long tiles = (long long)n_tiles * ((m + nt - 1) / nt);
-    const double waves = (double)((tiles + 147) / 148);
-    const double fill = (double)tiles / (waves * 148.0) * ((double)m / (double)(((m + nt - 1) / nt) * nt));
-    if (fill > best_fill + 1e-9) {
-      best_fill = fill;
-      best_nt = nt;
-    }
-  }
+  // Tile width along the activation rows.  A tile's time is dominated by per-K-tile costs that do
+  // not depend on its width (dequantization of the 128 weight rows, copy and MMA issue), measured
+  // ~51 us for K = 8192 at either width, so the wide tile wins whenever M has the rows for it.
+  const int best_nt = m > 32 ? 64 : 32;
   if (best_nt == 32) return launch_tc_t<32>(prm, stream);
   return launch_tc_t<64>(prm, stream);
 }
