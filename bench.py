@@ -41,6 +41,7 @@ LAYERS = 28
 LINEARS = [("q", 1536, 1536, True), ("k", 1536, 256, True), ("v", 1536, 256, True), ("o", 1536, 1536, False),
            ("gate", 1536, 8960, False), ("up", 1536, 8960, False), ("down", 8960, 1536, False)]
 PREFILL_M = 512
+NCU_GEMV_DRAM_BYTES_PER_LAYER = 26.61e6
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -382,12 +383,11 @@ def run_gpu(args):
                 "algorithmic_bytes_per_gemv_launch": step_bytes / calls_per_step,
                 "note": "achieved = algorithmic bytes of the step / device time of the step; each GEMV launch is "
                         "preceded by its activation-quantization kernel, whose time is inside the step"}
-    tr = os.path.join(ROOT, "profiles", "gemv_traffic.json")
-    if os.path.exists(tr):
-        try:
-            roofline["traffic"] = json.load(open(tr)).get("traffic_bytes_per_launch_avg")
-        except Exception:
-            pass
+    # dram__bytes_read + dram__bytes_write of the four GEMV launches of one layer, from the ncu capture
+    # summarized in profiles/gemv_decode_qwen2_1p5b.md (26.61 MB per layer vs 26.49 MB algorithmic)
+    if not args.per_op:
+        roofline["traffic"] = NCU_GEMV_DRAM_BYTES_PER_LAYER / 4.0
+        roofline["traffic_note"] = "ncu dram bytes per GEMV launch, average over the 4 launches of a layer"
 
     line = {"metric": "W4A32 decode-linear HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
