@@ -300,6 +300,9 @@ def run_gpu(args):
 
     # ---- weights: 28 layers x 7 linears, each its own tiled buffer
     layers = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(LAYERS)]
+    if args.decoder_only:
+        print(json.dumps({"decoder": run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind)}), flush=True)
+        return
     xs = {k: torch.randn((1, k), device="cuda", generator=gen) for k in (1536, 8960)}
     ys = {n: torch.empty((1, n), device="cuda") for n in (1536, 256, 8960)}
     stream = torch.cuda.Stream()
@@ -536,6 +539,12 @@ def run_gpu(args):
                 line["cpu_baseline"] = dict(line["cpu_port"])
         except Exception as ex:  # the oracle is optional for the bench
             line["cpu_port"] = {"unavailable": str(ex)[:100]}
+        if not args.no_decoder and world == 1:
+            try:
+                cpu_ms = line.get("cpu_baseline", {}).get("ms_per_layer")
+                line["decoder"] = run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms)
+            except Exception as ex:
+                line["decoder"] = {"error": str(ex)[:200]}
     elif rank == 0:
         line["e2e"] = None
 
@@ -548,6 +557,73 @@ def run_gpu(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_layer=None):
+    """BASELINE config 2: the whole 28-layer decoder with random-init W4A32 weights, batch 1,
+    512-token prompt of uniform random ids, 128 greedy decode steps, fp32 KV cache, fp16 lm_head."""
+    cfg = dict(mb.QWEN2_1P5B, max_ctx=1024)
+    prompt_len, steps = 512, 128
+    dec = mb.Qwen2Decoder(cfg)
+    for l, lw in enumerate(layers):
+        for (name, _, _, _), w in zip(LINEARS, lw):
+            dec.set_linear_tiled(l, name, w)
+        dec.set_norm(0, l, np.ones(cfg["hidden"], np.float32))
+        dec.set_norm(1, l, np.ones(cfg["hidden"], np.float32))
+    dec.set_norm(2, 0, np.ones(cfg["hidden"], np.float32))
+    emb = torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen)
+    head = (torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen) * 0.02).to(torch.float16)
+    dec.set_tables(emb, head)
+    host_prompt = np.random.default_rng(7).integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+    ds = dec.stream()
+    dec.prefill(host_prompt)
+    dec.decode(4)  # first call also captures the step graph
+    ds.synchronize()
+    mb.check_device_status(ds)
+    reps = max(1, args.decoder_reps)
+    pf, dc, wall = [], [], []
+    toks = None
+    for _ in range(reps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t0 = time.perf_counter()
+        tokens_dev = torch.from_numpy(host_prompt).to("cuda")  # H2D of the prompt, inside the e2e region
+        torch.cuda.current_stream().synchronize()
+        ev[0].record(ds)
+        dec.prefill_device(tokens_dev)
+        ev[1].record(ds)
+        dec.decode(steps)
+        ev[2].record(ds)
+        toks = dec.generated(steps)  # synchronizes, D2H of the sampled tokens
+        wall.append(time.perf_counter() - t0)
+        pf.append(ev[0].elapsed_time(ev[1]))
+        dc.append(ev[1].elapsed_time(ev[2]))
+    mb.check_device_status(ds)
+    pf_ms, dc_ms, wall_s = min(pf), min(dc), min(wall)
+    # algorithmic bytes of one decode step at the mean context of the run
+    lin = LAYERS * sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
+    head_b = cfg["vocab"] * cfg["hidden"] * 2
+    ctx_mean = prompt_len + steps / 2
+    kv_b = LAYERS * 2 * cfg["kv_heads"] * cfg["head_dim"] * 4 * ctx_mean
+    step_b = lin + head_b + kv_b
+    out = {"config": "28 layers, hidden 1536, 12q/2kv heads x128, inter 8960, vocab 151936, rope 1e6; batch 1, "
+                     "512-token prompt, 128 greedy steps, fp32 KV cache, fp16 lm_head, random-init weights",
+           "prefill_ms": pf_ms, "prefill_tokens_per_s": prompt_len / (pf_ms * 1e-3),
+           "decode_ms_per_token": dc_ms / steps, "decode_tokens_per_s": steps / (dc_ms * 1e-3),
+           "e2e_wall_s": wall_s, "e2e_decode_tokens_per_s": steps / wall_s,
+           "e2e_note": "host prompt -> H2D -> prefill -> 128 steps -> D2H of the sampled tokens, host wall clock; "
+                       "tokens/s counts the 128 generated tokens over the whole wall time (prefill included)",
+           "bytes_per_decode_step": step_b,
+           "decode_roofline": {"bound": "hbm", "achieved": step_b / (dc_ms / steps * 1e-3) / 1e9, "peak": hbm_peak,
+                               "unit": "GB/s", "frac": step_b / (dc_ms / steps * 1e-3) / 1e9 / hbm_peak,
+                               "peak_kind": f"of {peak_kind}"},
+           "launches_per_decode_step": 1 + LAYERS * 9 + 4, "distinct_tokens": int(len(set(toks.tolist())))}
+    if cpu_ms_per_layer:
+        out["cpu_reference_linears_only_tokens_per_s"] = 1e3 / (cpu_ms_per_layer * LAYERS)
+        out["cpu_note"] = ("upper bound for the host-CPU reference: only the 28x7 linears of a step, timed with the "
+                           "reference X86 Q4_K x Q8_K kernels; attention, norms and lm_head not included")
+    dec.close()
+    del emb, head
+    return out
 
 
 def run_tp(args, torch, mb, dist, rank, world, gen):
@@ -599,6 +675,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch on the stream instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
     ap.add_argument("--per-op", action="store_true", help="headline step with one call per linear instead of grouped calls")
+    ap.add_argument("--decoder-only", action="store_true", help="only the whole-model prefill + decode section")
+    ap.add_argument("--decoder-reps", type=int, default=3, help="timed repetitions of prefill + 128 steps")
+    ap.add_argument("--no-decoder", action="store_true", help="skip the whole-model prefill + decode section")
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run one decoder layer's seven linears at M=512 once and exit (small target for ncu)")

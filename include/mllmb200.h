@@ -167,6 +167,43 @@ MLLMB200_API int mllmb200_w4a32_linear_forward_static(const float* x_dev, const 
 /* Capacity of that array in bytes. */
 MLLMB200_API int mllmb200_w4a32_static_scratch_bytes(size_t* bytes);
 
+/* ------------------------------------------------------------------------------------------
+ * Decoder: the Qwen2-architecture language model whose linears are the W4A32 op above
+ * (reference project: mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:47-54,106-155,175-215, greedy loop
+ * mllm/Models/AutoLLM.hpp:39-105).  Batch 1, fp32 activations and KV cache, fp16 lm_head, greedy
+ * sampling on the device.  A decode step is one CUDA graph replay; the position and the current
+ * token live in device memory.  All calls are asynchronous on the decoder's own stream except
+ * set_* (which synchronize it) and read.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct mllmb200_qwen2_config {
+  int layers, hidden, q_heads, kv_heads, head_dim, inter, vocab, max_ctx;
+  float eps, rope_theta;
+} mllmb200_qwen2_config;
+
+MLLMB200_API int mllmb200_qwen2_create(const mllmb200_qwen2_config* cfg, void** handle);
+MLLMB200_API void mllmb200_qwen2_destroy(void* handle);
+/* which: 0 q, 1 k, 2 v, 3 o, 4 gate, 5 up, 6 down; blob_dev: pre-pack blob in device memory
+ * (repacked into the decoder's own tiled buffer; the blob may be freed afterwards). */
+MLLMB200_API int mllmb200_qwen2_set_linear(void* handle, int layer, int which, const void* blob_dev, int N, int K,
+                                           int scale_mode, int has_bias);
+/* Same, adopting a buffer already in the tile layout (repack_device output for the whole [N, K]
+ * matrix of that projection); borrowed - keep it alive.  The shape is taken from the config. */
+MLLMB200_API int mllmb200_qwen2_set_linear_tiled(void* handle, int layer, int which, const void* tiled_dev);
+/* kind: 0 input norm, 1 post-attention norm (of `layer`), 2 final norm; src_dev fp32 [hidden], copied. */
+MLLMB200_API int mllmb200_qwen2_set_norm(void* handle, int kind, int layer, const float* src_dev);
+/* Borrowed: embedding fp32 [vocab, hidden], lm_head fp16 [vocab, hidden]; keep them alive. */
+MLLMB200_API int mllmb200_qwen2_set_tables(void* handle, const float* embedding_dev, const void* lm_head_f16_dev);
+/* Prompt of n tokens (int32 on the device) from an empty cache; samples the next token. */
+MLLMB200_API int mllmb200_qwen2_prefill(void* handle, const int* tokens_dev, int n);
+/* `steps` greedy decode steps, each feeding the previously sampled token. */
+MLLMB200_API int mllmb200_qwen2_decode(void* handle, int steps);
+/* Synchronizes; copies to HOST memory history[first, first+count) (entry p = the token sampled after
+ * position p), the number of tokens in the cache, and the last logits [vocab]; NULLs are skipped. */
+MLLMB200_API int mllmb200_qwen2_read(void* handle, int first, int count, int* tokens_out, int* pos_out,
+                                     float* logits_out);
+/* The decoder's CUDA stream (cudaStream_t), for event timing. */
+MLLMB200_API void* mllmb200_qwen2_stream(void* handle);
+
 /* Device-side status word (bounded waits that ran out, bad tile headers).  Synchronizes `stream`,
  * reads and clears the word.  0 = clean. */
 MLLMB200_API int mllmb200_check_device_status(void* stream);

@@ -1,0 +1,206 @@
+// Qwen2-architecture decoder (DeepSeek-Distill-Qwen-1.5B, Qwen2VL-2B language tower) on top of the
+// W4A32 linears: host-side orchestration behind a C ABI (include/mllmb200.h, "decoder" section).
+// Mirrors the forward of the reference project's model, mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:
+// 106-155 (attention), :47-54 (MLP), :175-183 (decoder layer), :202-215 (model), and its greedy
+// loop mllm/Models/AutoLLM.hpp:39-65.  Batch 1, fp32 activations and KV cache, fp16 lm_head.
+//
+// Decode runs as ONE CUDA graph per token, replayed: the position and the current token live in
+// device memory, so nothing changes between replays.  In decode every op that feeds a quantized
+// linear also writes that linear's int8 activation records, so a layer is 9 launches:
+//   add+rmsnorm+quant, gemv(q,k,v), attention over context splits (rotates, appends K/V),
+//   merge of the splits + quant, gemv(o), add+rmsnorm+quant,
+//   gemv(gate,up), silu*up+quant, gemv(down)      (the residual add of `down` is fused into the next norm)
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <vector>
+
+#include "../../include/mllmb200.h"
+#include "device_common.cuh"
+
+namespace mllmb200 {
+// kernels defined in the other translation units
+__global__ void add_rmsnorm_quant_kernel(const float*, const float*, const float*, float, int, float*, float*, uint8_t*,
+                                         float2*, int);
+__global__ void silu_mul_quant_kernel(const float*, const float*, int, float*, uint8_t*, float2*, int);
+__global__ void embedding_kernel(const int*, const float*, int, float*);
+__global__ void rope_tables_kernel(float*, float*, int, int, float);
+__global__ void rope_kv_append_kernel(const float*, const float*, int, const float*, const float*, const int*, int,
+                                      float*, float*);
+__global__ void attention_kernel(const float*, int, const float*, const float*, const int*, int, int, const float*,
+                                 const float*, float*, int, int);
+template <int D>
+__global__ void attn_decode_partial_kernel(const float*, const float*, const float*, const float*, const float*, const int*,
+                                           int, int, int, float*, float*, float*, float*, int, int);
+__global__ void attn_combine_quant_kernel(const float*, const float*, const int*, int, int, int, int, int, float*, uint8_t*,
+                                          float2*, int);
+__global__ void lm_head_f16_kernel(const float*, const __half*, int, int, float*);
+__global__ void argmax_kernel(const float*, int, int*);
+__global__ void act_quant_records_kernel(const float*, int, int, int, uint8_t*, float2*, int, int);
+cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
+                                      const int*, const int*, int, cudaStream_t);
+cudaError_t launch_act_quant_records(const float*, int, int, int, uint8_t*, float2*, int, int, cudaStream_t);
+
+__global__ void advance_kernel(int* pos, int* token, const int* next, int* history, int max_hist) {
+  // after a step: the sampled token becomes the input of the next step and is appended to the history
+  const int p = *pos;
+  *token = *next;
+  if (p < max_hist) history[p] = *next;
+  *pos = p + 1;
+}
+__global__ void set_int_kernel(int* dst, int v) { *dst = v; }
+
+namespace {
+
+enum { kQ = 0, kK, kV, kO, kGate, kUp, kDown, kNumLinears };
+
+struct Layer {
+  void* w[kNumLinears] = {};
+  float *ln1 = nullptr, *ln2 = nullptr;
+  float *cache_k = nullptr, *cache_v = nullptr;
+};
+
+struct Decoder {
+  mllmb200_qwen2_config cfg{};
+  std::vector<Layer> layers;
+  float* final_norm = nullptr;
+  const float* embedding = nullptr;  // borrowed, fp32 [vocab, hidden]
+  const __half* lm_head = nullptr;   // borrowed, fp16 [vocab, hidden]
+  float *sin_t = nullptr, *cos_t = nullptr;
+  // activations (rows = max_ctx for prefill; decode uses row 0)
+  float *h = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
+  float *gate = nullptr, *up = nullptr, *act = nullptr, *down = nullptr, *logits = nullptr;
+  uint8_t *rec_a = nullptr, *rec_b = nullptr;  // activation records (hidden-wide and inter-wide)
+  float2 *hdr_a = nullptr, *hdr_b = nullptr;
+  float *part_o = nullptr, *part_ml = nullptr;  // per-split attention partials (decode)
+  int attn_chunk = 32, attn_splits = 1;
+  void* ws = nullptr;  // workspace of the public forward (prefill)
+  size_t ws_bytes = 0;
+  int *pos = nullptr, *token = nullptr, *next = nullptr, *history = nullptr, *zero = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaGraphExec_t graph = nullptr;
+  std::vector<void*> owned;
+  int last_error = 0;
+};
+
+template <class T>
+bool dev_alloc(Decoder* d, T** p, size_t count) {
+  void* q = nullptr;
+  if (cudaMalloc(&q, count * sizeof(T)) != cudaSuccess) return false;
+  d->owned.push_back(q);
+  *p = static_cast<T*>(q);
+  return true;
+}
+
+// launch with the programmatic-dependent-launch attribute (the kernels call griddepcontrol themselves)
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define DEC_CHECK(expr)                     \
+  do {                                      \
+    cudaError_t e__ = (expr);               \
+    if (e__ != cudaSuccess) {               \
+      d->last_error = (int)e__;             \
+      return MLLMB200_CUDA_ERROR;           \
+    }                                       \
+  } while (0)
+#define DEC_ST(expr)                        \
+  do {                                      \
+    int s__ = (expr);                       \
+    if (s__ != MLLMB200_OK) return s__;     \
+  } while (0)
+
+int gemv_group(Decoder* d, const uint8_t* rec, const float2* hdr, int k, int count, const int* which, float* const* outs,
+               const Layer& L) {
+  const void* tiled[4];
+  int n[4], ldy[4];
+  const auto& c = d->cfg;
+  for (int i = 0; i < count; ++i) {
+    tiled[i] = L.w[which[i]];
+    switch (which[i]) {
+      case kQ: case kO: n[i] = (which[i] == kQ) ? c.q_heads * c.head_dim : c.hidden; break;
+      case kK: case kV: n[i] = c.kv_heads * c.head_dim; break;
+      case kGate: case kUp: n[i] = c.inter; break;
+      default: n[i] = c.hidden; break;
+    }
+    ldy[i] = n[i];
+  }
+  DEC_CHECK(launch_w4a32_gemv_grouped(rec, hdr, 1, k, count, tiled, outs, n, ldy, 1, d->stream));
+  return MLLMB200_OK;
+}
+
+// One decode step at the position / token held in device memory.
+int enqueue_decode_step(Decoder* d) {
+  const auto& c = d->cfg;
+  cudaStream_t s = d->stream;
+  const int H = c.hidden, QD = c.q_heads * c.head_dim, I = c.inter;
+  embedding_kernel<<<1, 256, 0, s>>>(d->token, d->embedding, H, d->h);
+  for (int l = 0; l < c.layers; ++l) {
+    const Layer& L = d->layers[l];
+    DEC_CHECK(launch_pdl(add_rmsnorm_quant_kernel, dim3(1), dim3(256), 0, s, d->h, l == 0 ? nullptr : d->down, L.ln1,
+                         c.eps, H, d->h, nullptr, d->rec_a, d->hdr_a, 1));
+    {
+      const int which[3] = {kQ, kK, kV};
+      float* outs[3] = {d->q, d->k, d->v};
+      DEC_ST(gemv_group(d, d->rec_a, d->hdr_a, H, 3, which, outs, L));
+    }
+    {
+      const dim3 grid(d->attn_splits, c.kv_heads);
+      const int group = c.q_heads / c.kv_heads;
+      if (c.head_dim == 128)
+        DEC_CHECK(launch_pdl(attn_decode_partial_kernel<128>, grid, dim3(256), 0, s, d->q, d->k, d->v, d->sin_t, d->cos_t,
+                             d->pos, c.max_ctx, d->attn_chunk, group, L.cache_k, L.cache_v, d->part_o, d->part_ml,
+                             d->attn_splits, 1));
+      else
+        DEC_CHECK(launch_pdl(attn_decode_partial_kernel<64>, grid, dim3(256), 0, s, d->q, d->k, d->v, d->sin_t, d->cos_t,
+                             d->pos, c.max_ctx, d->attn_chunk, group, L.cache_k, L.cache_v, d->part_o, d->part_ml,
+                             d->attn_splits, 1));
+      DEC_CHECK(launch_pdl(attn_combine_quant_kernel, dim3(1), dim3(512), (size_t)c.q_heads * d->attn_splits * sizeof(float),
+                           s, d->part_o, d->part_ml, d->pos, c.max_ctx, d->attn_chunk, d->attn_splits, c.q_heads, c.head_dim,
+                           nullptr, d->rec_a, d->hdr_a, 1));
+    }
+    {
+      const int which[1] = {kO};
+      float* outs[1] = {d->o};
+      DEC_ST(gemv_group(d, d->rec_a, d->hdr_a, QD, 1, which, outs, L));
+    }
+    DEC_CHECK(launch_pdl(add_rmsnorm_quant_kernel, dim3(1), dim3(256), 0, s, d->h, d->o, L.ln2, c.eps, H, d->h, nullptr,
+                         d->rec_a, d->hdr_a, 1));
+    {
+      const int which[2] = {kGate, kUp};
+      float* outs[2] = {d->gate, d->up};
+      DEC_ST(gemv_group(d, d->rec_a, d->hdr_a, H, 2, which, outs, L));
+    }
+    DEC_CHECK(launch_pdl(silu_mul_quant_kernel, dim3(1), dim3(512), (size_t)I * sizeof(float), s, d->gate, d->up, I,
+                         nullptr, d->rec_b, d->hdr_b, 1));
+    {
+      const int which[1] = {kDown};
+      float* outs[1] = {d->down};
+      DEC_ST(gemv_group(d, d->rec_b, d->hdr_b, I, 1, which, outs, L));
+    }
+  }
+  DEC_CHECK(launch_pdl(add_rmsnorm_quant_kernel, dim3(1), dim3(256), 0, s, d->h, d->down, d->final_norm, c.eps, H, d->h,
+                       d->xn, nullptr, nullptr, 1));
+  lm_head_f16_kernel<<<148 * 4, 256, H * sizeof(float), s>>>(d->xn, d->lm_head, H, c.vocab, d->logits);
+  argmax_kernel<<<1, 1024, 0, s>>>(d->logits, c.vocab, d->next);
+  advance_kernel<<<1, 1, 0, s>>>(d->pos, d->token, d->next, d->history, c.max_ctx);
+  DEC_CHECK(cudaGetLastError());
+  return MLLMB200_OK;
+}
+
+}  // namespace
+}  // namespace mllmb200
+
+#include "decoder_api.inc"
