@@ -195,8 +195,17 @@ MLLMB200_API int mllmb200_qwen2_set_norm(void* handle, int kind, int layer, cons
 MLLMB200_API int mllmb200_qwen2_set_tables(void* handle, const float* embedding_dev, const void* lm_head_f16_dev);
 /* Prompt of n tokens (int32 on the device) from an empty cache; samples the next token. */
 MLLMB200_API int mllmb200_qwen2_prefill(void* handle, const int* tokens_dev, int n);
-/* `steps` greedy decode steps, each feeding the previously sampled token. */
+/* `steps` greedy decode steps, each feeding the previously sampled token (needs a prefill first;
+ * position + steps must fit max_ctx).  mode 0 = automatic, 1 = one CUDA graph replay per step (one
+ * launch per operator), 2 = the persistent kernel: all steps in one cooperative launch of one CTA
+ * per SM that streams each CTA's share of the weights through a shared-memory ring
+ * (MLLMB200_UNSUPPORTED when the device or the shape does not allow it).  decode == decode_ex(.., 0). */
 MLLMB200_API int mllmb200_qwen2_decode(void* handle, int steps);
+MLLMB200_API int mllmb200_qwen2_decode_ex(void* handle, int steps, int mode);
+/* Host-only: builds the persistent kernel's static work plan for this shape and CTA count and
+ * verifies that every weight cell is streamed exactly once (no GPU needed).  Outputs may be NULL. */
+MLLMB200_API int mllmb200_qwen2_plan_check(const mllmb200_qwen2_config* cfg, int nctas, int* max_chunks,
+                                           int* max_slots, int* total_chunks);
 /* Synchronizes; copies to HOST memory history[first, first+count) (entry p = the token sampled after
  * position p), the number of tokens in the cache, and the last logits [vocab]; NULLs are skipped. */
 MLLMB200_API int mllmb200_qwen2_read(void* handle, int first, int count, int* tokens_out, int* pos_out,

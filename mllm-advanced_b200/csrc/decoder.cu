@@ -16,9 +16,15 @@
 #include <vector>
 
 #include "../../include/mllmb200.h"
+#include "decoder_state.h"
 #include "device_common.cuh"
 
 namespace mllmb200 {
+// persistent decode kernel (decoder_persistent.cu)
+void persistent_prepare(Decoder* d);
+bool persistent_usable(Decoder* d);
+cudaError_t persistent_decode(Decoder* d, int steps);
+void persistent_destroy(Decoder* d);
 // kernels defined in the other translation units
 __global__ void add_rmsnorm_quant_kernel(const float*, const float*, const float*, float, int, float*, float*, uint8_t*,
                                          float2*, int);
@@ -34,63 +40,16 @@ __global__ void attn_decode_partial_kernel(const float*, const float*, const flo
                                            int, int, int, float*, float*, float*, float*, int, int);
 __global__ void attn_combine_quant_kernel(const float*, const float*, const int*, int, int, int, int, int, float*, uint8_t*,
                                           float2*, int);
-__global__ void lm_head_f16_kernel(const float*, const __half*, int, int, float*);
-__global__ void argmax_kernel(const float*, int, int*);
+__global__ void lm_head_f16_kernel(const float*, const __half*, int, int, float*, float2*);
+__global__ void sample_advance_kernel(const float2*, int, int*, int*, int*, int*, int);
 __global__ void act_quant_records_kernel(const float*, int, int, int, uint8_t*, float2*, int, int);
 cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
                                       const int*, const int*, int, cudaStream_t);
 cudaError_t launch_act_quant_records(const float*, int, int, int, uint8_t*, float2*, int, int, cudaStream_t);
 
-__global__ void advance_kernel(int* pos, int* token, const int* next, int* history, int max_hist) {
-  // after a step: the sampled token becomes the input of the next step and is appended to the history
-  const int p = *pos;
-  *token = *next;
-  if (p < max_hist) history[p] = *next;
-  *pos = p + 1;
-}
 __global__ void set_int_kernel(int* dst, int v) { *dst = v; }
 
 namespace {
-
-enum { kQ = 0, kK, kV, kO, kGate, kUp, kDown, kNumLinears };
-
-struct Layer {
-  void* w[kNumLinears] = {};
-  float *ln1 = nullptr, *ln2 = nullptr;
-  float *cache_k = nullptr, *cache_v = nullptr;
-};
-
-struct Decoder {
-  mllmb200_qwen2_config cfg{};
-  std::vector<Layer> layers;
-  float* final_norm = nullptr;
-  const float* embedding = nullptr;  // borrowed, fp32 [vocab, hidden]
-  const __half* lm_head = nullptr;   // borrowed, fp16 [vocab, hidden]
-  float *sin_t = nullptr, *cos_t = nullptr;
-  // activations (rows = max_ctx for prefill; decode uses row 0)
-  float *h = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
-  float *gate = nullptr, *up = nullptr, *act = nullptr, *down = nullptr, *logits = nullptr;
-  uint8_t *rec_a = nullptr, *rec_b = nullptr;  // activation records (hidden-wide and inter-wide)
-  float2 *hdr_a = nullptr, *hdr_b = nullptr;
-  float *part_o = nullptr, *part_ml = nullptr;  // per-split attention partials (decode)
-  int attn_chunk = 32, attn_splits = 1;
-  void* ws = nullptr;  // workspace of the public forward (prefill)
-  size_t ws_bytes = 0;
-  int *pos = nullptr, *token = nullptr, *next = nullptr, *history = nullptr, *zero = nullptr;
-  cudaStream_t stream = nullptr;
-  cudaGraphExec_t graph = nullptr;
-  std::vector<void*> owned;
-  int last_error = 0;
-};
-
-template <class T>
-bool dev_alloc(Decoder* d, T** p, size_t count) {
-  void* q = nullptr;
-  if (cudaMalloc(&q, count * sizeof(T)) != cudaSuccess) return false;
-  d->owned.push_back(q);
-  *p = static_cast<T*>(q);
-  return true;
-}
 
 // launch with the programmatic-dependent-launch attribute (the kernels call griddepcontrol themselves)
 template <class... KArgs, class... Args>
@@ -193,9 +152,8 @@ int enqueue_decode_step(Decoder* d) {
   }
   DEC_CHECK(launch_pdl(add_rmsnorm_quant_kernel, dim3(1), dim3(256), 0, s, d->h, d->down, d->final_norm, c.eps, H, d->h,
                        d->xn, nullptr, nullptr, 1));
-  lm_head_f16_kernel<<<148 * 4, 256, H * sizeof(float), s>>>(d->xn, d->lm_head, H, c.vocab, d->logits);
-  argmax_kernel<<<1, 1024, 0, s>>>(d->logits, c.vocab, d->next);
-  advance_kernel<<<1, 1, 0, s>>>(d->pos, d->token, d->next, d->history, c.max_ctx);
+  lm_head_f16_kernel<<<kHeadCtas, 256, H * sizeof(float), s>>>(d->xn, d->lm_head, H, c.vocab, d->logits, d->best);
+  sample_advance_kernel<<<1, 32, 0, s>>>(d->best, kHeadCtas, d->pos, d->token, d->next, d->history, c.max_ctx);
   DEC_CHECK(cudaGetLastError());
   return MLLMB200_OK;
 }

@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 
 #include "device_common.cuh"
+#include "decoder_attn_body.cuh"
 
 namespace mllmb200 {
 
@@ -109,167 +110,26 @@ __global__ void attention_kernel(const float* __restrict__ q, int ldq, const flo
   out[(size_t)s * ldo + h * D + d] = o_acc;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Decode-step attention (one new token), split over the context so that the whole GPU works on it:
-// grid (splits, kv_heads), 256 threads.  CTA (split, kvh) covers cache positions
-// [split*chunk, min((split+1)*chunk, pos+1)) for all `group` query heads that share KV head kvh and
-// writes, per query head, an unnormalized partial output with its running maximum and sum
-// (the usual online-softmax split); attn_combine_quant_kernel merges the splits.  The CTA whose
-// range contains the new position rotates the new key, appends key and value to the cache and
-// uses them directly, so no separate append launch is needed.
-// part_o: [q_heads][splits][D], part_ml: [q_heads][splits][2] = {max, sum}.
-// ---------------------------------------------------------------------------------------------
-constexpr int kAttnThreads = 256;
-constexpr int kAttnMaxGroup = 8;
-constexpr int kAttnSub = 32;  // positions per inner block
-
+// Decode-step attention over context splits: the work of one CTA is attn_partial_body
+// (decoder_attn_body.cuh); grid (splits, kv_heads), 256 threads.
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(
     const float* __restrict__ q, const float* __restrict__ k_new, const float* __restrict__ v_new,
     const float* __restrict__ sin_t, const float* __restrict__ cos_t, const int* __restrict__ pos_ptr, int max_ctx,
     int chunk, int group, float* __restrict__ cache_k, float* __restrict__ cache_v, float* __restrict__ part_o,
     float* __restrict__ part_ml, int splits, int use_pdl) {
-  constexpr int VEC = D / 32, NG = kAttnThreads / D, HALF = D / 2, MAXH = (kAttnMaxGroup + NG - 1) / NG;
-  __shared__ float s_q[kAttnMaxGroup * D];
-  __shared__ float s_s[kAttnMaxGroup][kAttnSub];
-  __shared__ float s_alpha[kAttnMaxGroup], s_mrun[kAttnMaxGroup], s_lrun[kAttnMaxGroup];
+  __shared__ AttnSmem<D> sm;
   if (use_pdl) {
     pdl_launch_dependents();
     pdl_wait_prior();
   }
-  const int pos = min(*pos_ptr, max_ctx - 1), ctx = pos + 1;
+  const int pos = min(*pos_ptr, max_ctx - 1);
   const int split = blockIdx.x, kvh = blockIdx.y;
-  const int c0 = split * chunk;
-  if (c0 >= ctx) return;
-  const int c1 = min(c0 + chunk, ctx);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float scale = 1.0f / sqrtf((float)D);
-  // rotated queries of the group
-  for (int idx = tid; idx < group * D; idx += kAttnThreads) {
-    const int h = idx / D, d = idx - h * D;
-    const float* qr = q + (size_t)(kvh * group + h) * D;
-    const int dd = d < HALF ? d : d - HALF;
-    const float sn = sin_t[pos * HALF + dd], cs = cos_t[pos * HALF + dd];
-    const float x0 = qr[dd], x1 = qr[dd + HALF];
-    s_q[idx] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
-  }
-  if (tid < kAttnMaxGroup) {
-    s_mrun[tid] = -3.402823466e+38f;
-    s_lrun[tid] = 0.0f;
-  }
-  float* kc = cache_k + (size_t)kvh * max_ctx * D;
-  float* vc = cache_v + (size_t)kvh * max_ctx * D;
-  const float* kn = k_new + kvh * D;
-  const float* vn = v_new + kvh * D;
-  const int pd = tid % D, pg = tid / D;  // the output element / head slot this thread accumulates
-  float o_acc[MAXH];
-#pragma unroll
-  for (int i = 0; i < MAXH; ++i) o_acc[i] = 0.0f;
-  __syncthreads();
-
-  for (int b0 = c0; b0 < c1; b0 += kAttnSub) {
-    // ---- scores: warp w takes positions b0 + w + 8 j
-    constexpr int PER_WARP = kAttnSub / (kAttnThreads / 32);
-    float kv[PER_WARP][VEC];
-#pragma unroll
-    for (int j = 0; j < PER_WARP; ++j) {
-      const int t = b0 + warp + j * (kAttnThreads / 32);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) kv[j][e] = 0.0f;
-      if (t < c1) {
-        if (t == pos) {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const int d = lane * VEC + e, dd = d < HALF ? d : d - HALF;
-            const float sn = sin_t[pos * HALF + dd], cs = cos_t[pos * HALF + dd];
-            const float x0 = kn[dd], x1 = kn[dd + HALF];
-            kv[j][e] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
-            kc[(size_t)pos * D + d] = kv[j][e];
-          }
-        } else if constexpr (VEC == 4) {
-          const float4 v4 = *reinterpret_cast<const float4*>(kc + (size_t)t * D + lane * 4);
-          kv[j][0] = v4.x, kv[j][1] = v4.y, kv[j][2] = v4.z, kv[j][3] = v4.w;
-        } else {
-          const float2 v2 = *reinterpret_cast<const float2*>(kc + (size_t)t * D + lane * 2);
-          kv[j][0] = v2.x, kv[j][1] = v2.y;
-        }
-      }
-    }
-    for (int h = 0; h < group; ++h) {
-      float qv[VEC];
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) qv[e] = s_q[h * D + lane * VEC + e];
-#pragma unroll
-      for (int j = 0; j < PER_WARP; ++j) {
-        float acc = 0.0f;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) acc = fmaf(qv[e], kv[j][e], acc);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        const int tl = warp + j * (kAttnThreads / 32);
-        if (lane == 0) s_s[h][tl] = (b0 + tl < c1) ? acc * scale : -3.402823466e+38f;
-      }
-    }
-    __syncthreads();
-    // ---- online softmax bookkeeping: warp h owns head h
-    if (warp < group) {
-      const float sc = s_s[warp][lane];
-      float mx = sc;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_old = s_mrun[warp], m_new = fmaxf(m_old, mx);
-      const float p = (b0 + lane < c1) ? expf(sc - m_new) : 0.0f;
-      float sum = p;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      s_s[warp][lane] = p;
-      if (lane == 0) {
-        const float alpha = expf(m_old - m_new);  // 0 on the first block (m_old = -FLT_MAX)
-        s_alpha[warp] = alpha;
-        s_mrun[warp] = m_new;
-        s_lrun[warp] = s_lrun[warp] * alpha + sum;
-      }
-    }
-    __syncthreads();
-    // ---- P.V: thread (pd, pg) accumulates element pd of heads pg, pg + NG, ...
-    {
-      const int nt = min(kAttnSub, c1 - b0);
-      float vv[kAttnSub];
-#pragma unroll
-      for (int t = 0; t < kAttnSub; ++t) {
-        vv[t] = 0.0f;
-        if (t < nt) {
-          if (b0 + t == pos) {
-            vv[t] = vn[pd];
-            if (pg == 0) vc[(size_t)pos * D + pd] = vv[t];
-          } else {
-            vv[t] = vc[(size_t)(b0 + t) * D + pd];
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < MAXH; ++i) {
-        const int h = pg + i * NG;
-        if (h < group) {
-          float acc = o_acc[i] * s_alpha[h];
-#pragma unroll
-          for (int t = 0; t < kAttnSub; ++t) acc = fmaf(s_s[h][t], vv[t], acc);
-          o_acc[i] = acc;
-        }
-      }
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int i = 0; i < MAXH; ++i) {
-    const int h = pg + i * NG;
-    if (h < group) part_o[((size_t)(kvh * group + h) * splits + split) * D + pd] = o_acc[i];
-  }
-  if (tid < group) {
-    float* ml = part_ml + ((size_t)(kvh * group + tid) * splits + split) * 2;
-    ml[0] = s_mrun[tid];
-    ml[1] = s_lrun[tid];
-  }
+  if (split * chunk > pos) return;
+  attn_partial_body<D>(sm, threadIdx.x, [] { __syncthreads(); }, q + (size_t)kvh * group * D, k_new + kvh * D,
+                       v_new + kvh * D, sin_t, cos_t, pos, split * chunk, min((split + 1) * chunk, pos + 1), group,
+                       cache_k + (size_t)kvh * max_ctx * D, cache_v + (size_t)kvh * max_ctx * D,
+                       part_o + (size_t)kvh * group * splits * D, part_ml + (size_t)kvh * group * splits * 2, splits, split);
 }
 
 template __global__ void attn_decode_partial_kernel<64>(const float*, const float*, const float*, const float*, const float*,
@@ -279,13 +139,20 @@ template __global__ void attn_decode_partial_kernel<128>(const float*, const flo
                                                          float*, int, int);
 
 // logits[v] = sum_k x[k] * W[v,k], W fp16 [V, hidden] row-major, x fp32 (one row), fp32 accumulation.
-// One warp per output row, 16-byte loads; hidden a multiple of 8.
+// One warp per output row, 16-byte loads; hidden a multiple of 8.  Each CTA also leaves the largest
+// logit it produced and its index in best[blockIdx] (lowest index on ties), so that greedy sampling
+// is a reduction over gridDim.x pairs instead of a pass over the vocabulary.
 __global__ void __launch_bounds__(256) lm_head_f16_kernel(const float* __restrict__ x, const __half* __restrict__ w,
-                                                          int hidden, int vocab, float* __restrict__ logits) {
+                                                          int hidden, int vocab, float* __restrict__ logits,
+                                                          float2* __restrict__ best) {
   extern __shared__ float s_x[];
+  __shared__ float s_bv[8];
+  __shared__ int s_bi[8];
   for (int k = threadIdx.x; k < hidden; k += blockDim.x) s_x[k] = x[k];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  float bv = -3.402823466e+38f;
+  int bi = 0x7fffffff;
   for (int v = blockIdx.x * wpb + warp; v < vocab; v += gridDim.x * wpb) {
     const uint4* row = reinterpret_cast<const uint4*>(w + (size_t)v * hidden);
     float acc = 0.0f;
@@ -303,51 +170,59 @@ __global__ void __launch_bounds__(256) lm_head_f16_kernel(const float* __restric
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) logits[v] = acc;
+    if (acc > bv) {  // rows come in increasing order within a warp, so a strict test keeps the lowest index
+      bv = acc;
+      bi = v;
+    }
+  }
+  if (best == nullptr) return;
+  if (lane == 0) {
+    s_bv[warp] = bv;
+    s_bi[warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < wpb; ++i)
+      if (s_bv[i] > bv || (s_bv[i] == bv && s_bi[i] < bi)) {
+        bv = s_bv[i];
+        bi = s_bi[i];
+      }
+    best[blockIdx.x] = make_float2(bv, __int_as_float(bi));
   }
 }
 
-// Greedy sampling: index of the largest logit, lowest index on ties (AutoLLM.hpp:70-105 scans in
-// order with a strict comparison).  One CTA.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out) {
-  __shared__ float s_v[32];
-  __shared__ int s_i[32];
-  float best = -3.402823466e+38f;
+// Greedy sampling from the per-CTA candidates of lm_head_f16_kernel, then the bookkeeping of a
+// step (greedy = AutoLLM.hpp:70-105 of the reference project: scan in order, strict comparison, so the
+// lowest index wins ties): the sampled token becomes the next input and is appended to the history (entry p = the
+// token sampled after position p); the position advances.  One warp.
+__global__ void sample_advance_kernel(const float2* __restrict__ best, int count, int* __restrict__ pos,
+                                      int* __restrict__ token, int* __restrict__ next, int* __restrict__ history,
+                                      int max_hist) {
+  float bv = -3.402823466e+38f;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = logits[i];
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
+  for (int i = threadIdx.x; i < count; i += 32) {
+    const float2 c = best[i];
+    const int ci = __float_as_int(c.y);
+    if (c.x > bv || (c.x == bv && ci < bi)) {
+      bv = c.x;
+      bi = ci;
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
       bi = oi;
     }
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) {
-    s_v[warp] = best;
-    s_i[warp] = bi;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    best = lane < (blockDim.x >> 5) ? s_v[lane] : -3.402823466e+38f;
-    bi = lane < (blockDim.x >> 5) ? s_i[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
-      }
-    }
-    if (lane == 0) *out = bi;
+  if (threadIdx.x == 0) {
+    const int p = *pos;
+    *next = bi;
+    *token = bi;
+    if (p < max_hist) history[p] = bi;
+    *pos = p + 1;
   }
 }
 

@@ -22,7 +22,18 @@ class Qwen2Config(C.Structure):
 QWEN2_1P5B = dict(layers=28, hidden=1536, q_heads=12, kv_heads=2, head_dim=128, inter=8960, vocab=151936,
                   max_ctx=1024, eps=1e-6, rope_theta=1000000.0)
 
+DECODE_AUTO, DECODE_GRAPH, DECODE_PERSISTENT = 0, 1, 2
 _bound = False
+
+
+def plan_check(cfg, nctas):
+    """Host-only consistency check of the persistent kernel's work plan: (max chunks per CTA and
+    layer, max partial-sum slots per row, chunks per layer over all CTAs)."""
+    L = _bind()
+    a, b, c = C.c_int(), C.c_int(), C.c_int()
+    B._check(L.mllmb200_qwen2_plan_check(C.byref(Qwen2Config(**cfg)), nctas, C.byref(a), C.byref(b), C.byref(c)),
+             "qwen2_plan_check")
+    return a.value, b.value, c.value
 
 
 def _bind():
@@ -40,6 +51,8 @@ def _bind():
     L.mllmb200_qwen2_set_tables.argtypes = [vp, vp, vp]
     L.mllmb200_qwen2_prefill.argtypes = [vp, vp, ci]
     L.mllmb200_qwen2_decode.argtypes = [vp, ci]
+    L.mllmb200_qwen2_decode_ex.argtypes = [vp, ci, ci]
+    L.mllmb200_qwen2_plan_check.argtypes = [C.POINTER(Qwen2Config), ci, C.POINTER(ci), C.POINTER(ci), C.POINTER(ci)]
     L.mllmb200_qwen2_read.argtypes = [vp, ci, ci, vp, vp, vp]
     L.mllmb200_qwen2_stream.argtypes = [vp]
     L.mllmb200_qwen2_stream.restype = vp
@@ -107,8 +120,9 @@ class Qwen2Decoder:
         self.prompt_len = int(tokens_dev.numel())
         B._check(self._L.mllmb200_qwen2_prefill(self._h, tokens_dev.data_ptr(), self.prompt_len), "qwen2_prefill")
 
-    def decode(self, steps):
-        B._check(self._L.mllmb200_qwen2_decode(self._h, steps), "qwen2_decode")
+    def decode(self, steps, mode=0):
+        """mode: DECODE_AUTO, DECODE_GRAPH (one graph replay per step) or DECODE_PERSISTENT (one launch)."""
+        B._check(self._L.mllmb200_qwen2_decode_ex(self._h, steps, mode), "qwen2_decode")
 
     def read(self, first, count, want_logits=False):
         toks = np.zeros(max(count, 1), np.int32)

@@ -93,6 +93,21 @@ def test_config_struct_matches_header():
     assert "float eps, rope_theta;" in hdr
 
 
+@pytest.mark.parametrize("nctas", [1, 7, 132, 148, 160])
+def test_persistent_plan_covers_every_cell_once(nctas):
+    """The static work plan of the persistent decode kernel (host code): the library's own checker
+    walks every chunk of every CTA; here also the chunk totals against the cell counts."""
+    import mllm_b200 as mb
+    for cfg in (SMALL, WIDE, dict(mb.QWEN2_1P5B)):
+        max_chunks, max_slots, total = mb.plan_check(cfg, nctas)
+        H, QD, KD, I = cfg["hidden"], cfg["q_heads"] * cfg["head_dim"], cfg["kv_heads"] * cfg["head_dim"], cfg["inter"]
+        cells = ((QD + 2 * KD) * H + H * QD + 2 * I * H + H * I) // (32 * 32)
+        assert 1 <= max_slots <= 8 and max_chunks >= 1
+        assert cells / 16 <= total <= cells  # chunks hold 1..16 cells
+    with pytest.raises(mb.MllmB200Error):
+        mb.plan_check(dict(SMALL, hidden=250), 148)
+
+
 # ------------------------------------------------------------------ GPU
 def _gpu_decoder(cfg, w, raw):
     import torch
@@ -109,9 +124,10 @@ def _gpu_decoder(cfg, w, raw):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", [1, 2], ids=["graph", "persistent"])
 @pytest.mark.parametrize("cfg,seed,prompt_len,steps", [(SMALL, 11, 3, 20), (SMALL, 12, 9, 12), (SMALL, 13, 40, 24),
                                                        (WIDE, 14, 1, 10), (WIDE, 15, 33, 16)])
-def test_decoder_matches_oracle(cfg, seed, prompt_len, steps):
+def test_decoder_matches_oracle(cfg, seed, prompt_len, steps, mode):
     import torch
     import mllm_b200 as mb
     assert torch.cuda.is_available()
@@ -148,13 +164,13 @@ def test_decoder_matches_oracle(cfg, seed, prompt_len, steps):
     for i in range(steps):
         if got[-1] != ref_toks[i]:
             break
-        dec.decode(1)
+        dec.decode(1, mode)
         t, pos, lg = dec.read(prompt_len + i, 1, want_logits=True)
         assert pos == prompt_len + i + 1
         errs.append(rel_err(lg, i + 1))
         assert errs[-1] <= bars[i + 1], f"logits of step {i}: {errs[-1]:.3e} > {bars[i + 1]:.3e}"
         got.append(int(t[0]))
-    print(f"decoder parity hidden={cfg['hidden']} prompt={prompt_len}: max rel logit err {max(errs):.3e}, "
+    print(f"decoder parity mode={mode} hidden={cfg['hidden']} prompt={prompt_len}: max rel logit err {max(errs):.3e}, "
           f"bar {bars[0]:.1e}..{bars[len(errs) - 1]:.1e}, {len(got)} tokens")
     for i, (a, b) in enumerate(zip(got, ref_toks)):
         if a != b:
@@ -166,7 +182,7 @@ def test_decoder_matches_oracle(cfg, seed, prompt_len, steps):
         assert len(got) == steps + 1
     # a fresh prefill + all steps in one call (graph replays back to back) gives the same tokens
     dec.prefill(prompt)
-    dec.decode(len(got) - 1)
+    dec.decode(len(got) - 1, mode)
     again = dec.generated(len(got) - 1)
     assert again.tolist() == got
     mb.check_device_status()
