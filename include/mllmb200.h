@@ -210,6 +210,12 @@ MLLMB200_API int mllmb200_qwen2_plan_check(const mllmb200_qwen2_config* cfg, int
  * position p), the number of tokens in the cache, and the last logits [vocab]; NULLs are skipped. */
 MLLMB200_API int mllmb200_qwen2_read(void* handle, int first, int count, int* tokens_out, int* pos_out,
                                      float* logits_out);
+/* Per-phase cycle counters of the persistent kernel on/off (off by default; they cost a few percent). */
+MLLMB200_API int mllmb200_qwen2_set_profiling(void* handle, int on);
+/* Profiling of the persistent kernel: clock cycles that thread 0 of every CTA spent in each phase
+ * (work and barrier waits separately) during the last launch, out[nctas][stamps]; out may be NULL
+ * to query the two sizes.  Synchronizes the stream. */
+MLLMB200_API int mllmb200_qwen2_phase_cycles(void* handle, long long* out, int capacity, int* nctas, int* stamps);
 /* The decoder's CUDA stream (cudaStream_t), for event timing. */
 MLLMB200_API void* mllmb200_qwen2_stream(void* handle);
 

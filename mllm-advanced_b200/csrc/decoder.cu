@@ -25,6 +25,7 @@ void persistent_prepare(Decoder* d);
 bool persistent_usable(Decoder* d);
 cudaError_t persistent_decode(Decoder* d, int steps);
 void persistent_destroy(Decoder* d);
+int persistent_phase_cycles(Decoder* d, long long* out, int capacity, int* nctas, int* stamps);
 // kernels defined in the other translation units
 __global__ void add_rmsnorm_quant_kernel(const float*, const float*, const float*, float, int, float*, float*, uint8_t*,
                                          float2*, int);

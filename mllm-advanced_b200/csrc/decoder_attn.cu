@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_kernel(
   const int split = blockIdx.x, kvh = blockIdx.y;
   if (split * chunk > pos) return;
   attn_partial_body<D>(sm, threadIdx.x, [] { __syncthreads(); }, q + (size_t)kvh * group * D, k_new + kvh * D,
-                       v_new + kvh * D, sin_t, cos_t, pos, split * chunk, min((split + 1) * chunk, pos + 1), group,
+                       v_new + kvh * D, sin_t + (size_t)pos * (D / 2), cos_t + (size_t)pos * (D / 2), pos, split * chunk, min((split + 1) * chunk, pos + 1), group,
                        cache_k + (size_t)kvh * max_ctx * D, cache_v + (size_t)kvh * max_ctx * D,
                        part_o + (size_t)kvh * group * splits * D, part_ml + (size_t)kvh * group * splits * 2, splits, split);
 }

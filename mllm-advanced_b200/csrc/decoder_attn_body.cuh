@@ -9,6 +9,7 @@
 // append pass is needed.  Follows the reference project's attention
 // (mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:127-150; RoPE mllm/Backends/Arm/Kernels/rope.cpp:20-87).
 //
+// sin_row / cos_row: the D/2 rotation sines and cosines of position `pos`.
 // Threads tid < 256 work; the caller may run more threads, all of which must call the body (they
 // only take part in `sync`, which must synchronize every calling thread).
 // part_o: [group][splits][D], part_ml: [group][splits][2] = {max, sum}, both for this KV head.
@@ -30,21 +31,67 @@ struct AttnSmem {
 
 template <int D, class Sync>
 __device__ __forceinline__ void attn_partial_body(AttnSmem<D>& sm, int tid, Sync sync, const float* q, const float* kn,
-                                                  const float* vn, const float* __restrict__ sin_t,
-                                                  const float* __restrict__ cos_t, int pos, int c0, int c1, int group,
+                                                  const float* vn, const float* __restrict__ sin_row,
+                                                  const float* __restrict__ cos_row, int pos, int c0, int c1, int group,
                                                   float* kc, float* vc, float* part_o, float* part_ml, int splits,
                                                   int split) {
   constexpr int VEC = D / 32, NG = kAttnThreads / D, HALF = D / 2, MAXH = (kAttnMaxGroup + NG - 1) / NG;
   const bool active = tid < kAttnThreads;
   const int warp = tid >> 5, lane = tid & 31;
   const float scale = 1.0f / sqrtf((float)D);
+  constexpr int PER_WARP = kAttnSub / (kAttnThreads / 32);
+  const int pd = tid % D, pg = tid / D;  // the output element / head slot this thread accumulates
+  float kv[PER_WARP][VEC];  // this warp's key rows of the block (lane = VEC consecutive elements)
+  float vv[kAttnSub];       // element pd of the block's value rows
+  // All cache loads of a block are issued together, before anything that depends on them: they
+  // are L2 round trips (the rows may have been written by another SM earlier in the same launch).
+  auto load_block = [&](int b0) {
+#pragma unroll
+    for (int j = 0; j < PER_WARP; ++j) {
+      const int t = b0 + warp + j * (kAttnThreads / 32);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) kv[j][e] = 0.0f;
+      if (t < c1) {
+        if (t == pos) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const int d = lane * VEC + e, dd = d < HALF ? d : d - HALF;
+            const float sn = sin_row[dd], cs = cos_row[dd];
+            const float x0 = kn[dd], x1 = kn[dd + HALF];
+            kv[j][e] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
+            kc[(size_t)pos * D + d] = kv[j][e];
+          }
+        } else if constexpr (VEC == 4) {
+          const float4 v4 = __ldcg(reinterpret_cast<const float4*>(kc + (size_t)t * D + lane * 4));
+          kv[j][0] = v4.x, kv[j][1] = v4.y, kv[j][2] = v4.z, kv[j][3] = v4.w;
+        } else {
+          const float2 v2 = __ldcg(reinterpret_cast<const float2*>(kc + (size_t)t * D + lane * 2));
+          kv[j][0] = v2.x, kv[j][1] = v2.y;
+        }
+      }
+    }
+    const int nt = min(kAttnSub, c1 - b0);
+#pragma unroll
+    for (int t = 0; t < kAttnSub; ++t) {
+      vv[t] = 0.0f;
+      if (t < nt) {
+        if (b0 + t == pos) {
+          vv[t] = vn[pd];
+          if (pg == 0) vc[(size_t)pos * D + pd] = vv[t];
+        } else {
+          vv[t] = __ldcg(vc + (size_t)(b0 + t) * D + pd);
+        }
+      }
+    }
+  };
+  if (active) load_block(c0);
   // rotated queries of the group
   if (active) {
     for (int idx = tid; idx < group * D; idx += kAttnThreads) {
       const int h = idx / D, d = idx - h * D;
       const float* qr = q + (size_t)h * D;
       const int dd = d < HALF ? d : d - HALF;
-      const float sn = sin_t[pos * HALF + dd], cs = cos_t[pos * HALF + dd];
+      const float sn = sin_row[dd], cs = cos_row[dd];
       const float x0 = qr[dd], x1 = qr[dd + HALF];
       sm.q[idx] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
     }
@@ -53,42 +100,14 @@ __device__ __forceinline__ void attn_partial_body(AttnSmem<D>& sm, int tid, Sync
       sm.lrun[tid] = 0.0f;
     }
   }
-  const int pd = tid % D, pg = tid / D;  // the output element / head slot this thread accumulates
   float o_acc[MAXH];
 #pragma unroll
   for (int i = 0; i < MAXH; ++i) o_acc[i] = 0.0f;
   sync();
 
   for (int b0 = c0; b0 < c1; b0 += kAttnSub) {
-    // ---- scores: warp w takes positions b0 + w + 8 j
+    // ---- scores: warp w holds positions b0 + w + 8 j
     if (active) {
-      constexpr int PER_WARP = kAttnSub / (kAttnThreads / 32);
-      float kv[PER_WARP][VEC];
-#pragma unroll
-      for (int j = 0; j < PER_WARP; ++j) {
-        const int t = b0 + warp + j * (kAttnThreads / 32);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) kv[j][e] = 0.0f;
-        if (t < c1) {
-          if (t == pos) {
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-              const int d = lane * VEC + e, dd = d < HALF ? d : d - HALF;
-              const float sn = sin_t[pos * HALF + dd], cs = cos_t[pos * HALF + dd];
-              const float x0 = kn[dd], x1 = kn[dd + HALF];
-              kv[j][e] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
-              kc[(size_t)pos * D + d] = kv[j][e];
-            }
-          } else if constexpr (VEC == 4) {
-            // L2 loads: cache rows may have been written by another SM earlier in the same launch
-            const float4 v4 = __ldcg(reinterpret_cast<const float4*>(kc + (size_t)t * D + lane * 4));
-            kv[j][0] = v4.x, kv[j][1] = v4.y, kv[j][2] = v4.z, kv[j][3] = v4.w;
-          } else {
-            const float2 v2 = __ldcg(reinterpret_cast<const float2*>(kc + (size_t)t * D + lane * 2));
-            kv[j][0] = v2.x, kv[j][1] = v2.y;
-          }
-        }
-      }
       for (int h = 0; h < group; ++h) {
         float qv[VEC];
 #pragma unroll
@@ -128,20 +147,6 @@ __device__ __forceinline__ void attn_partial_body(AttnSmem<D>& sm, int tid, Sync
     sync();
     // ---- P.V: thread (pd, pg) accumulates element pd of heads pg, pg + NG, ...
     if (active) {
-      const int nt = min(kAttnSub, c1 - b0);
-      float vv[kAttnSub];
-#pragma unroll
-      for (int t = 0; t < kAttnSub; ++t) {
-        vv[t] = 0.0f;
-        if (t < nt) {
-          if (b0 + t == pos) {
-            vv[t] = vn[pd];
-            if (pg == 0) vc[(size_t)pos * D + pd] = vv[t];
-          } else {
-            vv[t] = __ldcg(vc + (size_t)(b0 + t) * D + pd);
-          }
-        }
-      }
 #pragma unroll
       for (int i = 0; i < MAXH; ++i) {
         const int h = pg + i * NG;
@@ -154,6 +159,7 @@ __device__ __forceinline__ void attn_partial_body(AttnSmem<D>& sm, int tid, Sync
       }
     }
     sync();
+    if (active && b0 + kAttnSub < c1) load_block(b0 + kAttnSub);
   }
   if (active) {
 #pragma unroll

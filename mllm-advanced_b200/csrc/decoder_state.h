@@ -42,6 +42,7 @@ struct Decoder {
   cudaStream_t stream = nullptr;
   cudaGraphExec_t graph = nullptr;
   PersistentState* persist = nullptr;  // persistent decode kernel state (built on first use)
+  int profile = 0;                     // persistent kernel: record per-phase cycle counts
   int host_pos = 0;                    // tokens in the cache, tracked on the host to bound requests
   std::vector<void*> owned;
   int last_error = 0;

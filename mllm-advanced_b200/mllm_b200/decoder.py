@@ -54,6 +54,8 @@ def _bind():
     L.mllmb200_qwen2_decode_ex.argtypes = [vp, ci, ci]
     L.mllmb200_qwen2_plan_check.argtypes = [C.POINTER(Qwen2Config), ci, C.POINTER(ci), C.POINTER(ci), C.POINTER(ci)]
     L.mllmb200_qwen2_read.argtypes = [vp, ci, ci, vp, vp, vp]
+    L.mllmb200_qwen2_set_profiling.argtypes = [vp, ci]
+    L.mllmb200_qwen2_phase_cycles.argtypes = [vp, vp, ci, C.POINTER(ci), C.POINTER(ci)]
     L.mllmb200_qwen2_stream.argtypes = [vp]
     L.mllmb200_qwen2_stream.restype = vp
     _bound = True
@@ -135,6 +137,18 @@ class Qwen2Decoder:
     def generated(self, steps):
         """Tokens sampled after the prompt and after each of `steps` decode steps."""
         return self.read(self.prompt_len - 1, steps + 1)[0]
+
+    def set_profiling(self, on):
+        B._check(self._L.mllmb200_qwen2_set_profiling(self._h, int(bool(on))), "qwen2_set_profiling")
+
+    def phase_cycles(self):
+        """[nctas, stamps] clock cycles per phase of the last persistent launch."""
+        n, k = C.c_int(), C.c_int()
+        B._check(self._L.mllmb200_qwen2_phase_cycles(self._h, None, 0, C.byref(n), C.byref(k)), "qwen2_phase_cycles")
+        out = np.zeros((n.value, k.value), np.int64)
+        B._check(self._L.mllmb200_qwen2_phase_cycles(self._h, out.ctypes.data, out.size, C.byref(n), C.byref(k)),
+                 "qwen2_phase_cycles")
+        return out
 
     def stream(self):
         import torch
