@@ -563,7 +563,7 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
     """BASELINE config 2: the whole 28-layer decoder with random-init W4A32 weights, batch 1,
     512-token prompt of uniform random ids, 128 greedy decode steps, fp32 KV cache, fp16 lm_head."""
     cfg = dict(mb.QWEN2_1P5B, max_ctx=1024)
-    prompt_len, steps = 512, 128
+    prompt_len, steps = args.decoder_prompt, args.decoder_steps  # BASELINE config 2: 512 and 128
     dec = mb.Qwen2Decoder(cfg)
     for l, lw in enumerate(layers):
         for (name, _, _, _), w in zip(LINEARS, lw):
@@ -577,12 +577,14 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
     host_prompt = np.random.default_rng(7).integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     ds = dec.stream()
     modes = {"persistent": mb.DECODE_PERSISTENT, "graph": mb.DECODE_GRAPH}
+    if args.decoder_mode != "both":
+        modes = {args.decoder_mode: modes[args.decoder_mode]}
     res = {}
     toks_by_mode = {}
     for mname, mode in modes.items():
         try:
             dec.prefill(host_prompt)
-            dec.decode(4, mode)  # first call builds the plan / captures the step graph
+            dec.decode(min(4, steps), mode)  # first call builds the plan / captures the step graph
             ds.synchronize()
             mb.check_device_status(ds)
         except Exception as ex:
@@ -640,8 +642,9 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
            "prefill_ms": pf_ms, "prefill_tokens_per_s": prompt_len / (pf_ms * 1e-3),
            "decode_ms_per_token": dc_ms / steps, "decode_tokens_per_s": steps / (dc_ms * 1e-3),
            "e2e_wall_s": wall_s, "e2e_decode_tokens_per_s": steps / wall_s,
-           "e2e_note": "host prompt -> H2D -> prefill -> 128 steps -> D2H of the sampled tokens, host wall clock; "
-                       "tokens/s counts the 128 generated tokens over the whole wall time (prefill included)",
+           "prompt_len": prompt_len, "steps": steps,
+           "e2e_note": "host prompt -> H2D -> prefill -> greedy steps -> D2H of the sampled tokens, host wall clock; "
+                       "tokens/s counts the generated tokens over the whole wall time (prefill included)",
            "bytes_per_decode_step": step_b,
            "decode_roofline": {"bound": "hbm", "achieved": step_b / (dc_ms / steps * 1e-3) / 1e9, "peak": hbm_peak,
                                "unit": "GB/s", "frac": step_b / (dc_ms / steps * 1e-3) / 1e9 / hbm_peak,
@@ -649,7 +652,7 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
            "decode_mode": best_mode,
            "decode_ms_per_token_by_mode": {m: (res[m]["decode_ms"] / steps if "error" not in res[m] else res[m]) for m in res},
            "modes_agree": (len(good) < 2 or toks_by_mode[good[0]] == toks_by_mode[good[1]]),
-           "launches_per_decode_step": {"persistent": "1 cooperative launch for all 128 steps", "graph": 1 + LAYERS * 9 + 3},
+           "launches_per_decode_step": {"persistent": "1 cooperative launch for all steps", "graph": 1 + LAYERS * 9 + 3},
            "distinct_tokens": int(len(set(toks.tolist())))}
     if "persistent" in good:
         out["persistent_phase_cycles"] = phase_prof
@@ -712,6 +715,9 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
     ap.add_argument("--per-op", action="store_true", help="headline step with one call per linear instead of grouped calls")
     ap.add_argument("--decoder-only", action="store_true", help="only the whole-model prefill + decode section")
+    ap.add_argument("--decoder-prompt", type=int, default=512, help="prompt length of the decoder section")
+    ap.add_argument("--decoder-steps", type=int, default=128, help="greedy steps of the decoder section (small values for ncu)")
+    ap.add_argument("--decoder-mode", default="both", choices=["both", "persistent", "graph"])
     ap.add_argument("--decoder-reps", type=int, default=3, help="timed repetitions of prefill + 128 steps")
     ap.add_argument("--no-decoder", action="store_true", help="skip the whole-model prefill + decode section")
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
