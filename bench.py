@@ -290,9 +290,10 @@ def run_gpu(args):
         lw = [make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS]
         ws = torch.empty(mb.workspace_size(PREFILL_M, 8960), dtype=torch.uint8, device="cuda")
         xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
+        kern = mb.KERNEL_TC_F16 if args.prefill_f16 else mb.KERNEL_AUTO
         for _ in range(max(1, args.steps)):
             for w in lw:
-                mb.linear_forward(xp[w.k], w, workspace=ws)
+                mb.linear_forward(xp[w.k], w, workspace=ws, kernel=kern)
         torch.cuda.synchronize()
         mb.check_device_status()
         print(json.dumps({"prefill_only": True, "M": PREFILL_M, "passes": max(1, args.steps)}))
@@ -469,6 +470,34 @@ def run_gpu(args):
                            "kernel": kern, "unit": "TOP/s (2*M*N*K int8 ops)",
                            "frac_of_bf16_peak": flops / (ms_pf * 1e-3) / 1e12 / tensor_peak, "peak_kind": f"of {peak_kind}"}
         mb.check_device_status()
+
+        # the same prefill pass with the fp16 tensor-core path (exact fp16 operands, fp32 accumulation over
+        # all of K in tensor memory; same 1e-3 * rms bound): kernel 4 everywhere, and kernel 5 = the "fastest"
+        # policy (fp16 path where it clearly wins - gate/up at this M - and the default int8 path elsewhere)
+        for key, kern_id, label in (("prefill_f16", mb.KERNEL_TC_F16, "tcgen05 kind::f16 on every linear (kernel 4)"),
+                                    ("prefill_fastest", mb.KERNEL_FASTEST, "fastest policy (kernel 5): kind::f16 for gate/up, kind::i8 elsewhere")):
+            try:
+                def pf_pass(kern_id=kern_id):
+                    for lw in layers[:n_pf_layers]:
+                        for w in lw:
+                            mb.linear_forward(xp[w.k], w, out=yp[w.n], workspace=ws, stream=stream, kernel=kern_id)
+                with torch.cuda.stream(stream):
+                    pf_pass()
+                stream.synchronize()
+                with torch.cuda.stream(stream):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    for _ in range(3):
+                        pf_pass()
+                    e1.record(stream)
+                stream.synchronize()
+                ms_v = e0.elapsed_time(e1) / 3
+                line[key] = {"M": PREFILL_M, "layers": n_pf_layers, "ms": ms_v, "tflops": flops / (ms_v * 1e-3) / 1e12,
+                             "kernel": label, "unit": "TOP/s (2*M*N*K)",
+                             "frac_of_bf16_peak": flops / (ms_v * 1e-3) / 1e12 / tensor_peak, "peak_kind": f"of {peak_kind}"}
+                mb.check_device_status()
+            except Exception as ex:
+                line[key] = {"error": str(ex)[:160]}
 
         # e2e: the same step with HOST buffers (pinned), through the C ABI, one graph per step, and a host
         # synchronize after every step because the host reads y.  Two ways to move the bytes:
@@ -723,6 +752,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run one decoder layer's seven linears at M=512 once and exit (small target for ncu)")
+    ap.add_argument("--prefill-f16", action="store_true", help="with --prefill-only: use the fp16 tensor-core path (kernel 4)")
     ap.add_argument("--fast-prefill", action="store_true", help="time the prefill linears on 2 layers instead of 28")
     args = ap.parse_args()
     if args.impl == "reference":

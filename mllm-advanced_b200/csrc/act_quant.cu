@@ -245,6 +245,98 @@ __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* _
   for (int i = threadIdx.x; i < k; i += blockDim.x) dst[8 + i] = (uint8_t)(int8_t)act_quant_value(row[i], p);
 }
 
+// The same for the fp16 tensor-core path (gemm_tcf16.cu): the zero-point-corrected values a_q + a_off
+// are written as fp16 (exact) in 512-byte canonical K-major blocks [group][row / 8]: 4 chunks of 128 bytes, chunk c =
+// 8 rows x 16 bytes holding k = 8c + {0,4,1,5,2,6,3,7} - the order in which the weight side's
+// nibble unpack (two nibbles 16 bits apart per half2) produces its elements.
+constexpr int kF16RowsPerCta = 2;   // rows 2i and 2i+1 sit side by side in a block: 32-byte pieces
+constexpr int kF16WarpsPerRow = 16;
+__global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_quant_blocks_f16_kernel(
+    const float* __restrict__ x, int m_total, int k, int ldx, int num_groups, int m8_pad, uint8_t* __restrict__ blocks,
+    float2* __restrict__ hdr) {
+  __shared__ float s_mm[kF16RowsPerCta][kF16WarpsPerRow][2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = warp & (kF16RowsPerCta - 1), part = warp / kF16RowsPerCta;
+  const int m = blockIdx.x * kF16RowsPerCta + r;
+  const bool live = m < m_total;
+  const float* row = x + (size_t)(live ? m : 0) * ldx;
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  if (live) {
+    const int stride = 32 * kF16WarpsPerRow, first = part * 32 + lane;
+    if (vec) {
+      const float4* r4 = reinterpret_cast<const float4*>(row);
+      for (int i = first; i < (k >> 2); i += stride) {
+        const float4 v = r4[i];
+        mn = fminf(mn, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
+        mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+      }
+      for (int i = (k & ~3) + first; i < k; i += stride) {
+        mn = fminf(mn, row[i]);
+        mx = fmaxf(mx, row[i]);
+      }
+    } else {
+      for (int i = first; i < k; i += stride) {
+        mn = fminf(mn, row[i]);
+        mx = fmaxf(mx, row[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (lane == 0) {
+    s_mm[r][part][0] = mn;
+    s_mm[r][part][1] = mx;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < kF16WarpsPerRow; ++q) {
+    mn = fminf(mn, s_mm[r][q][0]);
+    mx = fmaxf(mx, s_mm[r][q][1]);
+  }
+  const ActQuantParams p = act_quant_params(mn, mx);
+  if (live && lane == 0 && part == 0) hdr[m] = make_float2(p.recip_scale, __int_as_float(-p.nzp));
+  // padding rows (m >= m_total, inside the padded tile) are written as zeros: the tensor core reads them
+  for (int g = part * 32 + lane; g < num_groups; g += 32 * kF16WarpsPerRow) {
+    const int k0 = g * kGroup;
+    uint8_t* blk = blocks + ((size_t)g * m8_pad + (m >> 3)) * 512 + (m & 7) * 16;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float f[8];
+      const int kc = k0 + c * 8;
+      if (live && vec && kc + 8 <= k) {
+        const float4 a = *reinterpret_cast<const float4*>(row + kc);
+        const float4 b = *reinterpret_cast<const float4*>(row + kc + 4);
+        f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = (live && kc + j < k) ? row[kc + j] : 0.0f;
+      }
+      __align__(16) __half h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // a_q + a_off (= a_q - zero point), |.| <= 255: exact in fp16, and exactly the factor the reference
+        // multiplies the weight with, so no zero-point correction term (and none of its cancellation) is left
+        const int q = (live && kc + j < k) ? act_quant_value(f[j], p) - p.nzp : 0;
+        const int pos = (j < 4) ? 2 * j : 2 * (j - 4) + 1;  // chunk order {0,4,1,5,2,6,3,7}
+        h[pos] = __int2half_rn(q);
+      }
+      *reinterpret_cast<uint4*>(blk + c * 128) = *reinterpret_cast<const uint4*>(h);
+    }
+  }
+}
+
+cudaError_t launch_act_quant_blocks_f16(const float* x, int m, int m_pad, int k, int ldx, uint8_t* blocks, float2* hdr,
+                                        cudaStream_t stream) {
+  const int num_groups = (k + kGroup - 1) / kGroup;
+  act_quant_blocks_f16_kernel<<<m_pad / kF16RowsPerCta, kF16RowsPerCta * kF16WarpsPerRow * 32, 0, stream>>>(
+      x, m, k, ldx, num_groups, m_pad / 8, blocks, hdr);
+  return cudaGetLastError();
+}
+
 // m8_pad == 0: 48-byte records; m8_pad > 0: canonical 256-byte blocks with m8_pad blocks per K-group.
 cudaError_t launch_act_quant_records(const float* x, int m, int k, int ldx, uint8_t* records, float2* hdr, int use_pdl,
                                      int m8_pad, cudaStream_t stream) {

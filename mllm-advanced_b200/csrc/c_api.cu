@@ -1,5 +1,6 @@
 // Device side of the C ABI (include/mllmb200.h): argument checks, kernel selection, launches.
 #include <cuda_runtime.h>
+#include <stddef.h>
 
 #include "../../include/mllmb200.h"
 #include "device_common.cuh"
@@ -7,7 +8,8 @@
 namespace mllmb200 {
 // repack.cu
 __global__ void repack_cells_kernel(const uint8_t*, const uint16_t*, int, int, int, int, int, uint8_t*);
-__global__ void repack_rowdata_kernel(const uint8_t*, const float*, int, int, int, int, uint32_t, float*, float*);
+__global__ void repack_rowdata_kernel(const uint8_t*, const float*, int, int, int, int, uint32_t, float*, float*,
+                                      unsigned int*);
 __global__ void unpack_cells_kernel(const uint8_t*, int, int, int, int, uint8_t*, uint16_t*);
 __global__ void unpack_bias_kernel(const float*, int, float*);
 // act_quant.cu
@@ -21,6 +23,13 @@ cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, i
 cudaError_t launch_w4a32_gemm_simt(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
 cudaError_t launch_w4a32_gemm_tc(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
 bool w4a32_gemm_tc_supported(int m, int k, int n);
+// gemm_tcf16.cu (+ its activation layout in act_quant.cu)
+bool w4a32_gemm_tcf16_supported(int m, int k, int n);
+bool w4a32_gemm_tcf16_preferred(int m, int k, int n);
+int w4a32_gemm_tcf16_m_pad(int m, int n);
+int w4a32_gemm_tcf16_m_pad_max(int m);
+cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
+cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t);
 
 static thread_local int t_last_cuda_error = 0;
 static int cuda_fail(cudaError_t e) {
@@ -34,7 +43,10 @@ static inline size_t ws_rec_bytes(int m, int k) {
   const size_t rec = (size_t)m * blob_num_blocks(k) * kActRecordBytes;
   // operand blocks are only written when the tcgen05 path can be chosen for this M
   const size_t blk = w4a32_gemm_tc_supported(m, k, 1) ? (size_t)w4a32_gemm_tc_m_pad(m) * blob_num_blocks(k) * 32 : 0;
-  return align_up(rec > blk ? rec : blk, 256);
+  // fp16 operand blocks of the fp16 tensor-core path (64 bytes per row and K-group, rows padded to its widest tile)
+  const size_t blk16 = w4a32_gemm_tcf16_supported(m, k, 1) ? (size_t)w4a32_gemm_tcf16_m_pad_max(m) * blob_num_blocks(k) * 64 : 0;
+  const size_t big = rec > blk ? rec : blk;
+  return align_up(big > blk16 ? big : blk16, 256);
 }
 }  // namespace mllmb200
 
@@ -75,7 +87,8 @@ int mllmb200_w4a32_repack_device(const void* blob_dev, int N, int K, int scale_m
   repack_rowdata_kernel<<<blocks2, 256, 0, st>>>(
       tiled + th.cells_off, has_bias ? reinterpret_cast<const float*>(blob + bh.bias_off) : nullptr, row_begin,
       row_count, (int)th.num_groups, (int)th.num_panels, (uint32_t)scale_mode,
-      reinterpret_cast<float*>(tiled + th.zsum_off), reinterpret_cast<float*>(tiled + th.bias_off));
+      reinterpret_cast<float*>(tiled + th.zsum_off), reinterpret_cast<float*>(tiled + th.bias_off),
+      reinterpret_cast<unsigned int*>(tiled + offsetof(TiledHeader, max_scale_bits)));
   if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
   return MLLMB200_OK;
 }
@@ -150,10 +163,20 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int use_pdl = (kernel >> 8) & 1;
   kernel &= 0xFF;
-  if (kernel < 0 || kernel > 3) return MLLMB200_INVALID_ARG;
+  if (kernel < 0 || kernel > 5) return MLLMB200_INVALID_ARG;
+  if (kernel == 5) kernel = w4a32_gemm_tcf16_preferred(M, K, N) ? 4 : 0;  // "fastest": fp16 path where it wins
   if (kernel == 0) kernel = mllmb200_w4a32_select_kernel(M, K, N);
   if (kernel == 1 && !w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   if (kernel == 3 && !w4a32_gemm_tc_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
+  if (kernel == 4) {  // fp16 tensor-core path: its own activation layout
+    if (!w4a32_gemm_tcf16_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
+    if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+    uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
+    float2* hdr16 = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
+    cudaError_t e16 = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N), K, ldx, blocks, hdr16, st);
+    if (e16 == cudaSuccess) e16 = launch_w4a32_gemm_tcf16(blocks, hdr16, tiled_dev, y_dev, M, K, N, ldy, st);
+    return e16 == cudaSuccess ? MLLMB200_OK : cuda_fail(e16);
+  }
   uint8_t* a_rec;
   float2* a_hdr;
   if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, use_pdl & 1, st, &a_rec, &a_hdr, kernel == 3)) return s;

@@ -1,0 +1,318 @@
+// tcgen05 W4A32 GEMM with fp16 operands and fp32 accumulation over ALL of K in tensor memory
+// (sm_100a) - the high-throughput prefill path.
+//
+// The int8 path (gemm_tc.cu) keeps the reference's per-group int32 sums and therefore pays one
+// conversion and one FMA per (row, column, K-group) on the CUDA cores, which bounds it far below
+// the tensor cores.  Here the group scale moves INTO the weight operand:
+//   A[n, k] = fp16( (u[n,k] - 8) * s[n, group(k)] * 2^E )      B[m, k] = fp16( a_q[m, k] + a_off[m] )
+// Both are exact: (u - 8) has at most 4 significant bits (and 8 is a power of two), a bf16/fp16
+// scale at most 11 together with it, |a_q + a_off| <= 255 fits fp16 (so the zero point needs no
+// correction term and nothing cancels); 2^E (one exponent per matrix, from the
+// largest |scale| recorded in the tile header by the repack) keeps the products in fp16's normal
+// range.  Every product a_q * A is then exact in fp32, and the only difference to the reference
+// (tests/Arm/KaiLinearTest.hpp:338-377 of the reference project) is the order and rounding of the
+// fp32 additions, which the GEMV and SIMT paths change as well.  Stated bound: max|diff| <=
+// 1e-3 * rms(y), the bar of every other path; measured ~1e-6 * rms.  Scales more than 2^25 below
+// the matrix maximum fall into fp16 subnormals and lose low bits (contribution < 2^-25 of the
+// largest group's).
+//
+//   y[m,n] = lhs_scale[m] * 2^-E * sum_k A[n,k] B[m,k] + bias[n]
+//
+// Tile: 128 weight rows (MMA M, tensor-memory lanes) x NT activation rows (MMA N, columns), one
+// accumulator for the whole K loop, one CTA per SM.  Warp roles (320 threads):
+//   warps 0-7  dequant: thread j (mod 128) expands weight row j of the tile, warps 0-3 the first and
+//              warps 4-7 the second K-group of a stage (16 bytes of nibbles -> 64 bytes of
+//              fp16 per K-group: mask / or / HSUB2 / HMUL2 on pairs of nibbles 16 bits apart) into the
+//              canonical K-major core-matrix layout; after the loop the same warps run the epilogue
+//              (warp w owns tensor-memory lanes 32 (w % 4).. and half of the columns)
+//   warp 8     producer: bulk copies (cp.async.bulk) of the raw weight cells and of the activation
+//              blocks, which act_quant_blocks_f16_kernel already wrote in operand layout
+//   warp 9     MMA issuer (one lane; two K=16 instructions per K-group) and tensor-memory owner
+// Stages of 2 K-groups: kStages (4-7) loaded-data stages {raw cells 4.5 KB, B operand NT*128 B} and as
+// many stages of the dequantized A operand (16 KB).  Every mbarrier wait is bounded.
+// Measured on the Qwen2-1.5B layer shapes at M = 512: gate/up (N = 8960, NT = 256, 140 CTAs) 22.5 us =
+// 0.63 PFLOP/s; the K loop is bound by the issuing thread (one K-tile = 4 MMAs + 2 waits + 1 commit
+// ~ 700-900 cycles) and, for N = 1536 (48 CTAs), by the unfilled GPU.
+#include <cuda_fp16.h>
+
+#include "device_common.cuh"
+#include "tcgen05_common.cuh"
+
+namespace mllmb200 {
+
+constexpr int kTfDequantWarps = 8;  // warps w and w + 4 share the weight rows 32 (w % 4)..; each takes one K-group of a stage
+constexpr int kTfThreads = (kTfDequantWarps + 2) * 32;
+constexpr int kTfTileRows = 128;
+constexpr int kTfGroupABytes = kTfTileRows * kGroup * 2;  // 8192: one K-group of the A operand
+
+struct TfParams {
+  const uint8_t* a_blocks;  // activations, [num_groups][m8_pad][512 bytes] fp16 canonical blocks
+  const float2* a_hdr;      // [m] {lhs_scale, a_off bits}
+  const uint8_t* tiled;     // weights (TiledHeader at offset 0)
+  float* y;
+  int m, n, k, ldy;
+  int num_groups, num_panels, m8_pad;
+  size_t zsum_off, bias_off;
+};
+
+template <int NT>
+struct TfSmem {
+  // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
+  // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
+  static constexpr int kGroups = 2;  // (4 groups per stage with 2 stages was measured slower at NT = 256: 25 vs 22 us)
+  // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
+  // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
+  // the number of tiles in flight, so both rings are as deep as shared memory allows.
+  static constexpr int kStages = NT >= 256 ? 4 : (NT >= 128 ? 6 : 7);
+  static constexpr int kAStages = kStages;  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages)
+  static constexpr int kRawBytes = 4 * kGroups * kCellBytes;
+  static constexpr int kBBytes = kGroups * NT * 64;
+  static constexpr int kStageBytes = kRawBytes + kBBytes;
+  static constexpr int kABytes = kGroups * kTfGroupABytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kHdrBytes = NT * 8;  // {lhs_scale, a_off} of the tile's activation rows
+  static constexpr int kAOffset = kBarBytes + kHdrBytes + kStages * kStageBytes;
+  static constexpr int kTotal = kAOffset + kAStages * kABytes + 1024;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const TfParams p) {
+  using S = TfSmem<NT>;
+  constexpr int kStages = S::kStages, kTfAStages = S::kAStages, kTfGroupsPerStage = S::kGroups;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  static_assert((2 * S::kStages + kTfAStages + 1) * 8 + 8 <= S::kBarBytes, "barrier area");
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [kStages]   loaded data arrived
+  uint64_t* mma_done = raw_full + kStages;                 // [kStages]   the MMAs that read a stage completed
+  uint64_t* a_full = mma_done + kStages;                   // [kTfAStages] dequantized operand written
+  uint64_t* acc_done = a_full + kTfAStages;                // [1]         all MMAs of the tile completed
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  float2* s_hdr = reinterpret_cast<float2*>(smem + S::kBarBytes);
+  uint8_t* stages = smem + S::kBarBytes + S::kHdrBytes;
+  uint8_t* a_stages = smem + S::kAOffset;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  const int panel0 = tile_n * 4, m0 = tile_m * NT;
+  const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
+  constexpr uint32_t kTmemCols = NT < 32 ? 32 : NT;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&mma_done[s], 1);
+    }
+    for (int s = 0; s < kTfAStages; ++s) mbar_init(&a_full[s], kTfDequantWarps);  // one arrival per dequant warp
+    mbar_init(acc_done, 1);
+    mbar_fence_init();
+  }
+  for (int i = tid; i < NT; i += kTfThreads) s_hdr[i] = (m0 + i < p.m) ? p.a_hdr[m0 + i] : make_float2(0.0f, 0.0f);
+  if (warp == kTfDequantWarps + 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(p.tiled);
+  // 2^E maps the largest |scale| of the matrix into [2^11, 2^12): (u - 8) * s * 2^E < 2^15
+  const int emax = (int)((hdr->max_scale_bits >> 23) & 0xFFu);
+  const int E = emax == 0 ? 0 : 11 - (emax - 127);
+  const float up = exp2f((float)E), down = exp2f((float)-E);
+
+  if (warp == kTfDequantWarps) {
+    // ------------------------------------------------------------ producer
+    const int np = min(4, p.num_panels - panel0);
+    for (int it = 0; it < k_tiles; ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&mma_done[s], ph ^ 1u))) break;
+      const int g0 = it * kTfGroupsPerStage;
+      const int ng = min(kTfGroupsPerStage, p.num_groups - g0);
+      uint8_t* st = stages + (size_t)s * S::kStageBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCellBytes + ng * NT * 64));
+      __syncwarp();
+      if (lane < np) {
+        bulk_g2s(st + lane * kTfGroupsPerStage * kCellBytes,
+                 p.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCellBytes,
+                 (uint32_t)(ng * kCellBytes), &raw_full[s]);
+      } else if (lane >= 4 && lane < 4 + ng) {
+        const int g = lane - 4;
+        bulk_g2s(st + S::kRawBytes + g * NT * 64, p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 512,
+                 (uint32_t)(NT * 64), &raw_full[s]);
+      }
+    }
+  } else if (warp == kTfDequantWarps + 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = f32, A = B = f16, both K-major, N = NT, M = 128
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
+      bool ok = true;
+      uint32_t accumulate = 0;
+      for (int it = 0; it < k_tiles && ok; ++it) {
+        const int s = it % kStages, sa = it % kTfAStages;
+        ok = mbar_wait_bounded(&raw_full[s], (uint32_t)(it / kStages) & 1u) &&
+             mbar_wait_bounded(&a_full[sa], (uint32_t)(it / kTfAStages) & 1u);
+        if (!ok) break;
+        tc_fence_after();
+        const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
+        uint8_t* st = stages + (size_t)s * S::kStageBytes;
+        const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(a_stages + (size_t)sa * S::kABytes);
+        // K-major, no swizzle: 16-byte K chunks of a row 128 bytes apart, 8-row groups 512 bytes apart
+        const uint64_t a_desc = make_kmajor_desc(a_addr, 128, 512), b_desc = make_kmajor_desc(b_addr, 128, 512);
+#pragma unroll
+        for (int g = 0; g < kTfGroupsPerStage; ++g) {
+          if (g >= ng) break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {  // K = 16 per instruction: two chunks of 8; the start address counts 16-byte units
+            tc_mma_f16(tmem_base, a_desc + (uint64_t)((g * kTfGroupABytes + h * 256) >> 4),
+                       b_desc + (uint64_t)((g * NT * 64 + h * 256) >> 4), idesc, accumulate);
+            accumulate = 1;
+          }
+        }
+        tc_commit(&mma_done[s]);  // frees the loaded stage (producer) and the A stage (dequant)
+      }
+      if (ok) tc_commit(acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------ dequant: thread j = weight row j of the tile,
+    // K-group (warp / 4) of every stage
+    const int j = tid & 127, gsel = warp >> 2;
+    const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
+    const bool have_panel = panel0 + q < p.num_panels;
+    const uint32_t scale_mode = hdr->scale_mode;
+    bool ok = true;
+    for (int it = 0; it < k_tiles && ok; ++it) {
+      const int s = it % kStages, sa = it % kTfAStages;
+      ok = mbar_wait_bounded(&raw_full[s], (uint32_t)(it / kStages) & 1u);
+      if (ok && it >= kTfAStages) {  // the A stage is free once the MMAs of K-tile it - kTfAStages are done
+        const int prev = it - kTfAStages;
+        ok = mbar_wait_bounded(&mma_done[prev % kStages], (uint32_t)(prev / kStages) & 1u);
+      }
+      if (!ok) break;
+      const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
+      const uint8_t* raw = stages + (size_t)s * S::kStageBytes + q * kTfGroupsPerStage * kCellBytes;
+      uint8_t* a_out = a_stages + (size_t)sa * S::kABytes + (j >> 3) * 512 + (j & 7) * 16;
+#pragma unroll
+      for (int g = gsel; g < kTfGroupsPerStage; g += kTfDequantWarps / 4) {  // the two warp quartets alternate over the groups
+        if (g < ng) {
+        uint4 w = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+        float sc = 0.0f;
+        if (have_panel) {
+          w = *reinterpret_cast<const uint4*>(raw + g * kCellBytes + r * 16);
+          sc = decode_scale(*reinterpret_cast<const uint16_t*>(raw + g * kCellBytes + kCellNibbleBytes + r * 2), scale_mode);
+        }
+        const __half2 s2 = __float2half2_rn(sc * up);           // exact: a power-of-two multiple of a bf16/fp16 value
+        const __half2 off = __floats2half2_rn(1032.0f, 1032.0f);  // 0x6400 | nibble = 1024 + nibble; weight = nibble - 8
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // word c = k 8c..8c+7; half2 t = nibbles t and t + 4 (16 bits apart)
+          uint32_t o[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const uint32_t bits = ((ws[c] >> (4 * t)) & 0x000F000Fu) | 0x64006400u;
+            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&bits), off), s2);
+            o[t] = *reinterpret_cast<const uint32_t*>(&v);
+          }
+          *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        }
+      }
+      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_full[sa]);
+    }
+    // ------------------------------------------------------------ epilogue (same four warps)
+    // tensor-memory loads are warp-wide: every lane takes part, only the stores are guarded
+    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(acc_done, 0));
+    tc_fence_after();
+    const int n = tile_n * kTfTileRows + j;
+    const bool live = n < p.n;
+    const float bs = live ? reinterpret_cast<const float*>(p.tiled + p.bias_off)[n] : 0.0f;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const int col_begin = (warp >> 2) * (NT / 2), col_end = col_begin + NT / 2;  // warps w and w + 4 split the columns
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = col_begin; c0 < col_end && m0 + c0 < p.m; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(lane_addr + (uint32_t)c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int m = m0 + c0 + i;
+          if (live && m < p.m) {
+            const float2 h = s_hdr[c0 + i];
+            const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
+            p.y[(size_t)m * p.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == kTfDequantWarps + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int NT>
+static cudaError_t launch_tf_t(const TfParams& prm, cudaStream_t stream) {
+  using S = TfSmem<NT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const dim3 grid((unsigned)((prm.n + kTfTileRows - 1) / kTfTileRows), (unsigned)((prm.m + NT - 1) / NT));
+  w4a32_gemm_tcf16_kernel<NT><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
+  return cudaGetLastError();
+}
+
+// Activation rows per tile for this shape: the widest tile whose grid still covers most of the SMs
+// (wide tiles amortize the dequantization of the 128 weight rows over more tensor-core work).
+int w4a32_gemm_tcf16_tile(int m, int n) {
+  // A tcgen05.mma costs its issuing thread ~100 cycles whatever its size, and 128 x NT x 16 takes NT / 2
+  // cycles of tensor-core time: below NT = 128... the kernel is issue-bound, so narrow tiles lose even
+  // when they would fill more SMs (measured: K = 8960, N = 1536, M = 512: 74 us at NT = 64).
+  const long long ntiles = (n + kTfTileRows - 1) / kTfTileRows;
+  if (m >= 256 && ntiles * ((m + 255) / 256) >= 100) return 256;
+  if (m >= 128) return 128;
+  return 64;
+}
+int w4a32_gemm_tcf16_m_pad(int m, int n) {
+  const int nt = w4a32_gemm_tcf16_tile(m, n);
+  return (m + nt - 1) / nt * nt;
+}
+int w4a32_gemm_tcf16_m_pad_max(int m) { return (m + 255) / 256 * 256; }
+bool w4a32_gemm_tcf16_supported(int m, int k, int n) { return m >= 64 && k >= 1 && n >= 1 && (m + 63) / 64 <= 65535; }
+// Shapes on which this path beats the int8 path clearly (wide tiles on a grid that fills the GPU).
+bool w4a32_gemm_tcf16_preferred(int m, int k, int n) {
+  return w4a32_gemm_tcf16_supported(m, k, n) && w4a32_gemm_tcf16_tile(m, n) == 256;
+}
+
+cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
+                                    int n, int ldy, cudaStream_t stream) {
+  TfParams prm;
+  prm.a_blocks = a_blocks;
+  prm.a_hdr = a_hdr;
+  prm.tiled = static_cast<const uint8_t*>(tiled);
+  prm.y = y;
+  prm.m = m, prm.n = n, prm.k = k, prm.ldy = ldy;
+  prm.num_groups = (k + kGroup - 1) / kGroup;
+  prm.num_panels = (n + kPanelRows - 1) / kPanelRows;
+  prm.m8_pad = w4a32_gemm_tcf16_m_pad(m, n) / 8;
+  const TiledHeader th = make_tiled_header(n, k, 0, 0);
+  prm.zsum_off = th.zsum_off;
+  prm.bias_off = th.bias_off;
+  switch (w4a32_gemm_tcf16_tile(m, n)) {
+    case 256: return launch_tf_t<256>(prm, stream);
+    case 128: return launch_tf_t<128>(prm, stream);
+    default: return launch_tf_t<64>(prm, stream);
+  }
+}
+
+}  // namespace mllmb200

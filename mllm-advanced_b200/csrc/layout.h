@@ -56,7 +56,8 @@ constexpr int kCellBytes = kCellNibbleBytes + kCellScaleBytes;  // 576
 struct TiledHeader {
   uint32_t magic, version, n, k, num_groups, num_panels, scale_mode, has_bias;
   uint64_t cells_off, zsum_off, bias_off, total_bytes;
-  uint8_t pad[256 - 32 - 32];
+  uint32_t max_scale_bits;  // fp32 bits of the largest |group scale| of the matrix (written by the repack kernel)
+  uint8_t pad[256 - 32 - 32 - 4];
 };
 static_assert(sizeof(TiledHeader) == 256, "tiled header is 256 bytes");
 

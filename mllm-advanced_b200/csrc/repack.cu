@@ -47,7 +47,8 @@ __global__ void repack_cells_kernel(const uint8_t* __restrict__ nibbles, const u
 // a fixed order, rounded once to fp32; and the bias copy.
 __global__ void repack_rowdata_kernel(const uint8_t* __restrict__ cells, const float* __restrict__ bias_src,
                                       int row_begin, int row_count, int num_groups, int num_panels,
-                                      uint32_t scale_mode, float* __restrict__ zsum, float* __restrict__ bias_dst) {
+                                      uint32_t scale_mode, float* __restrict__ zsum, float* __restrict__ bias_dst,
+                                      unsigned int* __restrict__ max_scale_bits) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int padded_rows = num_panels * kPanelRows;
@@ -55,6 +56,7 @@ __global__ void repack_rowdata_kernel(const uint8_t* __restrict__ cells, const f
        row += gridDim.x * warps_per_block) {
     const int p = row / kPanelRows, r = row % kPanelRows;
     double acc = 0.0;
+    float smax = 0.0f;  // largest finite |scale| of the row (the fp16 tensor-core path scales by a power of two from it)
     for (int b = lane; b < num_groups; b += 32) {
       const uint8_t* cell = cells + ((size_t)p * num_groups + b) * kCellBytes;
       const uint4 v = *reinterpret_cast<const uint4*>(cell + r * 16);
@@ -70,10 +72,15 @@ __global__ void repack_rowdata_kernel(const uint8_t* __restrict__ cells, const f
       sum -= 8 * kGroup;
       const float s = decode_scale(raw, scale_mode);
       acc += (double)s * (double)sum;
+      if (fabsf(s) <= 3.402823466e+38f) smax = fmaxf(smax, fabsf(s));
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    for (int o = 16; o > 0; o >>= 1) {
+      acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+    }
     if (lane == 0) {
+      if (max_scale_bits != nullptr && row < row_count) atomicMax(max_scale_bits, __float_as_uint(smax));  // non-negative floats order as integers
       zsum[row] = (float)acc;
       bias_dst[row] = (bias_src != nullptr && row < row_count) ? bias_src[row_begin + row] : 0.0f;
     }

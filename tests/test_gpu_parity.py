@@ -207,6 +207,26 @@ def test_tcgen05_gemm_vs_oracle(orc, m, k, n):
     assert_close(y, y2, "tcgen05 vs simt")
 
 
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (64, 1536, 256), (100, 70, 45), (200, 1176, 1280), (512, 1536, 256),
+                                   (300, 4096, 96), (129, 32, 33), (256, 1536, 8960), (512, 8960, 1536),
+                                   (384, 1536, 12800)])
+def test_tcgen05_fp16_gemm_vs_oracle(orc, m, k, n):
+    """tcgen05 fp16 path: group scales folded into an exact fp16 weight operand, fp32 accumulation over
+    all of K in tensor memory.  Products are exact; the stated bound is the common 1e-3 * rms."""
+    rng = np.random.default_rng(m * 5 + k + n)
+    x, w, b = make_case(rng, m, n, k, x_scale=rng.uniform(0.2, 3.0))
+    x[7] = np.abs(x[7]) + 1.0   # zero point -128
+    x[8] = 0.0
+    w[3] *= 1e-3                # a row of small scales next to ordinary ones
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    y = gpu_forward(x, blob, mb.KERNEL_TC_F16)
+    assert_close(y, ref, f"tcgen05 fp16 m={m} k={k} n={n}")
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    print(f"tcgen05 fp16 m={m} k={k} n={n}: max|diff| / rms = {float(np.max(np.abs(y - ref))) / rms:.2e}")
+
+
 def test_tcgen05_prefill_layer_shapes_full_size():
     """All seven linears of a decoder layer at M=512 (BASELINE config 1): tcgen05 vs SIMT path."""
     rng = np.random.default_rng(77)
