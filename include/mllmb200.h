@@ -139,8 +139,10 @@ MLLMB200_API int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void
 /* Several linears that read the SAME activations (q/k/v, gate/up of a decoder layer,
  * mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:47-54,106-112 of the reference) in one call: count in
  * [1,4], all with the same K.  For M <= 4 this is a single kernel launch that quantizes x once per
- * CTA and streams all the weight matrices; for larger M it is `count` ordinary forwards.
- * flags: bit 8 = allow programmatic dependent launch (as in linear_forward_ex's kernel argument). */
+ * CTA and streams all the weight matrices; for larger M the matrices share one quantization of x
+ * when they take the same tensor-core path, else it is `count` ordinary forwards.
+ * flags: bit 8 = allow programmatic dependent launch; low byte = kernel policy for larger M: 0 auto or
+ * 5 fastest (as linear_forward_ex's kernel argument). */
 MLLMB200_API int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int ldx, int count,
                                                        const void* const* tiled_dev, float* const* y_dev,
                                                        const int* N, const int* ldy, void* ws_dev, int flags,

@@ -214,9 +214,37 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
     if (e != cudaErrorInvalidValue) return cuda_fail(e);
     // no joint plan (too much shared memory for the group): fall through to one call per matrix
   }
+  // Larger M: the matrices share ONE quantization of x when they all take the same tensor-core path
+  // (the usual case: q/k/v together, gate/up together); otherwise one ordinary forward per matrix.
+  const int policy = flags & 0xFF;  // 0 auto, 5 fastest (as the kernel argument of linear_forward_ex)
+  if (policy != 0 && policy != 5) return MLLMB200_INVALID_ARG;
+  int kind = -1;  // 3 int8 tcgen05, 4 fp16 tcgen05, -2 mixed / other
+  for (int i = 0; i < count; ++i) {
+    int kk = (policy == 5 && w4a32_gemm_tcf16_preferred(M, K, N[i])) ? 4 : mllmb200_w4a32_select_kernel(M, K, N[i]);
+    if (kk != 3 && kk != 4) kk = -2;
+    kind = (i == 0 || kind == kk) ? kk : -2;
+  }
+  if (count > 1 && kind == 4) {
+    // the fp16 activation blocks are padded to the tile width, which must then be the same for all
+    const int pad0 = w4a32_gemm_tcf16_m_pad(M, N[0]);
+    for (int i = 1; i < count; ++i)
+      if (w4a32_gemm_tcf16_m_pad(M, N[i]) != pad0) kind = -2;
+  }
+  if (count > 1 && (kind == 3 || kind == 4)) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+    uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
+    float2* hdr = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
+    cudaError_t e = kind == 4 ? launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N[0]), K, ldx, blocks, hdr, st)
+                              : launch_act_quant_records(x_dev, M, K, ldx, blocks, hdr, 0, w4a32_gemm_tc_m_pad(M) / 8, st);
+    for (int i = 0; i < count && e == cudaSuccess; ++i)
+      e = kind == 4 ? launch_w4a32_gemm_tcf16(blocks, hdr, tiled_dev[i], y_dev[i], M, K, N[i], ldy[i], st)
+                    : launch_w4a32_gemm_tc(blocks, hdr, tiled_dev[i], y_dev[i], M, K, N[i], ldy[i], st);
+    return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+  }
   for (int i = 0; i < count; ++i) {
     const int st = mllmb200_w4a32_linear_forward_ex(x_dev, tiled_dev[i], y_dev[i], ws_dev, M, K, N[i], ldx, ldy[i],
-                                                    flags & 0x100, stream);
+                                                    (flags & 0x100) | policy, stream);
     if (st != MLLMB200_OK) return st;
   }
   return MLLMB200_OK;

@@ -152,8 +152,9 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       uint32_t accumulate = 0;
       for (int it = 0; it < k_tiles && ok; ++it) {
         const int s = it % kStages, sa = it % kTfAStages;
-        ok = mbar_wait_bounded(&raw_full[s], (uint32_t)(it / kStages) & 1u) &&
-             mbar_wait_bounded(&a_full[sa], (uint32_t)(it / kTfAStages) & 1u);
+        // a_full[sa] is arrived on by the dequant warps AFTER they saw raw_full[s] complete, so it also
+        // orders this stage's bulk copies (the B operand) before the MMAs: one wait instead of two
+        ok = mbar_wait_bounded(&a_full[sa], (uint32_t)(it / kTfAStages) & 1u);
         if (!ok) break;
         tc_fence_after();
         const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);

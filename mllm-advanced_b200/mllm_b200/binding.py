@@ -201,8 +201,9 @@ def linear_forward(x, weights, out=None, workspace=None, kernel=KERNEL_AUTO, str
     return out
 
 
-def linear_forward_grouped(x, weights_list, outs=None, workspace=None, stream=None, pdl=False):
-    """Several linears on the same activations in one call (one launch for M <= 4)."""
+def linear_forward_grouped(x, weights_list, outs=None, workspace=None, stream=None, pdl=False, policy=KERNEL_AUTO):
+    """Several linears on the same activations in one call (one launch for M <= 4; one shared
+    quantization for larger M).  policy: KERNEL_AUTO or KERNEL_FASTEST."""
     import torch
     assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
     m, k = x.shape
@@ -217,7 +218,7 @@ def linear_forward_grouped(x, weights_list, outs=None, workspace=None, stream=No
     ns = (C.c_int * cnt)(*[w.n for w in weights_list])
     ldy = (C.c_int * cnt)(*[o.stride(0) for o in outs])
     _check(lib().mllmb200_w4a32_linear_forward_grouped(x.data_ptr(), m, k, x.stride(0), cnt, tiled, ys, ns, ldy,
-                                                       workspace.data_ptr(), KERNEL_FLAG_PDL if pdl else 0,
+                                                       workspace.data_ptr(), (KERNEL_FLAG_PDL if pdl else 0) | policy,
                                                        _stream_ptr(stream)), "linear_forward_grouped")
     return outs
 

@@ -227,6 +227,28 @@ def test_tcgen05_fp16_gemm_vs_oracle(orc, m, k, n):
     print(f"tcgen05 fp16 m={m} k={k} n={n}: max|diff| / rms = {float(np.max(np.abs(y - ref))) / rms:.2e}")
 
 
+@pytest.mark.parametrize("policy", [0, 5])
+def test_grouped_prefill_shares_quantization(orc, policy):
+    """q/k/v and gate/up at prefill size through the grouped call (one quantization of x, then one
+    GEMM per matrix) equal the single calls of the same kernel policy bit for bit."""
+    rng = np.random.default_rng(91)
+    m, k = 300, 1536
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    for ns in ((1536, 256, 256), (8960, 8960)):
+        wts = []
+        for n in ns:
+            w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+            wts.append(mb.W4A32Weights.from_blob(mb.quant_prepack(w, None)))
+        outs = mb.linear_forward_grouped(xd, wts, policy=policy)
+        torch.cuda.synchronize()
+        for wt, o in zip(wts, outs):
+            single = mb.linear_forward(xd, wt, kernel=policy)
+            torch.cuda.synchronize()
+            assert torch.equal(o, single), (policy, wt.n)
+    mb.check_device_status()
+
+
 def test_tcgen05_prefill_layer_shapes_full_size():
     """All seven linears of a decoder layer at M=512 (BASELINE config 1): tcgen05 vs SIMT path."""
     rng = np.random.default_rng(77)
