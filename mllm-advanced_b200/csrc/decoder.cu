@@ -34,13 +34,15 @@ __global__ void embedding_kernel(const int*, const float*, int, float*);
 __global__ void rope_tables_kernel(float*, float*, int, int, float);
 __global__ void rope_kv_append_kernel(const float*, const float*, int, const float*, const float*, const int*, int,
                                       float*, float*);
-__global__ void attention_kernel(const float*, int, const float*, const float*, const int*, int, int, const float*,
-                                 const float*, float*, int, int);
 template <int D>
 __global__ void attn_decode_partial_kernel(const float*, const float*, const float*, const float*, const float*, const int*,
                                            int, int, int, float*, float*, float*, float*, int, int);
 __global__ void attn_combine_quant_kernel(const float*, const float*, const int*, int, int, int, int, int, float*, uint8_t*,
                                           float2*, int);
+template <int D>
+__global__ void attention_prefill_kernel(const float*, int, int, const float*, const float*, const int*, int, int, const float*,
+                                         const float*, float*, int);
+size_t attention_prefill_smem_bytes(int head_dim);
 __global__ void lm_head_f16_kernel(const float*, const __half*, int, int, float*, float2*);
 __global__ void sample_advance_kernel(const float2*, int, int*, int*, int*, int*, int);
 __global__ void act_quant_records_kernel(const float*, int, int, int, uint8_t*, float2*, int, int);

@@ -44,70 +44,196 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ k_new, const flo
   cache_v[((size_t)h * max_ctx + pos) * D + d] = vr[d];
 }
 
-// grid (q_heads, S), block D (= 128).  Query row s attends to cache positions [0, pos0 + s].
-// q: rows of ldq floats [q_heads * D]; out: rows of ldo floats [q_heads * D].
-// Shared memory: (ctx_max + D + 64) floats.
-__global__ void attention_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ sin_t,
-                                 const float* __restrict__ cos_t, const int* __restrict__ pos0_ptr, int max_ctx, int group,
-                                 const float* __restrict__ cache_k, const float* __restrict__ cache_v,
-                                 float* __restrict__ out, int ldo, int use_pdl) {
-  extern __shared__ float sm[];
-  if (use_pdl) {
-    pdl_launch_dependents();
-    pdl_wait_prior();
+// ---------------------------------------------------------------------------------------------
+// Prefill attention, tiled: grid (ceil(S / 8), kv_heads), 256 threads.  A CTA owns 8 consecutive
+// query rows of all `group` query heads that share one KV head (8 * group <= 64 query vectors,
+// rotated into shared memory once) and walks the cache in blocks of 32 positions up to the causal
+// limit: a key/value block is read from L2 once per CTA (not once per head and row), scores are formed with lane = key position (key rows padded to D + 1 floats:
+// no bank conflicts), and the running softmax (max, sum, rescale) is the usual online form.
+// Arithmetic: scores * 1/sqrt(D), causal mask, softmax, P.V (modeling_ds_qwen2.hpp:127-150 of the reference project).
+// q: rows of ldq floats, row s at position pos0 + s; out: rows of ldo floats.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPfRows = 8;      // query rows per CTA
+constexpr int kPfKeys = 32;     // cache positions per block
+constexpr int kPfThreads = 256;
+
+template <int D>
+struct PrefillAttnSmem {
+  float q[kPfRows * kAttnMaxGroup][D];
+  float k[kPfKeys][D + 1];
+  float v[kPfKeys][D];
+  float p[kPfRows * kAttnMaxGroup][kPfKeys];
+  float alpha[kPfRows * kAttnMaxGroup], lsum[kPfRows * kAttnMaxGroup];
+};
+
+template <int D>
+__global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(
+    const float* __restrict__ q, int ldq, int S, const float* __restrict__ sin_t, const float* __restrict__ cos_t,
+    const int* __restrict__ pos0_ptr, int max_ctx, int group, const float* __restrict__ cache_k,
+    const float* __restrict__ cache_v, float* __restrict__ out, int ldo) {
+  extern __shared__ __align__(16) uint8_t pf_smem[];
+  PrefillAttnSmem<D>& sm = *reinterpret_cast<PrefillAttnSmem<D>*>(pf_smem);
+  constexpr int HALF = D / 2, NG = kPfThreads / (D / 4), QPT = (kPfRows * kAttnMaxGroup + NG - 1) / NG;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int s0 = blockIdx.x * kPfRows, kvh = blockIdx.y;
+  const int pos0 = *pos0_ptr;
+  const int nrows = min(kPfRows, S - s0);
+  const int nq = group * kPfRows;  // query vectors of this CTA: index = h * kPfRows + r
+  // rotated queries (rows past S stay zero)
+  for (int idx = tid; idx < nq * D; idx += kPfThreads) {
+    const int qi = idx / D, d = idx - qi * D;
+    const int h = qi / kPfRows, r = qi - h * kPfRows;
+    float val = 0.0f;
+    if (r < nrows) {
+      const int pos = min(pos0 + s0 + r, max_ctx - 1);
+      const float* qr = q + (size_t)(s0 + r) * ldq + (kvh * group + h) * D;
+      const int dd = d < HALF ? d : d - HALF;
+      const float sn = sin_t[pos * HALF + dd], cs = cos_t[pos * HALF + dd];
+      const float x0 = qr[dd], x1 = qr[dd + HALF];
+      val = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
+    }
+    sm.q[qi][d] = val;
   }
-  const int h = blockIdx.x, s = blockIdx.y, d = threadIdx.x, D = blockDim.x, half = D >> 1;
-  const int pos = min(*pos0_ptr + s, max_ctx - 1), ctx = pos + 1;
-  float* s_q = sm;            // D
-  float* s_red = sm + D;      // 64
-  float* s_p = sm + D + 64;   // ctx scores
-  const int kvh = h / group;
-  // rotated query
-  {
-    const float* qr = q + (size_t)s * ldq + h * D;
-    const int dd = d < half ? d : d - half;
-    const float sn = sin_t[pos * half + dd], cs = cos_t[pos * half + dd];
-    const float x0 = qr[dd], x1 = qr[dd + half];
-    s_q[d] = d < half ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
-  }
-  __syncthreads();
-  const int warp = d >> 5, lane = d & 31, nwarps = D >> 5;
   const float scale = 1.0f / sqrtf((float)D);
   const float* kbase = cache_k + (size_t)kvh * max_ctx * D;
   const float* vbase = cache_v + (size_t)kvh * max_ctx * D;
-  float mx = -3.402823466e+38f;
-  for (int t = warp; t < ctx; t += nwarps) {
-    const float* kr = kbase + (size_t)t * D;
-    float acc = 0.0f;
-    for (int i = lane; i < D; i += 32) acc += s_q[i] * kr[i];
+  const int last_pos = min(pos0 + s0 + nrows - 1, max_ctx - 1);  // causal limit of the tile
+  // running state: warp w owns query vectors w, w + 8, ... (lane-uniform copies of max and sum)
+  float m_run[kAttnMaxGroup], l_run[kAttnMaxGroup];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    acc *= scale;
-    if (lane == 0) s_p[t] = acc;
-    mx = fmaxf(mx, acc);
-  }
-  // block max
-  if (lane == 0) s_red[warp] = mx;
-  __syncthreads();
-  mx = s_red[0];
-  for (int w = 1; w < nwarps; ++w) mx = fmaxf(mx, s_red[w]);
-  __syncthreads();
-  float sum = 0.0f;
-  for (int t = d; t < ctx; t += D) {
-    const float e = expf(s_p[t] - mx);
-    s_p[t] = e;
-    sum += e;
-  }
+  for (int i = 0; i < kAttnMaxGroup; ++i) m_run[i] = -3.402823466e+38f, l_run[i] = 0.0f;
+  // output accumulators: thread (pc, pg) holds elements 4 pc .. 4 pc + 3 of query vectors pg, pg + NG, ...
+  // (a 4-wide register tile: one 16-byte value load and one 16-byte probability load feed 16 FMAs -
+  // the kernel is bound by shared-memory wavefronts, not by FMAs)
+  const int pc = tid % (D / 4), pg = tid / (D / 4);
+  float o_acc[QPT][4];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if (lane == 0) s_red[32 + warp] = sum;
+  for (int i = 0; i < QPT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.0f;
+
+  // A block's key/value rows are requested into registers one block ahead (L2 round trips of ~1k
+  // cycles each otherwise sit between the blocks): thread t moves chunks t, t + 256, ... of the block.
+  constexpr int kLd = kPfKeys * (D / 4) / kPfThreads;  // 16-byte chunks per thread and matrix
+  float4 kreg[kLd], vreg[kLd];
+  auto fetch = [&](int b0) {
+    const int nk = min(kPfKeys, last_pos + 1 - b0);
+#pragma unroll
+    for (int u = 0; u < kLd; ++u) {
+      const int idx = tid + u * kPfThreads;
+      const int j = idx / (D / 4), c = idx - j * (D / 4);
+      kreg[u] = vreg[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < nk) {
+        kreg[u] = *reinterpret_cast<const float4*>(kbase + (size_t)(b0 + j) * D + c * 4);
+        vreg[u] = *reinterpret_cast<const float4*>(vbase + (size_t)(b0 + j) * D + c * 4);
+      }
+    }
+  };
+  fetch(0);
+  for (int b0 = 0; b0 <= last_pos; b0 += kPfKeys) {
+    const int nk = min(kPfKeys, last_pos + 1 - b0);
+    __syncthreads();  // the previous block's k, v, p are no longer read
+#pragma unroll
+    for (int u = 0; u < kLd; ++u) {
+      const int idx = tid + u * kPfThreads;
+      const int j = idx / (D / 4), c = idx - j * (D / 4);
+      sm.k[j][c * 4 + 0] = kreg[u].x, sm.k[j][c * 4 + 1] = kreg[u].y, sm.k[j][c * 4 + 2] = kreg[u].z, sm.k[j][c * 4 + 3] = kreg[u].w;
+      *reinterpret_cast<float4*>(&sm.v[j][c * 4]) = vreg[u];
+    }
+    if (b0 + kPfKeys <= last_pos) fetch(b0 + kPfKeys);
+    __syncthreads();
+    // ---- scores: lane = key position, warp w takes query vectors w + 8 i
+    {
+      float sc[kAttnMaxGroup];
+#pragma unroll
+      for (int i = 0; i < kAttnMaxGroup; ++i) sc[i] = 0.0f;
+      for (int d = 0; d < D; d += 4) {  // query elements as 16-byte broadcast loads, key elements scalar (padded rows)
+        const float k0 = sm.k[lane][d], k1 = sm.k[lane][d + 1], k2 = sm.k[lane][d + 2], k3 = sm.k[lane][d + 3];
+#pragma unroll
+        for (int i = 0; i < kAttnMaxGroup; ++i) {
+          if (i < group) {
+            const float4 q4 = *reinterpret_cast<const float4*>(&sm.q[warp + 8 * i][d]);
+            sc[i] = fmaf(q4.x, k0, sc[i]);
+            sc[i] = fmaf(q4.y, k1, sc[i]);
+            sc[i] = fmaf(q4.z, k2, sc[i]);
+            sc[i] = fmaf(q4.w, k3, sc[i]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kAttnMaxGroup; ++i) {
+        if (i >= group) break;
+        const int qi = warp + 8 * i;          // = h * 8 + r with r = warp, h = i  (kPfRows == 8 warps)
+        const int pos = pos0 + s0 + warp;      // position of this query row
+        const bool valid = lane < nk && b0 + lane <= pos && warp < nrows;
+        const float sv = valid ? sc[i] * scale : -3.402823466e+38f;
+        float mx = sv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m_run[i], mx);
+        const float pv = valid ? expf(sv - m_new) : 0.0f;
+        float sum = pv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float alpha = expf(m_run[i] - m_new);
+        m_run[i] = m_new;
+        l_run[i] = l_run[i] * alpha + sum;
+        sm.p[qi][lane] = pv;
+        if (lane == 0) {
+          sm.alpha[qi] = alpha;
+          sm.lsum[qi] = l_run[i];
+        }
+      }
+    }
+    __syncthreads();
+    // ---- P.V: keys outermost, so that a value row is loaded once for all query vectors of the thread
+#pragma unroll
+    for (int i = 0; i < QPT; ++i) {
+      const int qi = pg + i * NG;
+      const float al = qi < nq ? sm.alpha[qi] : 1.0f;
+      o_acc[i][0] *= al, o_acc[i][1] *= al, o_acc[i][2] *= al, o_acc[i][3] *= al;
+    }
+#pragma unroll 2
+    for (int j = 0; j < kPfKeys; j += 4) {
+      float4 v4[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) v4[jj] = *reinterpret_cast<const float4*>(&sm.v[j + jj][pc * 4]);
+#pragma unroll
+      for (int i = 0; i < QPT; ++i) {
+        const int qi = pg + i * NG;
+        if (qi < nq) {
+          const float4 p4 = *reinterpret_cast<const float4*>(&sm.p[qi][j]);
+          const float pj[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            o_acc[i][0] = fmaf(pj[jj], v4[jj].x, o_acc[i][0]);
+            o_acc[i][1] = fmaf(pj[jj], v4[jj].y, o_acc[i][1]);
+            o_acc[i][2] = fmaf(pj[jj], v4[jj].z, o_acc[i][2]);
+            o_acc[i][3] = fmaf(pj[jj], v4[jj].w, o_acc[i][3]);
+          }
+        }
+      }
+    }
+  }
   __syncthreads();
-  float total = 0.0f;
-  for (int w = 0; w < nwarps; ++w) total += s_red[32 + w];
-  const float inv = 1.0f / total;
-  float o_acc = 0.0f;
-  for (int t = 0; t < ctx; ++t) o_acc += (s_p[t] * inv) * vbase[(size_t)t * D + d];
-  out[(size_t)s * ldo + h * D + d] = o_acc;
+#pragma unroll
+  for (int i = 0; i < QPT; ++i) {
+    const int qi = pg + i * NG;
+    if (qi < nq) {
+      const int h = qi / kPfRows, r = qi - h * kPfRows;
+      if (r < nrows) {
+        const float inv = 1.0f / sm.lsum[qi];
+        *reinterpret_cast<float4*>(out + (size_t)(s0 + r) * ldo + (kvh * group + h) * D + pc * 4) =
+            make_float4(o_acc[i][0] * inv, o_acc[i][1] * inv, o_acc[i][2] * inv, o_acc[i][3] * inv);
+      }
+    }
+  }
+}
+
+template __global__ void attention_prefill_kernel<64>(const float*, int, int, const float*, const float*, const int*, int, int,
+                                                      const float*, const float*, float*, int);
+template __global__ void attention_prefill_kernel<128>(const float*, int, int, const float*, const float*, const int*, int, int,
+                                                       const float*, const float*, float*, int);
+size_t attention_prefill_smem_bytes(int head_dim) {
+  return head_dim == 128 ? sizeof(PrefillAttnSmem<128>) : sizeof(PrefillAttnSmem<64>);
 }
 
 // Decode-step attention over context splits: the work of one CTA is attn_partial_body

@@ -146,13 +146,28 @@ __global__ void __launch_bounds__(kSiluThreads) silu_mul_quant_kernel(const floa
   }
   const int m = blockIdx.x, tid = threadIdx.x;
   float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-  for (int k = tid; k < inter; k += kSiluThreads) {
-    const float g = gate[(size_t)m * inter + k];
-    const float a = (g / (1.0f + expf(-g))) * up[(size_t)m * inter + k];
-    s_a[k] = a;
-    if (a_out) a_out[(size_t)m * inter + k] = a;
-    mn = fminf(mn, a);
-    mx = fmaxf(mx, a);
+  // eight gate/up pairs per thread are requested before the first is used: with one CTA per row the
+  // kernel is a chain of memory round trips, not a bandwidth problem
+  constexpr int kBatch = 8;
+  for (int k0 = 0; k0 < inter; k0 += kSiluThreads * kBatch) {
+    float g[kBatch], u[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int k = k0 + j * kSiluThreads + tid;
+      g[j] = k < inter ? gate[(size_t)m * inter + k] : 0.0f;
+      u[j] = k < inter ? up[(size_t)m * inter + k] : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int k = k0 + j * kSiluThreads + tid;
+      if (k < inter) {
+        const float a = (g[j] / (1.0f + expf(-g[j]))) * u[j];
+        s_a[k] = a;
+        if (a_out) a_out[(size_t)m * inter + k] = a;
+        mn = fminf(mn, a);
+        mx = fmaxf(mx, a);
+      }
+    }
   }
   if (records == nullptr) return;
   block_minmax(mn, mx, scratch);
