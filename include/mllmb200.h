@@ -174,6 +174,21 @@ MLLMB200_API int mllmb200_w4a32_linear_forward_static(const float* x_dev, const 
 MLLMB200_API int mllmb200_w4a32_static_scratch_bytes(size_t* bytes);
 
 /* ------------------------------------------------------------------------------------------
+ * Conv3D as a W4A32 linear (the Qwen2VL patch embedding): im2col, the quantized linear on
+ * [B*T'*H'*W', C*kt*kh*kw], permutation to [B, O, T', H', W'] - the flow of
+ * mllm/Backends/Arm/Ops/Conv3DOp.cpp:31-170 (no padding, dilation 1; column order c, kt, kh, kw as
+ * mllm/Backends/Arm/Kernels/conv3d.cpp:15-79).  in_shape = {B, C, T, H, W}, kernel = {kt, kh, kw},
+ * stride = {st, sh, sw}.  plan: the implied linear's M and K and the workspace bytes (outputs may be
+ * NULL).  forward: x_dev / y_dev contiguous fp32; tiled_dev = the [out_ch, K] weight (+ bias) in the
+ * tile layout (prepack + repack as for any linear); ws_dev 256-byte aligned.
+ * ------------------------------------------------------------------------------------------ */
+MLLMB200_API int mllmb200_conv3d_w4a32_plan(const int* in_shape, const int* kernel, const int* stride, int out_ch,
+                                            int* M, int* K, size_t* workspace_bytes);
+MLLMB200_API int mllmb200_conv3d_w4a32_forward(const float* x_dev, const void* tiled_dev, float* y_dev, void* ws_dev,
+                                               const int* in_shape, const int* kernel, const int* stride, int out_ch,
+                                               void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Decoder: the Qwen2-architecture language model whose linears are the W4A32 op above
  * (reference project: mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:47-54,106-155,175-215, greedy loop
  * mllm/Models/AutoLLM.hpp:39-105).  Batch 1, fp32 activations and KV cache, fp16 lm_head, greedy

@@ -51,6 +51,46 @@ void CUDAW4A32LinearOp::releaseDevice() {
   workspace_bytes_ = 0;
 }
 
+void* uploadW4A32Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, int k, const std::string& name) {
+  std::vector<unsigned char> owned;  // holds the blob when it is produced here
+  const void* blob = nullptr;
+  size_t blob_bytes = 0;
+  if (weight.dtype() == kInt8) {
+    // the quantization pass's output: an opaque 1-D int8 tensor (KaiQuantizationPass.cpp:167-184 convention)
+    blob = weight.ptr<unsigned char>();
+    blob_bytes = weight.numel();
+  } else if (weight.dtype() == kFp32) {
+    // unquantized checkpoint: quantize at load time with the same routine the pass uses; any trailing
+    // dimensions (a Conv3D kernel [O, C, kt, kh, kw]) are the row of the implied [N, K] matrix
+    MLLM_RT_ASSERT_EQ((size_t)weight.numel(), (size_t)n * (size_t)k);
+    const bool has_bias = want_bias && bias.dtype() == kFp32 && (int)bias.numel() == n;
+    MLLMB200_CHECK(mllmb200_w4a32_prepack_size(n, k, has_bias, &blob_bytes));
+    owned.resize(blob_bytes);
+    MLLMB200_CHECK(mllmb200_w4a32_quant_prepack(weight.ptr<float>(), has_bias ? bias.ptr<float>() : nullptr, n, k,
+                                                MLLMB200_SCALE_BF16_TRUNC, owned.data()));
+    blob = owned.data();
+  } else {
+    MLLM_ERROR_EXIT(kError, "{}: weight dtype must be int8 (pre-packed) or fp32", name);
+  }
+
+  int bn = 0, bk = 0, scale_mode = 0, has_bias = 0;
+  MLLMB200_CHECK(mllmb200_w4a32_blob_info(blob, blob_bytes, &bn, &bk, &scale_mode, &has_bias));
+  if (bn != n || bk != k) { MLLM_ERROR_EXIT(kError, "{}: blob is {}x{} but the layer is {}x{}", name, bn, bk, n, k); }
+
+  auto stream = static_cast<cudaStream_t>(currentW4A32Stream());
+  void* blob_dev = nullptr;
+  void* tiled_dev = nullptr;
+  size_t tiled_bytes = 0;
+  MLLMB200_CHECK(mllmb200_w4a32_tiled_size(n, k, &tiled_bytes));
+  MLLMB200_CHECK_CUDA(cudaMalloc(&blob_dev, blob_bytes));
+  MLLMB200_CHECK_CUDA(cudaMalloc(&tiled_dev, tiled_bytes));
+  MLLMB200_CHECK_CUDA(cudaMemcpyAsync(blob_dev, blob, blob_bytes, cudaMemcpyHostToDevice, stream));
+  MLLMB200_CHECK(mllmb200_w4a32_repack_device(blob_dev, n, k, scale_mode, has_bias, 0, n, tiled_dev, stream));
+  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` and blob_dev go away below
+  MLLMB200_CHECK_CUDA(cudaFree(blob_dev));
+  return tiled_dev;
+}
+
 void CUDAW4A32LinearOp::load(const std::shared_ptr<ParameterLoader>& ploader) {
   LinearOp::load(ploader);  // weight_ / bias_ by name (mllm/Core/AOps/LinearOp.cpp:60-63)
   if (!isW4A32ImplType(cargo_.impl_type_)) {
@@ -60,46 +100,13 @@ void CUDAW4A32LinearOp::load(const std::shared_ptr<ParameterLoader>& ploader) {
   releaseDevice();
   k_ = cargo_.in_channels;
   n_ = cargo_.out_channels;
-
-  std::vector<unsigned char> owned;  // holds the blob when it is produced here
-  const void* blob = nullptr;
-  size_t blob_bytes = 0;
-  if (weight_.dtype() == kInt8) {
-    // the quantization pass's output: an opaque 1-D int8 tensor (KaiQuantizationPass.cpp:167-184 convention)
-    blob = weight_.ptr<unsigned char>();
-    blob_bytes = weight_.numel();
-  } else if (weight_.dtype() == kFp32) {
-    // unquantized checkpoint: quantize at load time with the same routine the pass uses
+  if (weight_.dtype() == kFp32) {
     auto shape = weight_.shape();
     MLLM_RT_ASSERT_EQ(shape.size(), 2);
     MLLM_RT_ASSERT_EQ(shape[0], n_);
     MLLM_RT_ASSERT_EQ(shape[1], k_);
-    const bool has_bias = cargo_.bias && bias_.dtype() == kFp32 && (int)bias_.numel() == n_;
-    MLLMB200_CHECK(mllmb200_w4a32_prepack_size(n_, k_, has_bias, &blob_bytes));
-    owned.resize(blob_bytes);
-    MLLMB200_CHECK(mllmb200_w4a32_quant_prepack(weight_.ptr<float>(), has_bias ? bias_.ptr<float>() : nullptr, n_, k_,
-                                                MLLMB200_SCALE_BF16_TRUNC, owned.data()));
-    blob = owned.data();
-  } else {
-    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: weight dtype must be int8 (pre-packed) or fp32", name());
   }
-
-  int bn = 0, bk = 0, scale_mode = 0, has_bias = 0;
-  MLLMB200_CHECK(mllmb200_w4a32_blob_info(blob, blob_bytes, &bn, &bk, &scale_mode, &has_bias));
-  if (bn != n_ || bk != k_) {
-    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: blob is {}x{} but the layer is {}x{}", name(), bn, bk, n_, k_);
-  }
-
-  auto stream = static_cast<cudaStream_t>(currentW4A32Stream());
-  void* blob_dev = nullptr;
-  size_t tiled_bytes = 0;
-  MLLMB200_CHECK(mllmb200_w4a32_tiled_size(n_, k_, &tiled_bytes));
-  MLLMB200_CHECK_CUDA(cudaMalloc(&blob_dev, blob_bytes));
-  MLLMB200_CHECK_CUDA(cudaMalloc(&tiled_dev_, tiled_bytes));
-  MLLMB200_CHECK_CUDA(cudaMemcpyAsync(blob_dev, blob, blob_bytes, cudaMemcpyHostToDevice, stream));
-  MLLMB200_CHECK(mllmb200_w4a32_repack_device(blob_dev, n_, k_, scale_mode, has_bias, 0, n_, tiled_dev_, stream));
-  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` and blob_dev go away below
-  MLLMB200_CHECK_CUDA(cudaFree(blob_dev));
+  tiled_dev_ = uploadW4A32Weights(weight_, bias_, cargo_.bias, n_, k_, "CUDAW4A32LinearOp " + name());
 }
 
 void CUDAW4A32LinearOp::reshape(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) {

@@ -5,6 +5,7 @@
 
 #include <cstddef>
 #include <memory>
+#include <string>
 
 #include "mllm/Core/AOps/LinearOp.hpp"
 
@@ -38,6 +39,10 @@ class CUDALinearOpFactory : public TypedOpFactory<OpType::kLinear, LinearOpCargo
     return std::make_shared<CUDAW4A32LinearOp>(cargo);
   }
 };
+
+// Pre-pack blob (int8 tensor) or fp32 weight of an [n, k] matrix -> device buffer in the tile layout
+// (cudaMalloc'ed; the caller frees it).  Shared with the Conv3D op.
+void* uploadW4A32Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, int k, const std::string& name);
 
 // True for the impl types this op implements (the six f32 W4 Kai tiles; the tile choice is an
 // Arm micro-kernel detail and is ignored here).

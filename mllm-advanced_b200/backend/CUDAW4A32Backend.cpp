@@ -2,6 +2,7 @@
 
 #include <cuda_runtime.h>
 
+#include "CUDAConv3DOp.hpp"
 #include "CUDALinearOp.hpp"
 #include "mllm/Utils/Common.hpp"
 #include "mllm/Utils/Log.hpp"
@@ -85,6 +86,7 @@ CUDAW4A32Backend::CUDAW4A32Backend() : BackendBase(kCUDA) {
   g_stream = s;
   allocator_ = std::make_shared<CUDAW4A32Allocator>();
   regOpFactory<CUDALinearOpFactory>();
+  regOpFactory<CUDAConv3DOpFactory>();
 }
 
 CUDAW4A32Backend::~CUDAW4A32Backend() {

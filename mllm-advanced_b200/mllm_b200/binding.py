@@ -56,6 +56,8 @@ def lib():
         "mllmb200_w4a32_select_kernel": ([C.c_int, C.c_int, C.c_int], C.c_int),
         "mllmb200_w4a32_quant_activations": ([vp, C.c_int, C.c_int, C.c_int, vp, vp], C.c_int),
         "mllmb200_check_device_status": ([vp], C.c_int),
+        "mllmb200_conv3d_w4a32_plan": ([int_p, int_p, int_p, C.c_int, int_p, int_p, sz_p], C.c_int),
+        "mllmb200_conv3d_w4a32_forward": ([vp, vp, vp, vp, int_p, int_p, int_p, C.c_int, vp], C.c_int),
     }
     for name, (args, res) in sig.items():
         fn = getattr(L, name)
@@ -235,3 +237,23 @@ def quant_activations(x, stream=None):
 
 def check_device_status(stream=None):
     _check(lib().mllmb200_check_device_status(_stream_ptr(stream)), "device status")
+
+
+def conv3d_forward(x, weights, kernel, stride, stream=None):
+    """Conv3D (no padding, dilation 1) as a W4A32 linear: x [B, C, T, H, W] fp32 on the device,
+    weights = W4A32Weights of the [out_ch, C*kt*kh*kw] matrix.  Returns [B, out_ch, T', H', W']."""
+    import torch
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 5 and x.is_contiguous()
+    shp = (C.c_int * 5)(*x.shape)
+    ker = (C.c_int * 3)(*kernel)
+    strd = (C.c_int * 3)(*stride)
+    m, k, wsb = C.c_int(), C.c_int(), C.c_size_t()
+    _check(lib().mllmb200_conv3d_w4a32_plan(shp, ker, strd, weights.n, C.byref(m), C.byref(k), C.byref(wsb)), "conv3d_plan")
+    assert k.value == weights.k, (k.value, weights.k)
+    ot, oh, ow = [(x.shape[2 + i] - kernel[i]) // stride[i] + 1 for i in range(3)]
+    y = torch.empty((x.shape[0], weights.n, ot, oh, ow), dtype=torch.float32, device=x.device)
+    ws = torch.empty(wsb.value + 256, dtype=torch.uint8, device=x.device)
+    off = (-ws.data_ptr()) % 256
+    _check(lib().mllmb200_conv3d_w4a32_forward(x.data_ptr(), weights.tiled.data_ptr(), y.data_ptr(), ws.data_ptr() + off,
+                                               shp, ker, strd, weights.n, _stream_ptr(stream)), "conv3d_forward")
+    return y

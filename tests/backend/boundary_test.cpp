@@ -2,7 +2,8 @@
 // (MllmEngineCtx / BackendBase / nn::Module / nn::Linear / ParameterLoader / ir::PassManager),
 // compiled against the reference's real classes.  Follows the shape of the reference's
 // op-through-plugin test (tests/Arm/SingleConv3DTest.cpp:88-120): build a one-layer module, hand it
-// a ParameterLoader, call it, compare with a scalar reference - here the CPU oracle.
+// a ParameterLoader, call it, compare with a scalar reference - here the CPU oracle.  The quantized
+// parameters also make the trip through a .mllm file written and read by the reference's own code.
 //
 //   1. CudaQuantizationPass on a flat IR module (as tools/Quantizer/FlatModuleBuilder.cpp builds it):
 //      the int8 blob's nibble and scale sections must equal the oracle's quantizer bit for bit.
@@ -135,14 +136,36 @@ void runCase(const std::string& model, int k, int n, bool with_bias, const std::
   check(std::memcmp(blob_bytes + off_s, s_ref.data(), s_ref.size() * 2) == 0, "  scales bit-identical to the oracle");
   if (with_bias) check(std::memcmp(blob_bytes + off_b, b.ptr<float>(), n * 4) == 0, "  bias carried inside the blob");
 
-  if (g_host_only) return;
-  // ---- 2. one-layer module: load on the host, move to the GPU, run
-  auto net = SingleLinear(model, k, n, with_bias);
-  auto ploader = std::make_shared<ParameterLoader>();
-  blob.setMemType(kParams);
+  // ---- 1b. the .mllm parameter file: what mllm-quantizer writes after its pass
+  // (tools/Quantizer/main.cpp -> mllm::write) and what a model loads (mllm::load): the blob must
+  // come back byte for byte under the same name and dtype, through the reference's own writer/reader
   Tensor bias_placeholder = host_linear->bias();
-  ploader->params().insert({layer + ".weight", blob.impl()});
-  if (with_bias) ploader->params().insert({layer + ".bias", bias_placeholder.impl()});
+  const std::string file = "/tmp/mllmb200_boundary_" + model + ".mllm";
+  {
+    std::unordered_map<std::string, Tensor> params;
+    params.insert({layer + ".weight", blob});
+    if (with_bias) params.insert({layer + ".bias", bias_placeholder});
+    mllm::write(file, params, model);
+  }
+  auto ploader = mllm::load(file);
+  {
+    auto back = ploader->params().find(layer + ".weight");
+    bool ok = back != ploader->params().end();
+    if (ok) {
+      Tensor t(back->second);
+      ok = t.dtype() == kInt8 && (size_t)t.numel() == (size_t)blob.numel() &&
+           std::memcmp(t.ptr<uint8_t>(), blob.ptr<uint8_t>(), blob.numel()) == 0;
+    }
+    check(ok, "  .mllm round trip (reference ParameterWriter -> ParameterLoader): blob byte-identical");
+    if (with_bias) check(ploader->params().count(layer + ".bias") == 1, "  .mllm round trip: bias placeholder present");
+  }
+
+  if (g_host_only) {
+    std::remove(file.c_str());
+    return;
+  }
+  // ---- 2. one-layer module: load from the parameter file, move to the GPU, run
+  auto net = SingleLinear(model, k, n, with_bias);
   net.load(ploader);
   net.to(kCUDA);
   auto stream = static_cast<cudaStream_t>(cuda::currentW4A32Stream());
