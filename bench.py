@@ -601,6 +601,11 @@ def run_gpu(args):
                 line["cpu_baseline"] = dict(line["cpu_port"])
         except Exception as ex:  # the oracle is optional for the bench
             line["cpu_port"] = {"unavailable": str(ex)[:100]}
+        if world == 1 and not args.no_config4:
+            try:
+                line["config4"] = run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)
+            except Exception as ex:
+                line["config4"] = {"error": str(ex)[:200]}
         if not args.no_decoder and world == 1:
             try:
                 cpu_ms = line.get("cpu_baseline", {}).get("ms_per_layer")
@@ -727,6 +732,60 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
     return out
 
 
+def run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
+    """BASELINE config 4 on one GPU: W [28672, 8192] int4 g32 (132 MB).  The same kernels as the
+    headline, at a size where fixed latencies no longer dominate: GEMV at M=1 (HBM roofline) and the
+    GEMM at M=2048 rows of x per call (4 calls = the config's 8192 rows), per kernel policy."""
+    n, k = 28672, 8192
+    copies = [make_random_weights(mb, torch, n, k, False, gen) for _ in range(4)]  # 4 x 132 MB > L2
+    out = {"workload": "config4: W[28672,8192] int4 g32; GEMV M=1 over 4 weight copies, GEMM M=2048"}
+    stream = torch.cuda.Stream()
+    x1 = torch.randn((1, k), device="cuda", generator=gen)
+    y1 = torch.empty((1, n), device="cuda")
+    ws1 = torch.empty(mb.workspace_size(1, k), dtype=torch.uint8, device="cuda")
+
+    def gemv_pass():
+        for w in copies:
+            mb.linear_forward(x1, w, out=y1, workspace=ws1, stream=stream, pdl=True)
+    with torch.cuda.stream(stream):
+        gemv_pass()
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        gemv_pass()
+    for _ in range(3):
+        g.replay()
+    ms = event_time_ms(torch, g.replay, 20) / len(copies)
+    by = algorithmic_bytes(1, k, n, False)
+    out["gemv_M1"] = {"us": ms * 1e3, "GBs": by / (ms * 1e-3) / 1e9, "frac": by / (ms * 1e-3) / 1e9 / hbm_peak,
+                      "peak_kind": f"of {peak_kind}", "how": "graph of 4 calls (quantization + GEMV each) over 4 weight copies"}
+    del g
+    m = 2048
+    xm = torch.randn((m, k), device="cuda", generator=gen)
+    ym = torch.empty((m, n), device="cuda")
+    wsm = torch.empty(mb.workspace_size(m, k), dtype=torch.uint8, device="cuda")
+    flops = 2.0 * m * n * k
+    for key, kern in (("gemm_M2048_int8", mb.KERNEL_AUTO), ("gemm_M2048_fp16", mb.KERNEL_TC_F16)):
+        def gemm_pass(kern=kern):
+            with torch.cuda.stream(stream):
+                for w in copies[:2]:
+                    mb.linear_forward(xm, w, out=ym, workspace=wsm, stream=stream, kernel=kern)
+        gemm_pass()
+        stream.synchronize()
+        with torch.cuda.stream(stream):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                gemm_pass()
+            e1.record(stream)
+        stream.synchronize()
+        msg = e0.elapsed_time(e1) / 6
+        out[key] = {"ms": msg, "tflops": flops / (msg * 1e-3) / 1e12, "frac_of_bf16_peak": flops / (msg * 1e-3) / 1e12 / tensor_peak,
+                    "peak_kind": f"of {peak_kind}", "unit": "TOP/s (2*M*N*K), activation quantization included"}
+    mb.check_device_status()
+    return out
+
+
 def run_tp(args, torch, mb, dist, rank, world, gen):
     """BASELINE config 4: W [28672, 8192] column-sharded over the ranks, x replicated, NCCL all-gather of y.
     M=1 (GEMV) and a reduced M for the GEMM; device time, max over ranks."""
@@ -776,6 +835,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch on the stream instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
     ap.add_argument("--per-op", action="store_true", help="headline step with one call per linear instead of grouped calls")
+    ap.add_argument("--no-config4", action="store_true", help="skip the single-GPU section on BASELINE config 4's large matrix")
     ap.add_argument("--decoder-only", action="store_true", help="only the whole-model prefill + decode section")
     ap.add_argument("--decoder-prompt", type=int, default=512, help="prompt length of the decoder section")
     ap.add_argument("--decoder-steps", type=int, default=128, help="greedy steps of the decoder section (small values for ncu)")
