@@ -299,6 +299,10 @@ def run_gpu(args):
         print(json.dumps({"prefill_only": True, "M": PREFILL_M, "passes": max(1, args.steps)}))
         return
 
+    if args.config4_only:
+        print(json.dumps({"config4": run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)}), flush=True)
+        return
+
     # ---- weights: 28 layers x 7 linears, each its own tiled buffer
     layers = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(LAYERS)]
     if args.decoder_only:
@@ -835,6 +839,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch on the stream instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
     ap.add_argument("--per-op", action="store_true", help="headline step with one call per linear instead of grouped calls")
+    ap.add_argument("--config4-only", action="store_true", help="only the section on BASELINE config 4's large matrix")
     ap.add_argument("--no-config4", action="store_true", help="skip the single-GPU section on BASELINE config 4's large matrix")
     ap.add_argument("--decoder-only", action="store_true", help="only the whole-model prefill + decode section")
     ap.add_argument("--decoder-prompt", type=int, default=512, help="prompt length of the decoder section")
