@@ -806,11 +806,13 @@ def run_tp(args, torch, mb, dist, rank, world, gen):
         y_loc = torch.empty((m, n_loc), device="cuda")
         ws = torch.empty(mb.workspace_size(m, k), dtype=torch.uint8, device="cuda")
 
+        kern = mb.KERNEL_AUTO if m == 1 else mb.KERNEL_FASTEST
+
         def fwd():
-            mb.linear_forward(x, w, out=y_loc, workspace=ws)
+            mb.linear_forward(x, w, out=y_loc, workspace=ws, kernel=kern)
 
         def fwd_gather():
-            mb.linear_forward(x, w, out=y_loc, workspace=ws)
+            mb.linear_forward(x, w, out=y_loc, workspace=ws, kernel=kern)
             tp.gather_columns(y_loc, n_total, n_loc)  # all-gather + [world, M, N/world] -> [M, N]
         res = {}
         for name, fn in (("compute_ms", fwd), ("compute_allgather_ms", fwd_gather)):
