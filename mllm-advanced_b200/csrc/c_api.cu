@@ -30,6 +30,9 @@ int w4a32_gemm_tcf16_m_pad(int m, int n);
 int w4a32_gemm_tcf16_m_pad_max(int m);
 cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
 cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t);
+int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n);
+cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
+                                            const int*, const int*, cudaStream_t);
 
 static thread_local int t_last_cuda_error = 0;
 static int cuda_fail(cudaError_t e) {
@@ -214,32 +217,35 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
     if (e != cudaErrorInvalidValue) return cuda_fail(e);
     // no joint plan (too much shared memory for the group): fall through to one call per matrix
   }
-  // Larger M: the matrices share ONE quantization of x when they all take the same tensor-core path
-  // (the usual case: q/k/v together, gate/up together); otherwise one ordinary forward per matrix.
+  // Larger M: the matrices share ONE quantization of x.  With the "fastest" policy (5) and M >= 128 they
+  // also share ONE launch of the fp16 tensor-core kernel (their tiles side by side in the grid: q, k, v
+  // alone fill 16 + 2 + 2 tiles); with the default policy, or when the fp16 path does not apply, they
+  // run as separate int8 tensor-core launches behind one quantization, or as ordinary forwards.
   const int policy = flags & 0xFF;  // 0 auto, 5 fastest (as the kernel argument of linear_forward_ex)
   if (policy != 0 && policy != 5) return MLLMB200_INVALID_ARG;
-  int kind = -1;  // 3 int8 tcgen05, 4 fp16 tcgen05, -2 mixed / other
-  for (int i = 0; i < count; ++i) {
-    int kk = (policy == 5 && w4a32_gemm_tcf16_preferred(M, K, N[i])) ? 4 : mllmb200_w4a32_select_kernel(M, K, N[i]);
-    if (kk != 3 && kk != 4) kk = -2;
-    kind = (i == 0 || kind == kk) ? kk : -2;
+  cudaStream_t st_grp = static_cast<cudaStream_t>(stream);
+  if (count > 1 && policy == 5 && M >= 128) {
+    bool all16 = true;
+    for (int i = 0; i < count; ++i) all16 = all16 && w4a32_gemm_tcf16_supported(M, K, N[i]);
+    if (all16) {
+      if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+      uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
+      float2* hdr = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
+      const int nt = w4a32_gemm_tcf16_tile_grouped(M, count, N);
+      cudaError_t e = launch_act_quant_blocks_f16(x_dev, M, (M + nt - 1) / nt * nt, K, ldx, blocks, hdr, st_grp);
+      if (e == cudaSuccess) e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, count, tiled_dev, y_dev, N, ldy, st_grp);
+      return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+    }
   }
-  if (count > 1 && kind == 4) {
-    // the fp16 activation blocks are padded to the tile width, which must then be the same for all
-    const int pad0 = w4a32_gemm_tcf16_m_pad(M, N[0]);
-    for (int i = 1; i < count; ++i)
-      if (w4a32_gemm_tcf16_m_pad(M, N[i]) != pad0) kind = -2;
-  }
-  if (count > 1 && (kind == 3 || kind == 4)) {
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+  bool all8 = count > 1;
+  for (int i = 0; i < count; ++i) all8 = all8 && mllmb200_w4a32_select_kernel(M, K, N[i]) == 3;
+  if (all8) {
     if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
     uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
     float2* hdr = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
-    cudaError_t e = kind == 4 ? launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N[0]), K, ldx, blocks, hdr, st)
-                              : launch_act_quant_records(x_dev, M, K, ldx, blocks, hdr, 0, w4a32_gemm_tc_m_pad(M) / 8, st);
+    cudaError_t e = launch_act_quant_records(x_dev, M, K, ldx, blocks, hdr, 0, w4a32_gemm_tc_m_pad(M) / 8, st_grp);
     for (int i = 0; i < count && e == cudaSuccess; ++i)
-      e = kind == 4 ? launch_w4a32_gemm_tcf16(blocks, hdr, tiled_dev[i], y_dev[i], M, K, N[i], ldy[i], st)
-                    : launch_w4a32_gemm_tc(blocks, hdr, tiled_dev[i], y_dev[i], M, K, N[i], ldy[i], st);
+      e = launch_w4a32_gemm_tc(blocks, hdr, tiled_dev[i], y_dev[i], M, K, N[i], ldy[i], st_grp);
     return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
   }
   for (int i = 0; i < count; ++i) {

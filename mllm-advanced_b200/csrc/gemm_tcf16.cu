@@ -45,14 +45,19 @@ constexpr int kTfThreads = (kTfDequantWarps + 2) * 32;
 constexpr int kTfTileRows = 128;
 constexpr int kTfGroupABytes = kTfTileRows * kGroup * 2;  // 8192: one K-group of the A operand
 
+constexpr int kTfMaxProblems = 4;
+struct TfProblem {          // one weight matrix of a launch; all problems share x (M, K, the activation blocks)
+  const uint8_t* tiled;     // TiledHeader at offset 0
+  float* y;
+  int n, ldy, num_panels;
+  int tile_begin;           // first blockIdx.x of this problem
+  size_t bias_off;
+};
 struct TfParams {
   const uint8_t* a_blocks;  // activations, [num_groups][m8_pad][512 bytes] fp16 canonical blocks
   const float2* a_hdr;      // [m] {lhs_scale, a_off bits}
-  const uint8_t* tiled;     // weights (TiledHeader at offset 0)
-  float* y;
-  int m, n, k, ldy;
-  int num_groups, num_panels, m8_pad;
-  size_t zsum_off, bias_off;
+  int m, k, num_groups, m8_pad, num_problems;
+  TfProblem prob[kTfMaxProblems];
 };
 
 template <int NT>
@@ -92,7 +97,12 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   uint8_t* a_stages = smem + S::kAOffset;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  int pi = 0;
+#pragma unroll
+  for (int i = 1; i < kTfMaxProblems; ++i)
+    if (i < p.num_problems && (int)blockIdx.x >= p.prob[i].tile_begin) pi = i;
+  const TfProblem& pr = p.prob[pi];
+  const int tile_n = (int)blockIdx.x - pr.tile_begin, tile_m = blockIdx.y;
   const int panel0 = tile_n * 4, m0 = tile_m * NT;
   const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
   constexpr uint32_t kTmemCols = NT < 32 ? 32 : NT;
@@ -115,7 +125,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
-  const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(p.tiled);
+  const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(pr.tiled);
   // 2^E maps the largest |scale| of the matrix into [2^11, 2^12): (u - 8) * s * 2^E < 2^15
   const int emax = (int)((hdr->max_scale_bits >> 23) & 0xFFu);
   const int E = emax == 0 ? 0 : 11 - (emax - 127);
@@ -123,7 +133,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
 
   if (warp == kTfDequantWarps) {
     // ------------------------------------------------------------ producer
-    const int np = min(4, p.num_panels - panel0);
+    const int np = min(4, pr.num_panels - panel0);
     for (int it = 0; it < k_tiles; ++it) {
       const int s = it % kStages;
       const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -135,7 +145,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       __syncwarp();
       if (lane < np) {
         bulk_g2s(st + lane * kTfGroupsPerStage * kCellBytes,
-                 p.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCellBytes,
+                 pr.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCellBytes,
                  (uint32_t)(ng * kCellBytes), &raw_full[s]);
       } else if (lane >= 4 && lane < 4 + ng) {
         const int g = lane - 4;
@@ -181,7 +191,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     // K-group (warp / 4) of every stage
     const int j = tid & 127, gsel = warp >> 2;
     const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
-    const bool have_panel = panel0 + q < p.num_panels;
+    const bool have_panel = panel0 + q < pr.num_panels;
     const uint32_t scale_mode = hdr->scale_mode;
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
@@ -229,8 +239,8 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(acc_done, 0));
     tc_fence_after();
     const int n = tile_n * kTfTileRows + j;
-    const bool live = n < p.n;
-    const float bs = live ? reinterpret_cast<const float*>(p.tiled + p.bias_off)[n] : 0.0f;
+    const bool live = n < pr.n;
+    const float bs = live ? reinterpret_cast<const float*>(pr.tiled + pr.bias_off)[n] : 0.0f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const int col_begin = (warp >> 2) * (NT / 2), col_end = col_begin + NT / 2;  // warps w and w + 4 split the columns
     if (ok) {
@@ -245,7 +255,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
           if (live && m < p.m) {
             const float2 h = s_hdr[c0 + i];
             const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
-            p.y[(size_t)m * p.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+            pr.y[(size_t)m * pr.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
           }
         }
       }
@@ -260,7 +270,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
 }
 
 template <int NT>
-static cudaError_t launch_tf_t(const TfParams& prm, cudaStream_t stream) {
+static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_t stream) {
   using S = TfSmem<NT>;
   static bool configured = false;
   if (!configured) {
@@ -268,21 +278,26 @@ static cudaError_t launch_tf_t(const TfParams& prm, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const dim3 grid((unsigned)((prm.n + kTfTileRows - 1) / kTfTileRows), (unsigned)((prm.m + NT - 1) / NT));
+  const dim3 grid((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
   w4a32_gemm_tcf16_kernel<NT><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
   return cudaGetLastError();
 }
 
-// Activation rows per tile for this shape: the widest tile whose grid still covers most of the SMs
-// (wide tiles amortize the dequantization of the 128 weight rows over more tensor-core work).
-int w4a32_gemm_tcf16_tile(int m, int n) {
-  // A tcgen05.mma costs its issuing thread ~100 cycles whatever its size, and 128 x NT x 16 takes NT / 2
-  // cycles of tensor-core time: below NT = 128... the kernel is issue-bound, so narrow tiles lose even
-  // when they would fill more SMs (measured: K = 8960, N = 1536, M = 512: 74 us at NT = 64).
-  const long long ntiles = (n + kTfTileRows - 1) / kTfTileRows;
+// Activation rows per tile for `ntiles` 128-row weight tiles (of all matrices of the launch together):
+// the widest tile whose grid still covers most of the SMs.  A tcgen05.mma costs its issuing thread
+// ~100 cycles whatever its size, and 128 x NT x 16 takes NT / 2 cycles of tensor-core time: below
+// NT = 128 the kernel is issue-bound, so narrow tiles lose even when they would fill more SMs
+// (measured: K = 8960, N = 1536, M = 512: 74 us at NT = 64 as at NT = 128).
+static int tf_tile_for(int m, long long ntiles) {
   if (m >= 256 && ntiles * ((m + 255) / 256) >= 100) return 256;
   if (m >= 128) return 128;
   return 64;
+}
+int w4a32_gemm_tcf16_tile(int m, int n) { return tf_tile_for(m, (n + kTfTileRows - 1) / kTfTileRows); }
+int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n) {
+  long long t = 0;
+  for (int i = 0; i < count; ++i) t += (n[i] + kTfTileRows - 1) / kTfTileRows;
+  return tf_tile_for(m, t);
 }
 int w4a32_gemm_tcf16_m_pad(int m, int n) {
   const int nt = w4a32_gemm_tcf16_tile(m, n);
@@ -295,25 +310,43 @@ bool w4a32_gemm_tcf16_preferred(int m, int k, int n) {
   return w4a32_gemm_tcf16_supported(m, k, n) && w4a32_gemm_tcf16_tile(m, n) == 256;
 }
 
-cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
-                                    int n, int ldy, cudaStream_t stream) {
-  TfParams prm;
+// Up to four matrices that share x in ONE launch (their 128-row tiles side by side in the grid):
+// the activation blocks must be padded to m_pad = a multiple of the tile width `nt` chosen by
+// w4a32_gemm_tcf16_tile_grouped for the same arguments.
+cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float2* a_hdr, int m, int k, int count,
+                                            const void* const* tiled, float* const* y, const int* n, const int* ldy,
+                                            cudaStream_t stream) {
+  if (count < 1 || count > kTfMaxProblems) return cudaErrorInvalidValue;
+  const int nt = w4a32_gemm_tcf16_tile_grouped(m, count, n);
+  TfParams prm = {};
   prm.a_blocks = a_blocks;
   prm.a_hdr = a_hdr;
-  prm.tiled = static_cast<const uint8_t*>(tiled);
-  prm.y = y;
-  prm.m = m, prm.n = n, prm.k = k, prm.ldy = ldy;
+  prm.m = m, prm.k = k;
   prm.num_groups = (k + kGroup - 1) / kGroup;
-  prm.num_panels = (n + kPanelRows - 1) / kPanelRows;
-  prm.m8_pad = w4a32_gemm_tcf16_m_pad(m, n) / 8;
-  const TiledHeader th = make_tiled_header(n, k, 0, 0);
-  prm.zsum_off = th.zsum_off;
-  prm.bias_off = th.bias_off;
-  switch (w4a32_gemm_tcf16_tile(m, n)) {
-    case 256: return launch_tf_t<256>(prm, stream);
-    case 128: return launch_tf_t<128>(prm, stream);
-    default: return launch_tf_t<64>(prm, stream);
+  prm.m8_pad = (m + nt - 1) / nt * nt / 8;
+  prm.num_problems = count;
+  int tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    const TiledHeader th = make_tiled_header(n[i], k, 0, 0);
+    prm.prob[i].tiled = static_cast<const uint8_t*>(tiled[i]);
+    prm.prob[i].y = y[i];
+    prm.prob[i].n = n[i];
+    prm.prob[i].ldy = ldy[i];
+    prm.prob[i].num_panels = (n[i] + kPanelRows - 1) / kPanelRows;
+    prm.prob[i].tile_begin = tiles;
+    prm.prob[i].bias_off = th.bias_off;
+    tiles += (n[i] + kTfTileRows - 1) / kTfTileRows;
   }
+  switch (nt) {
+    case 256: return launch_tf_t<256>(prm, tiles, stream);
+    case 128: return launch_tf_t<128>(prm, tiles, stream);
+    default: return launch_tf_t<64>(prm, tiles, stream);
+  }
+}
+
+cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
+                                    int n, int ldy, cudaStream_t stream) {
+  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream);
 }
 
 }  // namespace mllmb200
