@@ -477,9 +477,9 @@ def run_gpu(args):
 
         # the same prefill pass with the fp16 tensor-core path (exact fp16 operands, fp32 accumulation over
         # all of K in tensor memory; same 1e-3 * rms bound): kernel 4 everywhere, and kernel 5 = the "fastest"
-        # policy (fp16 path where it clearly wins - gate/up at this M - and the default int8 path elsewhere)
+        # policy (the fp16 path for M >= 128, the default paths below)
         for key, kern_id, label in (("prefill_f16", mb.KERNEL_TC_F16, "tcgen05 kind::f16 on every linear (kernel 4)"),
-                                    ("prefill_fastest", mb.KERNEL_FASTEST, "fastest policy (kernel 5): kind::f16 for gate/up, kind::i8 elsewhere")):
+                                    ("prefill_fastest", mb.KERNEL_FASTEST, "fastest policy (kernel 5): kind::f16 for M >= 128")):
             try:
                 def pf_pass(kern_id=kern_id):
                     for lw in layers[:n_pf_layers]:

@@ -130,8 +130,7 @@ MLLMB200_API int mllmb200_w4a32_linear_forward(const float* x_dev, const void* t
  * 0 auto, 1 streaming GEMV (M <= 4), 2 SIMT dp4a GEMM, 3 tcgen05 kind::i8 GEMM (exact int32 group
  * sums, as the reference), 4 tcgen05 fp16 GEMM (M >= 64: group scales folded into an exact fp16 weight
  * operand, fp32 accumulation over all of K in tensor memory; same 1e-3*rms bound; auto never picks
- * it), 5 fastest: kernel 4 where it clearly wins (M >= 256 and enough 128-row tiles to fill the GPU),
- * else auto. */
+ * it), 5 fastest: kernel 4 for M >= 128, else auto. */
 MLLMB200_API int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, float* y_dev,
                                                   void* ws_dev, int M, int K, int N, int ldx, int ldy,
                                                   int kernel, void* stream);

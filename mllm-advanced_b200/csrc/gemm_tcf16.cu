@@ -64,11 +64,11 @@ template <int NT>
 struct TfSmem {
   // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
   // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
-  static constexpr int kGroups = 2;  // (4 groups per stage with 2 stages was measured slower at NT = 256: 25 vs 22 us)
+  static constexpr int kGroups = NT >= 256 ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
   // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
   // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
   // the number of tiles in flight, so both rings are as deep as shared memory allows.
-  static constexpr int kStages = NT >= 256 ? 4 : (NT >= 128 ? 6 : 7);
+  static constexpr int kStages = NT >= 256 ? 4 : 3;
   static constexpr int kAStages = kStages;  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages)
   static constexpr int kRawBytes = 4 * kGroups * kCellBytes;
   static constexpr int kBBytes = kGroups * NT * 64;
@@ -126,10 +126,6 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(pr.tiled);
-  // 2^E maps the largest |scale| of the matrix into [2^11, 2^12): (u - 8) * s * 2^E < 2^15
-  const int emax = (int)((hdr->max_scale_bits >> 23) & 0xFFu);
-  const int E = emax == 0 ? 0 : 11 - (emax - 127);
-  const float up = exp2f((float)E), down = exp2f((float)-E);
 
   if (warp == kTfDequantWarps) {
     // ------------------------------------------------------------ producer
@@ -193,6 +189,11 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
     const bool have_panel = panel0 + q < pr.num_panels;
     const uint32_t scale_mode = hdr->scale_mode;
+    // 2^E maps the largest |scale| of the matrix into [2^11, 2^12): (u - 8) * s * 2^E < 2^15.
+    // (Read here, not before the role split: the producer must not wait for this load.)
+    const int emax = (int)((hdr->max_scale_bits >> 23) & 0xFFu);
+    const int E = emax == 0 ? 0 : 11 - (emax - 127);
+    const float up = exp2f((float)E), down = exp2f((float)-E);
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
       const int s = it % kStages, sa = it % kTfAStages;
@@ -305,10 +306,9 @@ int w4a32_gemm_tcf16_m_pad(int m, int n) {
 }
 int w4a32_gemm_tcf16_m_pad_max(int m) { return (m + 255) / 256 * 256; }
 bool w4a32_gemm_tcf16_supported(int m, int k, int n) { return m >= 64 && k >= 1 && n >= 1 && (m + 63) / 64 <= 65535; }
-// Shapes on which this path beats the int8 path clearly (wide tiles on a grid that fills the GPU).
-bool w4a32_gemm_tcf16_preferred(int m, int k, int n) {
-  return w4a32_gemm_tcf16_supported(m, k, n) && w4a32_gemm_tcf16_tile(m, n) == 256;
-}
+// Shapes on which this path is at least as fast as the int8 path (measured on the Qwen2-1.5B layer
+// shapes at M = 512: 17 vs 18 us for N = 1536 / 256, 24 vs 60 us for N = 8960, 59 vs 68 us for K = 8960).
+bool w4a32_gemm_tcf16_preferred(int m, int k, int n) { return w4a32_gemm_tcf16_supported(m, k, n) && m >= 128; }
 
 // Up to four matrices that share x in ONE launch (their 128-row tiles side by side in the grid):
 // the activation blocks must be padded to m_pad = a multiple of the tile width `nt` chosen by
