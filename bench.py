@@ -215,6 +215,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # a multi-process launcher pins every rank to one OpenMP thread; this arm runs on rank 0 alone and
+    # is meant to use all the host threads (the variable is read when the OpenMP runtime starts, i.e.
+    # when the kernels' library is loaded below)
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     val, info = time_reference_cpu(budget_s=20.0, steps=None, warmup=max(1, args.warmup))
     if val is None:
         print(json.dumps({"impl": "reference", "unavailable": info["why"]}))
@@ -591,13 +596,16 @@ def run_gpu(args):
                        "how": "per linear: x in pinned host memory -> C-ABI forward -> y in pinned host memory; "
                               "one CUDA graph per step; host synchronizes and reads y every step; host wall clock"}
 
-        # CPU baselines on this box's host cores
-        val, info = time_reference_cpu(budget_s=10.0)
+        # CPU baselines on this box's host cores (single-process runs only: under a multi-process launcher
+        # every rank is pinned to one OpenMP thread, which would misstate the host)
+        val, info = time_reference_cpu(budget_s=10.0) if world == 1 else (None, {})
         if val is not None:
             line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": info["cores"], "kind": "reference",
                                     "sample": info["sample"], "variant": info["variant"],
                                     "ms_per_layer": info["ms_per_layer"]}
         try:
+            if world != 1:
+                raise RuntimeError("single-process runs only")
             pv, pc, pms = time_oracle_port(budget_s=6.0)
             line["cpu_port"] = {"value": pv, "unit": "GB/s", "cores": pc, "kind": "port", "ms_per_layer": pms,
                                 "sample": "same sample on oracle/w4a32_oracle.c (W4A32 format, OpenMP over output rows)"}
@@ -605,6 +613,8 @@ def run_gpu(args):
                 line["cpu_baseline"] = dict(line["cpu_port"])
         except Exception as ex:  # the oracle is optional for the bench
             line["cpu_port"] = {"unavailable": str(ex)[:100]}
+        if "cpu_baseline" not in line:
+            line["cpu_baseline"] = None
         if world == 1 and not args.no_config4:
             try:
                 line["config4"] = run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)
