@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(
       float sc[kAttnMaxGroup];
 #pragma unroll
       for (int i = 0; i < kAttnMaxGroup; ++i) sc[i] = 0.0f;
+#pragma unroll 4
       for (int d = 0; d < D; d += 4) {  // query elements as 16-byte broadcast loads, key elements scalar (padded rows)
         const float k0 = sm.k[lane][d], k1 = sm.k[lane][d + 1], k2 = sm.k[lane][d + 2], k3 = sm.k[lane][d + 3];
 #pragma unroll

@@ -94,12 +94,13 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_quant_kernel(
   }
   const int m = blockIdx.x, tid = threadIdx.x;
   const float* hi = h_in + (size_t)m * hidden;
-  float v[kNormMaxPerThread];
+  float v[kNormMaxPerThread], wv[kNormMaxPerThread];
   float ss = 0.0f;
 #pragma unroll
   for (int i = 0; i < kNormMaxPerThread; ++i) {
     const int k = tid + i * kNormThreads;
     v[i] = 0.0f;
+    wv[i] = k < hidden ? w[k] : 0.0f;  // requested with the row, used after the reduction
     if (k < hidden) {
       v[i] = hi[k] + (delta ? delta[(size_t)m * hidden + k] : 0.0f);
       if (h_out) h_out[(size_t)m * hidden + k] = v[i];
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_quant_kernel(
   for (int i = 0; i < kNormMaxPerThread; ++i) {
     const int k = tid + i * kNormThreads;
     if (k < hidden) {
-      const float y = v[i] * (w[k] * rms);
+      const float y = v[i] * (wv[i] * rms);
       s_y[k] = y;
       if (y_out) y_out[(size_t)m * hidden + k] = y;
       mn = fminf(mn, y);
@@ -222,7 +223,13 @@ __global__ void __launch_bounds__(kCombineThreads) attn_combine_quant_kernel(
     const int h = idx / head_dim, d = idx - h * head_dim;
     const float* po = part_o + (size_t)h * splits * head_dim + d;
     float acc = 0.0f;
-    for (int sidx = 0; sidx < nact; ++sidx) acc = fmaf(s_w[h * splits + sidx], po[(size_t)sidx * head_dim], acc);
+    for (int s0 = 0; s0 < nact; s0 += 8) {  // eight partial rows requested together (no branch between the loads); summed in split order
+      float pv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pv[j] = po[(size_t)min(s0 + j, nact - 1) * head_dim];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(s0 + j < nact ? s_w[h * splits + s0 + j] : 0.0f, pv[j], acc);
+    }
     s_y[idx] = acc;
     if (attn_out) attn_out[idx] = acc;
     mn = fminf(mn, acc);
