@@ -216,7 +216,7 @@ MLLMB200_API int mllmb200_qwen2_set_tables(void* handle, const float* embedding_
 /* Prompt of n tokens (int32 on the device) from an empty cache; samples the next token. */
 MLLMB200_API int mllmb200_qwen2_prefill(void* handle, const int* tokens_dev, int n);
 /* `steps` greedy decode steps, each feeding the previously sampled token (needs a prefill first;
- * position + steps must fit max_ctx).  mode 0 = automatic, 1 = one CUDA graph replay per step (one
+ * position + steps must fit max_ctx).  mode 0 (default) or 1 = one CUDA graph replay per step (one
  * launch per operator), 2 = the persistent kernel: all steps in one cooperative launch of one CTA
  * per SM that streams each CTA's share of the weights through a shared-memory ring
  * (MLLMB200_UNSUPPORTED when the device or the shape does not allow it).  decode == decode_ex(.., 0). */
