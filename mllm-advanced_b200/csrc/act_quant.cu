@@ -299,33 +299,31 @@ __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_qua
   }
   const ActQuantParams p = act_quant_params(mn, mx);
   if (live && lane == 0 && part == 0) hdr[m] = make_float2(p.recip_scale, __int_as_float(-p.nzp));
-  // padding rows (m >= m_total, inside the padded tile) are written as zeros: the tensor core reads them
-  for (int g = part * 32 + lane; g < num_groups; g += 32 * kF16WarpsPerRow) {
-    const int k0 = g * kGroup;
+  // padding rows (m >= m_total, inside the padded tile) are written as zeros: the tensor core reads them.
+  // One thread per (K-group, 8-element chunk): 4 x the parallelism of one thread per group.
+  for (int it = part * 32 + lane; it < num_groups * 4; it += 32 * kF16WarpsPerRow) {
+    const int g = it >> 2, c = it & 3;
+    const int kc = g * kGroup + c * 8;
     uint8_t* blk = blocks + ((size_t)g * m8_pad + (m >> 3)) * 512 + (m & 7) * 16;
+    float f[8];
+    if (live && vec && kc + 8 <= k) {
+      const float4 a = *reinterpret_cast<const float4*>(row + kc);
+      const float4 b = *reinterpret_cast<const float4*>(row + kc + 4);
+      f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+    } else {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float f[8];
-      const int kc = k0 + c * 8;
-      if (live && vec && kc + 8 <= k) {
-        const float4 a = *reinterpret_cast<const float4*>(row + kc);
-        const float4 b = *reinterpret_cast<const float4*>(row + kc + 4);
-        f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = (live && kc + j < k) ? row[kc + j] : 0.0f;
-      }
-      __align__(16) __half h[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // a_q + a_off (= a_q - zero point), |.| <= 255: exact in fp16, and exactly the factor the reference
-        // multiplies the weight with, so no zero-point correction term (and none of its cancellation) is left
-        const int q = (live && kc + j < k) ? act_quant_value(f[j], p) - p.nzp : 0;
-        const int pos = (j < 4) ? 2 * j : 2 * (j - 4) + 1;  // chunk order {0,4,1,5,2,6,3,7}
-        h[pos] = __int2half_rn(q);
-      }
-      *reinterpret_cast<uint4*>(blk + c * 128) = *reinterpret_cast<const uint4*>(h);
+      for (int jj = 0; jj < 8; ++jj) f[jj] = (live && kc + jj < k) ? row[kc + jj] : 0.0f;
     }
+    __align__(16) __half h[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      // a_q + a_off (= a_q - zero point), |.| <= 255: exact in fp16, and exactly the factor the reference
+      // multiplies the weight with, so no zero-point correction term (and none of its cancellation) is left
+      const int q = (live && kc + jj < k) ? act_quant_value(f[jj], p) - p.nzp : 0;
+      const int pos = (jj < 4) ? 2 * jj : 2 * (jj - 4) + 1;  // chunk order {0,4,1,5,2,6,3,7}
+      h[pos] = __int2half_rn(q);
+    }
+    *reinterpret_cast<uint4*>(blk + c * 128) = *reinterpret_cast<const uint4*>(h);
   }
 }
 
