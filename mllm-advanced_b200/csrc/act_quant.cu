@@ -193,11 +193,13 @@ __global__ void __launch_bounds__(8 * kBlocksWarpsPerRow * 32) act_quant_blocks_
   }
   const ActQuantParams p = act_quant_params(mn, mx);
   if (lane == 0 && part == 0) hdr[m] = make_float2(p.recip_scale, __int_as_float(-p.nzp));
-  for (int g = part * 32 + lane; g < num_groups; g += 32 * kBlocksWarpsPerRow) {
-    const int k0 = g * kGroup;
-    uint32_t w[8];  // lo0 hi0 lo1 hi1 | lo2 hi2 lo3 hi3 : the two 16-byte K chunks of this row
+  // one thread per (K-group, 16-byte K chunk): twice the parallelism of one thread per group
+  for (int it = part * 32 + lane; it < num_groups * 2; it += 32 * kBlocksWarpsPerRow) {
+    const int g = it >> 1, c = it & 1;
+    const int k0 = g * kGroup + c * 16;
+    uint32_t w[4];  // lo hi lo hi: the chunk's 16 elements in the order the nibble masks produce
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       float f[8];
       if (vec && k0 + i * 8 + 8 <= k) {
         const float4 a = *reinterpret_cast<const float4*>(row + k0 + i * 8);
@@ -218,8 +220,7 @@ __global__ void __launch_bounds__(8 * kBlocksWarpsPerRow * 32) act_quant_blocks_
       w[2 * i + 1] = hi;
     }
     uint8_t* blk = blocks + ((size_t)g * m8_pad + (m >> 3)) * 256 + (m & 7) * 16;
-    *reinterpret_cast<uint4*>(blk) = make_uint4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<uint4*>(blk + 128) = make_uint4(w[4], w[5], w[6], w[7]);
+    *reinterpret_cast<uint4*>(blk + c * 128) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
