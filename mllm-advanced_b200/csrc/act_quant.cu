@@ -250,8 +250,8 @@ __global__ void __launch_bounds__(256) act_quant_reflayout_kernel(const float* _
 // are written as fp16 (exact) in 512-byte canonical K-major blocks [group][row / 8]: 4 chunks of 128 bytes, chunk c =
 // 8 rows x 16 bytes holding k = 8c + {0,4,1,5,2,6,3,7} - the order in which the weight side's
 // nibble unpack (two nibbles 16 bits apart per half2) produces its elements.
-constexpr int kF16RowsPerCta = 2;   // rows 2i and 2i+1 sit side by side in a block: 32-byte pieces
-constexpr int kF16WarpsPerRow = 16;
+constexpr int kF16RowsPerCta = 4;   // rows 4i .. 4i+3 sit side by side in a block: 64-byte pieces
+constexpr int kF16WarpsPerRow = 8;
 __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_quant_blocks_f16_kernel(
     const float* __restrict__ x, int m_total, int k, int ldx, int num_groups, int m8_pad, uint8_t* __restrict__ blocks,
     float2* __restrict__ hdr) {
