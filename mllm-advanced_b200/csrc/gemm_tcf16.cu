@@ -42,8 +42,7 @@ namespace mllmb200 {
 
 constexpr int kTfDequantWarps = 8;  // warps w and w + 4 share the weight rows 32 (w % 4)..; each takes one K-group of a stage
 constexpr int kTfThreads = (kTfDequantWarps + 2) * 32;
-constexpr int kTfTileRows = 128;
-constexpr int kTfGroupABytes = kTfTileRows * kGroup * 2;  // 8192: one K-group of the A operand
+constexpr int kTfTileRows = 128;   // weight rows per MMA (tensor-memory lanes); a CTA tile is ROWS = 128 or 256 of them
 
 constexpr int kTfMaxProblems = 4;
 struct TfProblem {          // one weight matrix of a launch; all problems share x (M, K, the activation blocks)
@@ -60,29 +59,36 @@ struct TfParams {
   TfProblem prob[kTfMaxProblems];
 };
 
-template <int NT>
+template <int NT, int ROWS>
 struct TfSmem {
   // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
   // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
-  static constexpr int kGroups = NT >= 256 ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
+  static constexpr int kGroups = (NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
   // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
   // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
   // the number of tiles in flight, so both rings are as deep as shared memory allows.
-  static constexpr int kStages = NT >= 256 ? 4 : 3;
+  static constexpr int kStages = (NT >= 256 && ROWS == 128) ? 4 : 3;
   static constexpr int kAStages = kStages;  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages)
-  static constexpr int kRawBytes = 4 * kGroups * kCellBytes;
+  static constexpr int kPanels = ROWS / kPanelRows;
+  static constexpr int kGroupABytes = ROWS * kGroup * 2;  // one K-group of the A operand (8 or 16 KB)
+  static constexpr int kRawBytes = kPanels * kGroups * kCellBytes;
   static constexpr int kBBytes = kGroups * NT * 64;
   static constexpr int kStageBytes = kRawBytes + kBBytes;
-  static constexpr int kABytes = kGroups * kTfGroupABytes;
+  static constexpr int kABytes = kGroups * kGroupABytes;
   static constexpr int kBarBytes = 256;
   static constexpr int kHdrBytes = NT * 8;  // {lhs_scale, a_off} of the tile's activation rows
   static constexpr int kAOffset = kBarBytes + kHdrBytes + kStages * kStageBytes;
   static constexpr int kTotal = kAOffset + kAStages * kABytes + 1024;
+  static_assert(kTotal <= 227 * 1024, "shared memory");
 };
 
-template <int NT>
+// ROWS = 256: two 128-row accumulators side by side in tensor memory share every activation block
+// that is loaded - the activation (B) operand is re-read from L2 once per weight tile, which bounds
+// the 128-row tile on large grids.
+template <int NT, int ROWS>
 __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const TfParams p) {
-  using S = TfSmem<NT>;
+  using S = TfSmem<NT, ROWS>;
+  constexpr int kPanels = S::kPanels, kHalves = ROWS / kTfTileRows, kTfGroupABytes = S::kGroupABytes;
   constexpr int kStages = S::kStages, kTfAStages = S::kAStages, kTfGroupsPerStage = S::kGroups;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -103,9 +109,9 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     if (i < p.num_problems && (int)blockIdx.x >= p.prob[i].tile_begin) pi = i;
   const TfProblem& pr = p.prob[pi];
   const int tile_n = (int)blockIdx.x - pr.tile_begin, tile_m = blockIdx.y;
-  const int panel0 = tile_n * 4, m0 = tile_m * NT;
+  const int panel0 = tile_n * kPanels, m0 = tile_m * NT;
   const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
-  constexpr uint32_t kTmemCols = NT < 32 ? 32 : NT;
+  constexpr uint32_t kTmemCols = (uint32_t)(kHalves * NT) < 32u ? 32u : (uint32_t)(kHalves * NT);
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -129,7 +135,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
 
   if (warp == kTfDequantWarps) {
     // ------------------------------------------------------------ producer
-    const int np = min(4, pr.num_panels - panel0);
+    const int np = min(kPanels, pr.num_panels - panel0);
     for (int it = 0; it < k_tiles; ++it) {
       const int s = it % kStages;
       const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -143,8 +149,8 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
         bulk_g2s(st + lane * kTfGroupsPerStage * kCellBytes,
                  pr.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCellBytes,
                  (uint32_t)(ng * kCellBytes), &raw_full[s]);
-      } else if (lane >= 4 && lane < 4 + ng) {
-        const int g = lane - 4;
+      } else if (lane >= kPanels && lane < kPanels + ng) {
+        const int g = lane - kPanels;
         bulk_g2s(st + S::kRawBytes + g * NT * 64, p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 512,
                  (uint32_t)(NT * 64), &raw_full[s]);
       }
@@ -173,8 +179,11 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
           if (g >= ng) break;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {  // K = 16 per instruction: two chunks of 8; the start address counts 16-byte units
-            tc_mma_f16(tmem_base, a_desc + (uint64_t)((g * kTfGroupABytes + h * 256) >> 4),
-                       b_desc + (uint64_t)((g * NT * 64 + h * 256) >> 4), idesc, accumulate);
+#pragma unroll
+            for (int rh = 0; rh < kHalves; ++rh)  // 128-row halves of the tile: own accumulator (NT columns each), same B
+              tc_mma_f16(tmem_base + (uint32_t)(rh * NT),
+                         a_desc + (uint64_t)((g * kTfGroupABytes + rh * (kTfTileRows * 64) + h * 256) >> 4),
+                         b_desc + (uint64_t)((g * NT * 64 + h * 256) >> 4), idesc, accumulate);
             accumulate = 1;
           }
         }
@@ -183,9 +192,11 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       if (ok) tc_commit(acc_done);
     }
   } else {
-    // ------------------------------------------------------------ dequant: thread j = weight row j of the tile,
-    // K-group (warp / 4) of every stage
-    const int j = tid & 127, gsel = warp >> 2;
+    // ------------------------------------------------------------ dequant: thread j = weight row j of the tile.
+    // ROWS = 128: rows are shared by warps w and w + 4, which alternate over the K-groups of a stage;
+    // ROWS = 256: one row per thread, every group.
+    const int j = ROWS == 128 ? (tid & 127) : tid;
+    const int gsel = ROWS == 128 ? (warp >> 2) : 0, gstep = ROWS == 128 ? kTfDequantWarps / 4 : 1;
     const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
     const bool have_panel = panel0 + q < pr.num_panels;
     const uint32_t scale_mode = hdr->scale_mode;
@@ -207,7 +218,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       const uint8_t* raw = stages + (size_t)s * S::kStageBytes + q * kTfGroupsPerStage * kCellBytes;
       uint8_t* a_out = a_stages + (size_t)sa * S::kABytes + (j >> 3) * 512 + (j & 7) * 16;
 #pragma unroll
-      for (int g = gsel; g < kTfGroupsPerStage; g += kTfDequantWarps / 4) {  // the two warp quartets alternate over the groups
+      for (int g = gsel; g < kTfGroupsPerStage; g += gstep) {
         if (g < ng) {
         uint4 w = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
         float sc = 0.0f;
@@ -239,24 +250,27 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     // tensor-memory loads are warp-wide: every lane takes part, only the stores are guarded
     ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(acc_done, 0));
     tc_fence_after();
-    const int n = tile_n * kTfTileRows + j;
-    const bool live = n < pr.n;
-    const float bs = live ? reinterpret_cast<const float*>(pr.tiled + pr.bias_off)[n] : 0.0f;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const int col_begin = (warp >> 2) * (NT / 2), col_end = col_begin + NT / 2;  // warps w and w + 4 split the columns
-    if (ok) {
 #pragma unroll 1
-      for (int c0 = col_begin; c0 < col_end && m0 + c0 < p.m; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(lane_addr + (uint32_t)c0, v);
-        tmem_ld_wait();
+    for (int rh = 0; rh < kHalves; ++rh) {  // the 128-row halves of the tile: accumulators NT columns apart
+      const int n = tile_n * ROWS + rh * kTfTileRows + (warp & 3) * 32 + lane;
+      const bool live = n < pr.n;
+      const float bs = live ? reinterpret_cast<const float*>(pr.tiled + pr.bias_off)[n] : 0.0f;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(rh * NT);
+      if (ok) {
+#pragma unroll 1
+        for (int c0 = col_begin; c0 < col_end && m0 + c0 < p.m; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(lane_addr + (uint32_t)c0, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int m = m0 + c0 + i;
-          if (live && m < p.m) {
-            const float2 h = s_hdr[c0 + i];
-            const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
-            pr.y[(size_t)m * pr.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+          for (int i = 0; i < 16; ++i) {
+            const int m = m0 + c0 + i;
+            if (live && m < p.m) {
+              const float2 h = s_hdr[c0 + i];
+              const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
+              pr.y[(size_t)m * pr.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+            }
           }
         }
       }
@@ -270,36 +284,50 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   }
 }
 
-template <int NT>
+template <int NT, int ROWS>
 static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_t stream) {
-  using S = TfSmem<NT>;
+  using S = TfSmem<NT, ROWS>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const dim3 grid((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
-  w4a32_gemm_tcf16_kernel<NT><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
+  w4a32_gemm_tcf16_kernel<NT, ROWS><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
   return cudaGetLastError();
 }
 
-// Activation rows per tile for `ntiles` 128-row weight tiles (of all matrices of the launch together):
-// the widest tile whose grid still covers most of the SMs.  A tcgen05.mma costs its issuing thread
-// ~100 cycles whatever its size, and 128 x NT x 16 takes NT / 2 cycles of tensor-core time: below
-// NT = 128 the kernel is issue-bound, so narrow tiles lose even when they would fill more SMs
-// (measured: K = 8960, N = 1536, M = 512: 74 us at NT = 64 as at NT = 128).
-static int tf_tile_for(int m, long long ntiles) {
-  if (m >= 256 && ntiles * ((m + 255) / 256) >= 100) return 256;
-  if (m >= 128) return 128;
-  return 64;
+// Tile shape for a launch: weight rows per CTA (128, or 256 = two accumulators sharing every loaded
+// activation block) and activation rows per tile.  A tcgen05.mma costs its issuing thread ~100
+// cycles whatever its size and 128 x NT x 16 takes NT / 2 cycles of tensor-core time, so narrow
+// activation tiles are issue-bound (measured: K = 8960, N = 1536, M = 512: 74 us at NT = 64 as at 128);
+// on grids that fill the GPU the 128-row tile is bound by L2 traffic for the activation operand,
+// which every weight tile re-reads - the 256-row tile halves it (config 4, M = 2048: 974 -> 1014 TFLOP/s;
+// with 8 MMAs per K-tile the issuing thread is then the limit).
+struct TfTile {
+  int rows, nt;
+};
+static TfTile tf_tile_for(int m, int count, const int* n) {
+  long long t128 = 0, t256 = 0;
+  bool wide = true;  // 256-row tiles only for matrices with at least 4096 rows
+  for (int i = 0; i < count; ++i) {
+    t128 += (n[i] + 127) / 128;
+    t256 += (n[i] + 255) / 256;
+    wide = wide && n[i] >= 4096;
+  }
+  TfTile t;
+  if (wide && m >= 256 && t256 * ((m + 255) / 256) >= 100) {  // (256 rows x 128: measured slower than 128 x 256, 31 vs 24 us)
+    t.rows = 256;
+    t.nt = 256;
+    return t;
+  }
+  t.rows = 128;
+  t.nt = (m >= 256 && t128 * ((m + 255) / 256) >= 100) ? 256 : (m >= 128 ? 128 : 64);
+  return t;
 }
-int w4a32_gemm_tcf16_tile(int m, int n) { return tf_tile_for(m, (n + kTfTileRows - 1) / kTfTileRows); }
-int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n) {
-  long long t = 0;
-  for (int i = 0; i < count; ++i) t += (n[i] + kTfTileRows - 1) / kTfTileRows;
-  return tf_tile_for(m, t);
-}
+int w4a32_gemm_tcf16_tile(int m, int n) { return tf_tile_for(m, 1, &n).nt; }
+int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n) { return tf_tile_for(m, count, n).nt; }
 int w4a32_gemm_tcf16_m_pad(int m, int n) {
   const int nt = w4a32_gemm_tcf16_tile(m, n);
   return (m + nt - 1) / nt * nt;
@@ -310,14 +338,15 @@ bool w4a32_gemm_tcf16_supported(int m, int k, int n) { return m >= 64 && k >= 1 
 // shapes at M = 512: 17 vs 18 us for N = 1536 / 256, 24 vs 60 us for N = 8960, 59 vs 68 us for K = 8960).
 bool w4a32_gemm_tcf16_preferred(int m, int k, int n) { return w4a32_gemm_tcf16_supported(m, k, n) && m >= 128; }
 
-// Up to four matrices that share x in ONE launch (their 128-row tiles side by side in the grid):
-// the activation blocks must be padded to m_pad = a multiple of the tile width `nt` chosen by
+// Up to four matrices that share x in ONE launch (their weight tiles side by side in the grid):
+// the activation blocks must be padded to m_pad = a multiple of the tile width chosen by
 // w4a32_gemm_tcf16_tile_grouped for the same arguments.
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float2* a_hdr, int m, int k, int count,
                                             const void* const* tiled, float* const* y, const int* n, const int* ldy,
                                             cudaStream_t stream) {
   if (count < 1 || count > kTfMaxProblems) return cudaErrorInvalidValue;
-  const int nt = w4a32_gemm_tcf16_tile_grouped(m, count, n);
+  const TfTile tile = tf_tile_for(m, count, n);
+  const int nt = tile.nt;
   TfParams prm = {};
   prm.a_blocks = a_blocks;
   prm.a_hdr = a_hdr;
@@ -335,12 +364,13 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
     prm.prob[i].num_panels = (n[i] + kPanelRows - 1) / kPanelRows;
     prm.prob[i].tile_begin = tiles;
     prm.prob[i].bias_off = th.bias_off;
-    tiles += (n[i] + kTfTileRows - 1) / kTfTileRows;
+    tiles += (n[i] + tile.rows - 1) / tile.rows;
   }
+  if (tile.rows == 256) return launch_tf_t<256, 256>(prm, tiles, stream);
   switch (nt) {
-    case 256: return launch_tf_t<256>(prm, tiles, stream);
-    case 128: return launch_tf_t<128>(prm, tiles, stream);
-    default: return launch_tf_t<64>(prm, tiles, stream);
+    case 256: return launch_tf_t<256, 128>(prm, tiles, stream);
+    case 128: return launch_tf_t<128, 128>(prm, tiles, stream);
+    default: return launch_tf_t<64, 128>(prm, tiles, stream);
   }
 }
 
