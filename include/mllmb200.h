@@ -188,6 +188,45 @@ MLLMB200_API int mllmb200_conv3d_w4a32_forward(const float* x_dev, const void* t
                                                void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * W4A16 sibling path.  Stands in for KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk
+ * (mllm/Backends/Arm/Kernels/kai_linear.cpp:680-951; op dispatch mllm/Backends/Arm/Ops/LinearOp.cpp:135-190,
+ * output dtype fp16 per LinearOp.cpp:246-251; impl types 9-11 of mllm/Core/AOps/LinearOp.hpp:28-30):
+ * asymmetric int4 weights in groups of 32 along K with an fp32 scale and an fp32 zero term per group,
+ * activations (fp32 or fp16) quantized inside the call to symmetric int8 per 32-element block with an
+ * fp32 scale, fp16 output clamped to +-65504:
+ *   y[m,n] = fp16( sum_b a_s[m,b] * ( s[n,b] * float(sum_{k in b} a_q[m,k] (u[n,k]-8))
+ *                                   + z[n,b] * float(sum_{k in b} a_q[m,k]) ) + bias[n] )
+ *
+ *   prepack_size / quant_prepack (host)  quant_pack_rhs_size / quant_pack_rhs_offline + quant_nxk_qai4c32_f32
+ *                                        (kai_linear.cpp:700-851).  Blob: the 64-byte header of the W4A32
+ *                                        blob with layout = 1, then nibbles u8 [N][ceil(K/2)] (q+8, EVEN k in
+ *                                        the HIGH half-byte, kai_linear.cpp:807-816), scales f32 [N][ceil(K/32)],
+ *                                        zeros f32 [N][ceil(K/32)] (= -zero_point*scale, kai_linear.cpp:797-805),
+ *                                        bias f32 [N] when present; sections 16-byte aligned, bit-identical to
+ *                                        what quant_nxk_qai4c32_f32 produces.
+ *   tiled_size / repack_device           the KleidiAI packing step kai_run_rhs_pack_nxk_qai4c32p_qau4c32s0s1_
+ *                                        f32_f32_f32_neon (call site kai_linear.cpp:845-847), on the GPU at
+ *                                        load time; a row range gives a tensor-parallel shard.
+ *   workspace_size / linear_forward      workspace_size + matmul (kai_linear.cpp:680-698, 853-951), both the
+ *                                        fp32 and the fp16 activation overloads (x_dtype).
+ * x_dev: [M, ldx] of x_dtype; y_dev: fp16 [M, ldy]; ws_dev: workspace_size bytes, 256-byte aligned.
+ * ------------------------------------------------------------------------------------------ */
+#define MLLMB200_DTYPE_F32 0
+#define MLLMB200_DTYPE_F16 1
+
+MLLMB200_API int mllmb200_w4a16_prepack_size(int N, int K, int has_bias, size_t* bytes);
+MLLMB200_API int mllmb200_w4a16_quant_prepack(const float* W, const float* bias, int N, int K, void* blob);
+MLLMB200_API int mllmb200_w4a16_blob_info(const void* blob, size_t blob_bytes, int* N, int* K, int* has_bias);
+MLLMB200_API int mllmb200_w4a16_blob_offsets(int N, int K, int has_bias, size_t* nibbles_off, size_t* scales_off,
+                                             size_t* zeros_off, size_t* bias_off);
+MLLMB200_API int mllmb200_w4a16_tiled_size(int N_rows, int K, size_t* bytes);
+MLLMB200_API int mllmb200_w4a16_repack_device(const void* blob_dev, int N, int K, int has_bias, int row_begin,
+                                              int row_count, void* tiled_dev, void* stream);
+MLLMB200_API int mllmb200_w4a16_workspace_size(int M, int K, int N, size_t* bytes);
+MLLMB200_API int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, const void* tiled_dev, void* y_dev,
+                                               void* ws_dev, int M, int K, int N, int ldx, int ldy, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Decoder: the Qwen2-architecture language model whose linears are the W4A32 op above
  * (reference project: mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:47-54,106-155,175-215, greedy loop
  * mllm/Models/AutoLLM.hpp:39-105).  Batch 1, fp32 activations and KV cache, fp16 lm_head, greedy

@@ -39,6 +39,7 @@ static int cuda_fail(cudaError_t e) {
   t_last_cuda_error = (int)e;
   return MLLMB200_CUDA_ERROR;
 }
+int record_cuda_failure(cudaError_t e) { return cuda_fail(e); }  // for the other C-ABI translation units
 // workspace = [quantized activations][row headers: M * 8 bytes], each 256-aligned.  The first part
 // holds either 48-byte records (GEMV, SIMT GEMM) or 256-byte operand blocks over rows padded to
 // the tcgen05 tile (tcgen05 GEMM); it is sized for the larger of the two.

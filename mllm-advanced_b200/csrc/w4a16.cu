@@ -1,0 +1,301 @@
+// W4A16 sibling of the quantized linear: asymmetric int4 weights (fp32 scale + fp32 zero term per group of
+// 32), activations quantized per 32-element block to symmetric int8 with an fp32 scale, fp16 output.
+// Stands in for KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk (reference project:
+// mllm/Backends/Arm/Kernels/kai_linear.cpp:680-951):
+//   y[m,n] = fp16( clamp( sum_b a_s[m,b] * ( s[n,b] * float(dot_b) + z[n,b] * float(sum_b) ) + bias[n] ) )
+//   dot_b = sum_{k in b} a_q[m,k] * (u[n,k] - 8),  sum_b = sum_{k in b} a_q[m,k]
+// Kernels: repack (blob -> 768-byte cells), activation quantization (48-byte records), and one dp4a
+// kernel for every M: a CTA owns one 32-row panel (lane = output row) and MT rows of x, its 8 warps split
+// the K groups, partial sums meet in shared memory; for small grids K is also split over gridDim.z with
+// fp32 partials in the workspace and a finishing kernel that adds them in slice order (deterministic).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/mllmb200.h"
+#include "device_common.cuh"
+#include "layout_a16.h"
+
+namespace mllmb200 {
+
+// ------------------------------------------------------------------ repack
+// One warp per (panel, group) cell, lane = row of the panel.
+__global__ void a16_repack_cells_kernel(const uint8_t* __restrict__ nib, const float* __restrict__ scales,
+                                        const float* __restrict__ zeros, int k, int row_begin, int row_count,
+                                        int num_groups, int num_panels, uint8_t* __restrict__ cells) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= num_panels * num_groups) return;
+  const int panel = warp / num_groups, g = warp % num_groups;
+  const int r = panel * kPanelRows + lane;
+  const bool row_ok = r < row_count;
+  const size_t stride = (size_t)(k + 1) / 2;
+  const size_t src_row = (size_t)(row_begin + r);
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kk = g * kGroup + (i * 4 + j) * 2;  // even k of this byte
+      uint32_t lo = 8, hi = 8;                       // padding: weight 0
+      if (row_ok && kk < k) {
+        const uint32_t b = nib[src_row * stride + (size_t)(kk >> 1)];
+        lo = b >> 4;  // the blob keeps the even k in the high half
+        if (kk + 1 < k) hi = b & 15u;
+      }
+      word |= (lo | (hi << 4)) << (8 * j);
+    }
+    w[i] = word;
+  }
+  uint8_t* cell = cells + (size_t)warp * kCellBytesA16;
+  reinterpret_cast<uint4*>(cell)[lane] = make_uint4(w[0], w[1], w[2], w[3]);
+  float s = 0.0f, z = 0.0f;
+  if (row_ok) {
+    s = scales[src_row * num_groups + g];
+    z = zeros[src_row * num_groups + g];
+  }
+  reinterpret_cast<float*>(cell + kCellNibbleBytes)[lane] = s;
+  reinterpret_cast<float*>(cell + kCellNibbleBytes + kPanelRows * 4)[lane] = z;
+}
+
+__global__ void a16_repack_bias_kernel(const float* __restrict__ bias, int row_begin, int row_count, int padded,
+                                       float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < padded) out[i] = (bias && i < row_count) ? bias[row_begin + i] : 0.0f;
+}
+
+// ------------------------------------------------------------------ activation quantization
+// grid (ceil(groups / 32), M), 256 threads: a warp takes 4 groups, 8 lanes per group, 4 consecutive k per lane.
+template <typename T>
+__device__ __forceinline__ float a16_load(const T* p);
+template <>
+__device__ __forceinline__ float a16_load<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float a16_load<__half>(const __half* p) { return __half2float(*p); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) a16_act_quant_kernel(const T* __restrict__ x, int k, int ldx, int num_groups,
+                                                            uint8_t* __restrict__ recs) {
+  const int m = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = blockIdx.x * 32 + warp * 4 + (lane >> 3);
+  const int j = lane & 7;  // which 4 of the group's 32 elements
+  const T* row = x + (size_t)m * ldx;
+  float v[4];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int kk = g * kGroup + j * 4 + i;
+    v[i] = (g < num_groups && kk < k) ? a16_load<T>(row + kk) : 0.0f;
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = __fdiv_rn(amax, 127.0f);
+  const float recip = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+  int q[4], sum = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float r = roundf(__fmul_rn(v[i], recip));  // half away from zero
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    q[i] = (int)r;
+    sum += q[i];
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  // this lane: k = 4j..4j+3 of the group -> even k {0,2} and odd k {1,3} halves of word j/2 and word 4 + j/2
+  const uint32_t ev = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[2] & 0xff) << 8);
+  const uint32_t od = (uint32_t)(q[1] & 0xff) | ((uint32_t)(q[3] & 0xff) << 8);
+  const uint32_t ev_p = __shfl_xor_sync(0xffffffffu, ev, 1), od_p = __shfl_xor_sync(0xffffffffu, od, 1);
+  if (g >= num_groups) return;
+  uint32_t* rec = reinterpret_cast<uint32_t*>(recs + ((size_t)m * num_groups + g) * kActRecordBytesA16);
+  if ((j & 1) == 0) rec[j >> 1] = ev | (ev_p << 16);
+  else rec[4 + (j >> 1)] = od_p | (od << 16);
+  if (j == 0) {
+    rec[8] = (uint32_t)sum;
+    rec[9] = __float_as_uint(scale);
+  }
+}
+
+// ------------------------------------------------------------------ linear
+__device__ __forceinline__ int a16_dot(const uint4& nw, const uint4& r0, const uint4& r1) {
+  int d = 0;
+  d = __dp4a((int)(nw.x & 0x0F0F0F0Fu), (int)r0.x, d);
+  d = __dp4a((int)(nw.y & 0x0F0F0F0Fu), (int)r0.y, d);
+  d = __dp4a((int)(nw.z & 0x0F0F0F0Fu), (int)r0.z, d);
+  d = __dp4a((int)(nw.w & 0x0F0F0F0Fu), (int)r0.w, d);
+  d = __dp4a((int)((nw.x >> 4) & 0x0F0F0F0Fu), (int)r1.x, d);
+  d = __dp4a((int)((nw.y >> 4) & 0x0F0F0F0Fu), (int)r1.y, d);
+  d = __dp4a((int)((nw.z >> 4) & 0x0F0F0F0Fu), (int)r1.z, d);
+  d = __dp4a((int)((nw.w >> 4) & 0x0F0F0F0Fu), (int)r1.w, d);
+  return d;
+}
+
+struct A16Cell {
+  uint4 nw;
+  float s, z;
+};
+__device__ __forceinline__ A16Cell a16_load_cell(const uint8_t* cell, int lane) {
+  A16Cell c;
+  c.nw = __ldg(reinterpret_cast<const uint4*>(cell) + lane);
+  c.s = __ldg(reinterpret_cast<const float*>(cell + kCellNibbleBytes) + lane);
+  c.z = __ldg(reinterpret_cast<const float*>(cell + kCellNibbleBytes + kPanelRows * 4) + lane);
+  return c;
+}
+
+// grid (panels, ceil(M / MT), ksplit), 256 threads.  partial == nullptr: finish here (bias, clamp, fp16).
+template <int MT>
+__global__ void __launch_bounds__(256) a16_linear_kernel(const uint8_t* __restrict__ tiled,
+                                                         const uint8_t* __restrict__ recs, int m, int k, int n,
+                                                         int groups_per_slice, __half* __restrict__ y, int ldy,
+                                                         float* __restrict__ partial, int n_pad) {
+  __shared__ float red[8][MT][32];
+  const TiledHeaderA16* hdr = reinterpret_cast<const TiledHeaderA16*>(tiled);
+  if (hdr->magic != kTiledMagicA16 || hdr->n != (uint32_t)n || hdr->k != (uint32_t)k) {
+    if (threadIdx.x == 0) atomicOr(&g_device_status, kDevStatusBadHeader);
+    return;
+  }
+  const int nb = (int)hdr->num_groups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int panel = blockIdx.x, m0 = blockIdx.y * MT;
+  const int g_begin = blockIdx.z * groups_per_slice;
+  const int g_end = min(nb, g_begin + groups_per_slice);
+  const uint8_t* cells = tiled + hdr->cells_off + (size_t)panel * nb * kCellBytesA16;
+
+  float acc[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
+
+  int g = g_begin + warp;
+  A16Cell cur;
+  if (g < g_end) cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
+  for (; g < g_end; g += 8) {
+    A16Cell nxt = cur;
+    if (g + 8 < g_end) nxt = a16_load_cell(cells + (size_t)(g + 8) * kCellBytesA16, lane);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const int row = m0 + i;
+      if (row < m) {  // uniform over the CTA
+        const uint4* rec = reinterpret_cast<const uint4*>(recs + ((size_t)row * nb + g) * kActRecordBytesA16);
+        const uint4 r0 = __ldg(rec), r1 = __ldg(rec + 1);
+        const uint2 r2 = __ldg(reinterpret_cast<const uint2*>(rec + 2));
+        const int asum = (int)r2.x;
+        const int dot = a16_dot(cur.nw, r0, r1) - 8 * asum;
+        const float t = fmaf(cur.s, (float)dot, cur.z * (float)asum);
+        acc[i] = fmaf(__uint_as_float(r2.y), t, acc[i]);
+      }
+    }
+    cur = nxt;
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i) red[warp][i][lane] = acc[i];
+  __syncthreads();
+  const int col = panel * kPanelRows;
+  for (int idx = threadIdx.x; idx < MT * 32; idx += 256) {
+    const int i = idx >> 5, l = idx & 31, row = m0 + i;
+    if (row >= m) continue;
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w][i][l];
+    if (partial) {
+      partial[((size_t)blockIdx.z * m + row) * n_pad + col + l] = s;
+    } else if (col + l < n) {
+      const float* bias = reinterpret_cast<const float*>(tiled + hdr->bias_off);
+      s += bias[col + l];
+      s = fminf(fmaxf(s, -65504.0f), 65504.0f);
+      y[(size_t)row * ldy + col + l] = __float2half_rn(s);
+    }
+  }
+}
+
+__global__ void a16_finish_kernel(const float* __restrict__ partial, const uint8_t* __restrict__ tiled, int slices,
+                                  int m, int n, int n_pad, __half* __restrict__ y, int ldy) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (col >= n) return;
+  const TiledHeaderA16* hdr = reinterpret_cast<const TiledHeaderA16*>(tiled);
+  float s = 0.0f;
+  for (int z = 0; z < slices; ++z) s += partial[((size_t)z * m + row) * n_pad + col];
+  s += reinterpret_cast<const float*>(tiled + hdr->bias_off)[col];
+  s = fminf(fmaxf(s, -65504.0f), 65504.0f);
+  y[(size_t)row * ldy + col] = __float2half_rn(s);
+}
+
+// ------------------------------------------------------------------ host side
+static inline int a16_mt(int m) { return m >= 16 ? 16 : m >= 8 ? 8 : m >= 4 ? 4 : m >= 2 ? 2 : 1; }
+
+// K slices: enough CTAs for two per SM when the (panel, row-tile) grid is small; a slice keeps >= 8 groups.
+int a16_slices(int m, int k, int n) {
+  const int nb = (int)blob_num_blocks(k), panels = (n + kPanelRows - 1) / kPanelRows;
+  const int mt = a16_mt(m), ctas = panels * ((m + mt - 1) / mt);
+  if (ctas >= 148) return 1;
+  int s = (296 + ctas - 1) / ctas;
+  s = min(s, max(1, nb / 8));
+  return min(s, 8);
+}
+
+size_t a16_workspace_bytes(int m, int k, int n) {
+  const size_t rec = align_up((size_t)m * blob_num_blocks(k) * kActRecordBytesA16, 256);
+  const int s = a16_slices(m, k, n);
+  const size_t n_pad = (size_t)((n + kPanelRows - 1) / kPanelRows) * kPanelRows;
+  return rec + (s > 1 ? align_up((size_t)s * m * n_pad * 4, 256) : 0);
+}
+
+template <int MT>
+static cudaError_t a16_launch_mt(const uint8_t* tiled, const uint8_t* recs, int m, int k, int n, __half* y, int ldy,
+                                 float* partial, int slices, cudaStream_t st) {
+  const int nb = (int)blob_num_blocks(k), panels = (n + kPanelRows - 1) / kPanelRows;
+  const int gps = (nb + slices - 1) / slices;
+  dim3 grid(panels, (m + MT - 1) / MT, slices);
+  a16_linear_kernel<MT><<<grid, 256, 0, st>>>(tiled, recs, m, k, n, gps, y, ldy, slices > 1 ? partial : nullptr,
+                                              panels * kPanelRows);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, void* y, void* ws, int m, int k, int n,
+                                int ldx, int ldy, cudaStream_t st) {
+  const int nb = (int)blob_num_blocks(k);
+  uint8_t* recs = static_cast<uint8_t*>(ws);
+  float* partial =
+      reinterpret_cast<float*>(recs + align_up((size_t)m * nb * kActRecordBytesA16, 256));
+  dim3 qgrid((nb + 31) / 32, m);
+  if (x_dtype == 1) a16_act_quant_kernel<__half><<<qgrid, 256, 0, st>>>(static_cast<const __half*>(x), k, ldx, nb, recs);
+  else a16_act_quant_kernel<float><<<qgrid, 256, 0, st>>>(static_cast<const float*>(x), k, ldx, nb, recs);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int slices = a16_slices(m, k, n);
+  const uint8_t* t = static_cast<const uint8_t*>(tiled);
+  __half* yh = static_cast<__half*>(y);
+  switch (a16_mt(m)) {
+    case 16: e = a16_launch_mt<16>(t, recs, m, k, n, yh, ldy, partial, slices, st); break;
+    case 8: e = a16_launch_mt<8>(t, recs, m, k, n, yh, ldy, partial, slices, st); break;
+    case 4: e = a16_launch_mt<4>(t, recs, m, k, n, yh, ldy, partial, slices, st); break;
+    case 2: e = a16_launch_mt<2>(t, recs, m, k, n, yh, ldy, partial, slices, st); break;
+    default: e = a16_launch_mt<1>(t, recs, m, k, n, yh, ldy, partial, slices, st); break;
+  }
+  if (e != cudaSuccess || slices == 1) return e;
+  const int n_pad = (n + kPanelRows - 1) / kPanelRows * kPanelRows;
+  a16_finish_kernel<<<dim3((n + 255) / 256, m), 256, 0, st>>>(partial, t, slices, m, n, n_pad, yh, ldy);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_w4a16_repack(const void* blob_dev, int n, int k, int has_bias, int row_begin, int row_count,
+                                void* tiled_dev, cudaStream_t st) {
+  const BlobHeader bh = make_blob_header_a16(n, k, has_bias);
+  const TiledHeaderA16 th = make_tiled_header_a16(row_count, k, has_bias);
+  cudaError_t e = cudaMemcpyAsync(tiled_dev, &th, sizeof(th), cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return e;
+  const uint8_t* b = static_cast<const uint8_t*>(blob_dev);
+  uint8_t* t = static_cast<uint8_t*>(tiled_dev);
+  const int cells = (int)(th.num_panels * th.num_groups);
+  a16_repack_cells_kernel<<<(cells * 32 + 255) / 256, 256, 0, st>>>(
+      b + bh.nibbles_off, reinterpret_cast<const float*>(b + bh.scales_off),
+      reinterpret_cast<const float*>(b + a16_zeros_off(bh)), k, row_begin, row_count, (int)th.num_groups,
+      (int)th.num_panels, t + th.cells_off);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int padded = (int)th.num_panels * kPanelRows;
+  a16_repack_bias_kernel<<<(padded + 255) / 256, 256, 0, st>>>(
+      has_bias ? reinterpret_cast<const float*>(b + bh.bias_off) : nullptr, row_begin, row_count, padded,
+      reinterpret_cast<float*>(t + th.bias_off));
+  return cudaGetLastError();
+}
+
+}  // namespace mllmb200

@@ -58,6 +58,14 @@ def lib():
         "mllmb200_check_device_status": ([vp], C.c_int),
         "mllmb200_conv3d_w4a32_plan": ([int_p, int_p, int_p, C.c_int, int_p, int_p, sz_p], C.c_int),
         "mllmb200_conv3d_w4a32_forward": ([vp, vp, vp, vp, int_p, int_p, int_p, C.c_int, vp], C.c_int),
+        "mllmb200_w4a16_prepack_size": ([C.c_int, C.c_int, C.c_int, sz_p], C.c_int),
+        "mllmb200_w4a16_quant_prepack": ([vp, vp, C.c_int, C.c_int, vp], C.c_int),
+        "mllmb200_w4a16_blob_info": ([vp, C.c_size_t, int_p, int_p, int_p], C.c_int),
+        "mllmb200_w4a16_blob_offsets": ([C.c_int, C.c_int, C.c_int, sz_p, sz_p, sz_p, sz_p], C.c_int),
+        "mllmb200_w4a16_tiled_size": ([C.c_int, C.c_int, sz_p], C.c_int),
+        "mllmb200_w4a16_repack_device": ([vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp], C.c_int),
+        "mllmb200_w4a16_workspace_size": ([C.c_int, C.c_int, C.c_int, sz_p], C.c_int),
+        "mllmb200_w4a16_linear_forward": ([vp, C.c_int, vp, vp, vp] + [C.c_int] * 5 + [vp], C.c_int),
     }
     for name, (args, res) in sig.items():
         fn = getattr(L, name)

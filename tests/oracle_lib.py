@@ -114,3 +114,63 @@ class Oracle:
     def linear(self, x, q, s, bias=None, scale_mode=0):
         x = np.ascontiguousarray(x, np.float32)
         return self.matmul(self.quant_act(x), q, s, x.shape[1], bias, scale_mode)
+
+
+class OracleW4A16:
+    """numpy-level wrapper of the W4A16 restatement (oracle/w4a16_oracle.c)."""
+
+    def __init__(self):
+        self.lib = lib = load_oracle()
+        _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+        lib.oracle_w4a16_quant_nxk_qai4c32_f32.argtypes = [C.c_size_t, C.c_size_t, C.c_size_t, _f32p, _u8p, _f32p,
+                                                           _f32p, _i32p]
+        lib.oracle_w4a16_quant_nxk_qai4c32_f32.restype = None
+        lib.oracle_w4a16_quant_lhs_f32.argtypes = [C.c_size_t, C.c_size_t, C.c_size_t, _f32p, _i8p, _f32p]
+        lib.oracle_w4a16_quant_lhs_f32.restype = None
+        lib.oracle_w4a16_matmul.argtypes = [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _i8p, _f32p, _u8p, _f32p,
+                                            _f32p, C.c_void_p, _u16p, C.c_float, C.c_float]
+        lib.oracle_w4a16_matmul.restype = None
+        lib.oracle_w4a16_fill_uniform_random_f16.argtypes = [C.c_size_t, _u16p, C.c_uint]
+        lib.oracle_w4a16_fill_uniform_random_f16.restype = None
+
+    @staticmethod
+    def nblocks(k, bl=32):
+        return (k + bl - 1) // bl
+
+    def fill_uniform_random_f16(self, count, seed):
+        out = np.empty(count, np.uint16)
+        self.lib.oracle_w4a16_fill_uniform_random_f16(count, out, seed)
+        return out.view(np.float16)
+
+    def quant_weights(self, w):
+        """-> nibbles u8 [n, ceil(k/2)] (even k in the high half), scales f32, zeros f32, zero points i32."""
+        n, k = w.shape
+        nb = self.nblocks(k)
+        q = np.zeros((n, (k + 1) // 2), np.uint8)
+        z = np.zeros((n, nb), np.float32)
+        s = np.zeros((n, nb), np.float32)
+        zp = np.zeros((n, nb), np.int32)
+        self.lib.oracle_w4a16_quant_nxk_qai4c32_f32(n, k, 32, np.ascontiguousarray(w, np.float32), q, z, s, zp)
+        return q, s, z, zp
+
+    def quant_act(self, x):
+        m, k = x.shape
+        nb = self.nblocks(k)
+        a_q = np.zeros((m, nb * 32), np.int8)
+        a_s = np.zeros((m, nb), np.float32)
+        self.lib.oracle_w4a16_quant_lhs_f32(m, k, 32, np.ascontiguousarray(x, np.float32), a_q, a_s)
+        return a_q, a_s
+
+    def linear(self, x, q, s, z, bias=None):
+        """x: fp32 or fp16 [m,k] (fp16 is widened, exactly) -> fp16 [m,n]."""
+        x = np.ascontiguousarray(np.asarray(x).astype(np.float32))
+        m, k = x.shape
+        n = q.shape[0]
+        a_q, a_s = self.quant_act(x)
+        y = np.zeros((m, n), np.uint16)
+        b = None
+        if bias is not None:
+            bias = np.ascontiguousarray(bias, np.float32)
+            b = bias.ctypes.data_as(C.c_void_p)
+        self.lib.oracle_w4a16_matmul(m, n, k, 32, a_q, a_s, q, s, z, b, y, -65504.0, 65504.0)
+        return y.view(np.float16)
