@@ -8,7 +8,7 @@
 namespace mllmb200 {
 // w4a16.cu
 size_t a16_workspace_bytes(int m, int k, int n);
-cudaError_t launch_w4a16_linear(const void*, int, const void*, void*, void*, int, int, int, int, int, cudaStream_t);
+cudaError_t launch_w4a16_linear(const void*, int, const void*, void*, void*, int, int, int, int, int, int, cudaStream_t);
 cudaError_t launch_w4a16_repack(const void*, int, int, int, int, int, void*, cudaStream_t);
 // c_api.cu
 int record_cuda_failure(cudaError_t e);
@@ -42,6 +42,13 @@ int mllmb200_w4a16_workspace_size(int M, int K, int N, size_t* bytes) {
 
 int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, const void* tiled_dev, void* y_dev, void* ws_dev,
                                   int M, int K, int N, int ldx, int ldy, void* stream) {
+  return mllmb200_w4a16_linear_forward_ex(x_dev, x_dtype, tiled_dev, y_dev, ws_dev, M, K, N, ldx, ldy, 0, stream);
+}
+
+int mllmb200_w4a16_linear_forward_ex(const void* x_dev, int x_dtype, const void* tiled_dev, void* y_dev, void* ws_dev,
+                                     int M, int K, int N, int ldx, int ldy, int kernel, void* stream) {
+  if (kernel != 0 && kernel != 2 && kernel != 4) return MLLMB200_INVALID_ARG;
+  if (kernel == 4 && M < 64) return MLLMB200_UNSUPPORTED;
   if (!x_dev || !tiled_dev || !y_dev || !ws_dev || M <= 0 || K <= 0 || N <= 0 || ldx < K || ldy < N)
     return MLLMB200_INVALID_ARG;
   if (x_dtype != MLLMB200_DTYPE_F32 && x_dtype != MLLMB200_DTYPE_F16) return MLLMB200_INVALID_ARG;
@@ -50,7 +57,7 @@ int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, const void* ti
     return MLLMB200_INVALID_ARG;
   if (M > 65535) return MLLMB200_UNSUPPORTED;  // rows of x ride on gridDim.y
   const cudaError_t e =
-      launch_w4a16_linear(x_dev, x_dtype, tiled_dev, y_dev, ws_dev, M, K, N, ldx, ldy, (cudaStream_t)stream);
+      launch_w4a16_linear(x_dev, x_dtype, tiled_dev, y_dev, ws_dev, M, K, N, ldx, ldy, kernel, (cudaStream_t)stream);
   return e == cudaSuccess ? MLLMB200_OK : record_cuda_failure(e);
 }
 

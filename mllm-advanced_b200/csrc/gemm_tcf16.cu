@@ -36,6 +36,7 @@
 #include <cuda_fp16.h>
 
 #include "device_common.cuh"
+#include "layout_a16.h"
 #include "tcgen05_common.cuh"
 
 namespace mllmb200 {
@@ -47,31 +48,35 @@ constexpr int kTfTileRows = 128;   // weight rows per MMA (tensor-memory lanes);
 constexpr int kTfMaxProblems = 4;
 struct TfProblem {          // one weight matrix of a launch; all problems share x (M, K, the activation blocks)
   const uint8_t* tiled;     // TiledHeader at offset 0
-  float* y;
+  void* y;                  // fp32 [M, ldy] (W4A32) or fp16 [M, ldy] (W4A16)
   int n, ldy, num_panels;
   int tile_begin;           // first blockIdx.x of this problem
   size_t bias_off;
 };
 struct TfParams {
   const uint8_t* a_blocks;  // activations, [num_groups][m8_pad][512 bytes] fp16 canonical blocks
-  const float2* a_hdr;      // [m] {lhs_scale, a_off bits}
+  const float2* a_hdr;      // [m] {lhs_scale, a_off bits}; unused (may be null) on the W4A16 path
   int m, k, num_groups, m8_pad, num_problems;
   TfProblem prob[kTfMaxProblems];
 };
 
-template <int NT, int ROWS>
+// A16 = the W4A16 sibling format (layout_a16.h): 768-byte cells with an fp32 scale and an fp32 zero term per
+// row and K-group, A = fp16( ((u - 8) * s + z) * 2^E ) (one rounding), B = fp16( a_q * a_s ) per 32-element
+// block (one rounding), fp16 output.
+template <int NT, int ROWS, bool A16 = false>
 struct TfSmem {
+  static constexpr int kCell = A16 ? kCellBytesA16 : kCellBytes;
   // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
   // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
-  static constexpr int kGroups = (NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
+  static constexpr int kGroups = (A16 || NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
   // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
   // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
   // the number of tiles in flight, so both rings are as deep as shared memory allows.
-  static constexpr int kStages = (NT >= 256 && ROWS == 128) ? 4 : 3;
+  static constexpr int kStages = A16 ? (NT >= 256 ? 4 : 5) : (NT >= 256 && ROWS == 128) ? 4 : 3;
   static constexpr int kAStages = kStages;  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages)
   static constexpr int kPanels = ROWS / kPanelRows;
   static constexpr int kGroupABytes = ROWS * kGroup * 2;  // one K-group of the A operand (8 or 16 KB)
-  static constexpr int kRawBytes = kPanels * kGroups * kCellBytes;
+  static constexpr int kRawBytes = kPanels * kGroups * kCell;
   static constexpr int kBBytes = kGroups * NT * 64;
   static constexpr int kStageBytes = kRawBytes + kBBytes;
   static constexpr int kABytes = kGroups * kGroupABytes;
@@ -85,9 +90,11 @@ struct TfSmem {
 // ROWS = 256: two 128-row accumulators side by side in tensor memory share every activation block
 // that is loaded - the activation (B) operand is re-read from L2 once per weight tile, which bounds
 // the 128-row tile on large grids.
-template <int NT, int ROWS>
+template <int NT, int ROWS, bool A16>
 __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const TfParams p) {
-  using S = TfSmem<NT, ROWS>;
+  using S = TfSmem<NT, ROWS, A16>;
+  constexpr int kCell = S::kCell;
+  static_assert(sizeof(TiledHeader) == sizeof(TiledHeaderA16), "both formats keep their cells 256 bytes in");
   constexpr int kPanels = S::kPanels, kHalves = ROWS / kTfTileRows, kTfGroupABytes = S::kGroupABytes;
   constexpr int kStages = S::kStages, kTfAStages = S::kAStages, kTfGroupsPerStage = S::kGroups;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -122,7 +129,8 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
-  for (int i = tid; i < NT; i += kTfThreads) s_hdr[i] = (m0 + i < p.m) ? p.a_hdr[m0 + i] : make_float2(0.0f, 0.0f);
+  if constexpr (!A16)
+    for (int i = tid; i < NT; i += kTfThreads) s_hdr[i] = (m0 + i < p.m) ? p.a_hdr[m0 + i] : make_float2(0.0f, 0.0f);
   if (warp == kTfDequantWarps + 1) {
     tmem_alloc(tmem_base_slot, kTmemCols);
     tmem_relinquish();
@@ -143,12 +151,12 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       const int g0 = it * kTfGroupsPerStage;
       const int ng = min(kTfGroupsPerStage, p.num_groups - g0);
       uint8_t* st = stages + (size_t)s * S::kStageBytes;
-      if (lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCellBytes + ng * NT * 64));
+      if (lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCell + ng * NT * 64));
       __syncwarp();
       if (lane < np) {
-        bulk_g2s(st + lane * kTfGroupsPerStage * kCellBytes,
-                 pr.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCellBytes,
-                 (uint32_t)(ng * kCellBytes), &raw_full[s]);
+        bulk_g2s(st + lane * kTfGroupsPerStage * kCell,
+                 pr.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCell,
+                 (uint32_t)(ng * kCell), &raw_full[s]);
       } else if (lane >= kPanels && lane < kPanels + ng) {
         const int g = lane - kPanels;
         bulk_g2s(st + S::kRawBytes + g * NT * 64, p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 512,
@@ -202,8 +210,10 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     const uint32_t scale_mode = hdr->scale_mode;
     // 2^E maps the largest |scale| of the matrix into [2^11, 2^12): (u - 8) * s * 2^E < 2^15.
     // (Read here, not before the role split: the producer must not wait for this load.)
-    const int emax = (int)((hdr->max_scale_bits >> 23) & 0xFFu);
-    const int E = emax == 0 ? 0 : 11 - (emax - 127);
+    // W4A16: the header word at the same offset holds the bits of max (8 |s| + |z|) >= max |weight|,
+    // mapped into [2^14, 2^15).
+    const int emax = (int)(((A16 ? reinterpret_cast<const TiledHeaderA16*>(pr.tiled)->max_weight_bits : hdr->max_scale_bits) >> 23) & 0xFFu);
+    const int E = emax == 0 ? 0 : (A16 ? 14 : 11) - (emax - 127);
     const float up = exp2f((float)E), down = exp2f((float)-E);
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
@@ -215,13 +225,38 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       }
       if (!ok) break;
       const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
-      const uint8_t* raw = stages + (size_t)s * S::kStageBytes + q * kTfGroupsPerStage * kCellBytes;
+      const uint8_t* raw = stages + (size_t)s * S::kStageBytes + q * kTfGroupsPerStage * kCell;
       uint8_t* a_out = a_stages + (size_t)sa * S::kABytes + (j >> 3) * 512 + (j & 7) * 16;
 #pragma unroll
       for (int g = gsel; g < kTfGroupsPerStage; g += gstep) {
         if (g < ng) {
         uint4 w = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
         float sc = 0.0f;
+        if constexpr (A16) {
+          // fp32 all the way to one rounding: ((u - 8) * s + z) * 2^E; 0x4B000000 | u = 2^23 + u as a float
+          float zr = 0.0f;
+          if (have_panel) {
+            w = *reinterpret_cast<const uint4*>(raw + g * kCell + r * 16);
+            sc = *reinterpret_cast<const float*>(raw + g * kCell + kCellNibbleBytes + r * 4);
+            zr = *reinterpret_cast<const float*>(raw + g * kCell + kCellNibbleBytes + kPanelRows * 4 + r * 4);
+          }
+          const float s_up = sc * up, z_up = zr * up;
+          const uint32_t wa[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float f[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+              f[t] = fmaf(__uint_as_float(0x4B000000u | ((wa[c] >> (4 * t)) & 15u)) - 8388616.0f, s_up, z_up);
+            uint32_t o[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {  // same element order as the W4A32 unpack: k = 8c + {0,4,1,5,2,6,3,7}
+              const __half2 v = __floats2half2_rn(f[t], f[t + 4]);
+              o[t] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        } else {
         if (have_panel) {
           w = *reinterpret_cast<const uint4*>(raw + g * kCellBytes + r * 16);
           sc = decode_scale(*reinterpret_cast<const uint16_t*>(raw + g * kCellBytes + kCellNibbleBytes + r * 2), scale_mode);
@@ -239,6 +274,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
             o[t] = *reinterpret_cast<const uint32_t*>(&v);
           }
           *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
         }
         }
       }
@@ -267,9 +303,14 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
           for (int i = 0; i < 16; ++i) {
             const int m = m0 + c0 + i;
             if (live && m < p.m) {
-              const float2 h = s_hdr[c0 + i];
-              const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
-              pr.y[(size_t)m * pr.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+              if constexpr (A16) {
+                const float val = fmaf(__uint_as_float(v[i]), down, bs);
+                static_cast<__half*>(pr.y)[(size_t)m * pr.ldy + n] = __float2half_rn(fminf(fmaxf(val, -65504.0f), 65504.0f));
+              } else {
+                const float2 h = s_hdr[c0 + i];
+                const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
+                static_cast<float*>(pr.y)[(size_t)m * pr.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+              }
             }
           }
         }
@@ -284,17 +325,17 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   }
 }
 
-template <int NT, int ROWS>
+template <int NT, int ROWS, bool A16 = false>
 static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_t stream) {
-  using S = TfSmem<NT, ROWS>;
+  using S = TfSmem<NT, ROWS, A16>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS, A16>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const dim3 grid((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
-  w4a32_gemm_tcf16_kernel<NT, ROWS><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
+  w4a32_gemm_tcf16_kernel<NT, ROWS, A16><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
   return cudaGetLastError();
 }
 
@@ -371,6 +412,36 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
     case 256: return launch_tf_t<256, 128>(prm, tiles, stream);
     case 128: return launch_tf_t<128, 128>(prm, tiles, stream);
     default: return launch_tf_t<64, 128>(prm, tiles, stream);
+  }
+}
+
+// W4A16: 128-row tiles; the activation blocks must be padded to a multiple of w4a16_gemm_tcf16_tile(m, n) rows.
+int w4a16_gemm_tcf16_tile(int m, int n) {
+  const long long t128 = (n + 127) / 128;
+  return (m >= 256 && t128 * ((m + 255) / 256) >= 100) ? 256 : (m >= 128 ? 128 : 64);
+}
+cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, void* y_f16, int m, int k, int n, int ldy,
+                                    cudaStream_t stream) {
+  const int nt = w4a16_gemm_tcf16_tile(m, n);
+  TfParams prm = {};
+  prm.a_blocks = a_blocks;
+  prm.a_hdr = nullptr;
+  prm.m = m, prm.k = k;
+  prm.num_groups = (k + kGroup - 1) / kGroup;
+  prm.m8_pad = (m + nt - 1) / nt * nt / 8;
+  prm.num_problems = 1;
+  prm.prob[0].tiled = static_cast<const uint8_t*>(tiled);
+  prm.prob[0].y = y_f16;
+  prm.prob[0].n = n;
+  prm.prob[0].ldy = ldy;
+  prm.prob[0].num_panels = (n + kPanelRows - 1) / kPanelRows;
+  prm.prob[0].tile_begin = 0;
+  prm.prob[0].bias_off = make_tiled_header_a16(n, k, 0).bias_off;
+  const int tiles = (n + 127) / 128;
+  switch (nt) {
+    case 256: return launch_tf_t<256, 128, true>(prm, tiles, stream);
+    case 128: return launch_tf_t<128, 128, true>(prm, tiles, stream);
+    default: return launch_tf_t<64, 128, true>(prm, tiles, stream);
   }
 }
 

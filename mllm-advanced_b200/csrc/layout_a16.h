@@ -47,7 +47,9 @@ constexpr int kCellBytesA16 = kCellNibbleBytes + kPanelRows * 4 + kPanelRows * 4
 struct TiledHeaderA16 {
   uint32_t magic, version, n, k, num_groups, num_panels, has_bias, reserved;
   uint64_t cells_off, bias_off, total_bytes;
-  uint8_t pad[256 - 32 - 24];
+  uint64_t reserved2;
+  uint32_t max_weight_bits;  // fp32 bits of max over the matrix of 8 |scale| + |zero| (>= any |weight|); written by the repack
+  uint8_t pad[256 - 32 - 32 - 4];
 };
 static_assert(sizeof(TiledHeaderA16) == 256, "tiled header is 256 bytes");
 

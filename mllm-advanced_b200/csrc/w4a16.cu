@@ -21,7 +21,8 @@ namespace mllmb200 {
 // One warp per (panel, group) cell, lane = row of the panel.
 __global__ void a16_repack_cells_kernel(const uint8_t* __restrict__ nib, const float* __restrict__ scales,
                                         const float* __restrict__ zeros, int k, int row_begin, int row_count,
-                                        int num_groups, int num_panels, uint8_t* __restrict__ cells) {
+                                        int num_groups, int num_panels, uint8_t* __restrict__ cells,
+                                        unsigned int* __restrict__ max_weight_bits) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= num_panels * num_groups) return;
   const int panel = warp / num_groups, g = warp % num_groups;
@@ -55,6 +56,12 @@ __global__ void a16_repack_cells_kernel(const uint8_t* __restrict__ nib, const f
   }
   reinterpret_cast<float*>(cell + kCellNibbleBytes)[lane] = s;
   reinterpret_cast<float*>(cell + kCellNibbleBytes + kPanelRows * 4)[lane] = z;
+  // 8 |s| + |z| bounds every |weight| of the group; the tensor-core path scales the matrix by it
+  float bound = fmaf(8.0f, fabsf(s), fabsf(z));
+  if (!(bound < 3.0e38f)) bound = 0.0f;  // inf / nan scales are not used for the range
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+  if (lane == 0 && bound > 0.0f) atomicMax(max_weight_bits, __float_as_uint(bound));  // positive floats order as their bits
 }
 
 __global__ void a16_repack_bias_kernel(const float* __restrict__ bias, int row_begin, int row_count, int padded,
@@ -112,6 +119,45 @@ __global__ void __launch_bounds__(256) a16_act_quant_kernel(const T* __restrict_
   if (j == 0) {
     rec[8] = (uint32_t)sum;
     rec[9] = __float_as_uint(scale);
+  }
+}
+
+// The same quantization for the tensor-core path: the de-quantized values a_q * a_s, rounded once to fp16,
+// in the 512-byte K-major operand blocks [group][row / 8] of gemm_tcf16.cu (4 chunks of 8 rows x 16 bytes,
+// chunk c = k 8c + {0,4,1,5,2,6,3,7}).  One CTA per (padded) row, one thread per 8-element chunk; the four
+// chunk threads of a group sit in adjacent lanes.  Padding rows are written as zeros.
+template <typename T>
+__global__ void __launch_bounds__(256) a16_act_quant_blocks_f16_kernel(const T* __restrict__ x, int m_total, int k,
+                                                                       int ldx, int num_groups, int m8_pad,
+                                                                       uint8_t* __restrict__ blocks) {
+  const int m = blockIdx.x;
+  const bool live = m < m_total;
+  const T* row = x + (size_t)(live ? m : 0) * ldx;
+  const int items = num_groups * 4;
+  for (int base = 0; base < items; base += 256) {  // uniform trip count: the shuffles below need whole warps
+    const int it = base + threadIdx.x;
+    const bool valid = it < items;
+    const int g = it >> 2, c = it & 3, kc = g * kGroup + c * 8;
+    float f[8], amax = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      f[jj] = (valid && live && kc + jj < k) ? a16_load<T>(row + kc + jj) : 0.0f;
+      amax = fmaxf(amax, fabsf(f[jj]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float scale = __fdiv_rn(amax, 127.0f);
+    const float recip = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+    __align__(16) __half h[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const float q = fminf(fmaxf(roundf(__fmul_rn(f[jj], recip)), -127.0f), 127.0f);
+      const int pos = (jj < 4) ? 2 * jj : 2 * (jj - 4) + 1;
+      h[pos] = __float2half_rn(__fmul_rn(q, scale));
+    }
+    if (valid)
+      *reinterpret_cast<uint4*>(blocks + ((size_t)g * m8_pad + (m >> 3)) * 512 + (m & 7) * 16 + c * 128) =
+          *reinterpret_cast<const uint4*>(h);
   }
 }
 
@@ -231,11 +277,21 @@ int a16_slices(int m, int k, int n) {
   return min(s, 8);
 }
 
+// gemm_tcf16.cu
+int w4a16_gemm_tcf16_tile(int m, int n);
+cudaError_t launch_w4a16_gemm_tcf16(const uint8_t*, const void*, void*, int, int, int, int, cudaStream_t);
+
+// The tensor-core path (fp16 operands, one rounding each) from this M on; below it the exact-integer dp4a kernel.
+bool w4a16_tensor_path(int m, int kernel) { return kernel == 4 ? m >= 64 : (kernel == 0 && m >= 128); }
+
 size_t a16_workspace_bytes(int m, int k, int n) {
   const size_t rec = align_up((size_t)m * blob_num_blocks(k) * kActRecordBytesA16, 256);
   const int s = a16_slices(m, k, n);
   const size_t n_pad = (size_t)((n + kPanelRows - 1) / kPanelRows) * kPanelRows;
-  return rec + (s > 1 ? align_up((size_t)s * m * n_pad * 4, 256) : 0);
+  const size_t simt = rec + (s > 1 ? align_up((size_t)s * m * n_pad * 4, 256) : 0);
+  // operand blocks of the tensor-core path: 64 bytes per row and K-group, rows padded to its widest tile
+  const size_t blk = m >= 64 ? align_up((size_t)((m + 255) / 256 * 256) * blob_num_blocks(k) * 64, 256) : 0;
+  return simt > blk ? simt : blk;
 }
 
 template <int MT>
@@ -250,9 +306,19 @@ static cudaError_t a16_launch_mt(const uint8_t* tiled, const uint8_t* recs, int 
 }
 
 cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, void* y, void* ws, int m, int k, int n,
-                                int ldx, int ldy, cudaStream_t st) {
+                                int ldx, int ldy, int kernel, cudaStream_t st) {
   const int nb = (int)blob_num_blocks(k);
   uint8_t* recs = static_cast<uint8_t*>(ws);
+  if (w4a16_tensor_path(m, kernel)) {
+    const int nt = w4a16_gemm_tcf16_tile(m, n), m_pad = (m + nt - 1) / nt * nt;
+    if (x_dtype == 1)
+      a16_act_quant_blocks_f16_kernel<__half><<<m_pad, 256, 0, st>>>(static_cast<const __half*>(x), m, k, ldx, nb, m_pad / 8, recs);
+    else
+      a16_act_quant_blocks_f16_kernel<float><<<m_pad, 256, 0, st>>>(static_cast<const float*>(x), m, k, ldx, nb, m_pad / 8, recs);
+    const cudaError_t qe = cudaGetLastError();
+    if (qe != cudaSuccess) return qe;
+    return launch_w4a16_gemm_tcf16(recs, tiled, y, m, k, n, ldy, st);
+  }
   float* partial =
       reinterpret_cast<float*>(recs + align_up((size_t)m * nb * kActRecordBytesA16, 256));
   dim3 qgrid((nb + 31) / 32, m);
@@ -288,7 +354,8 @@ cudaError_t launch_w4a16_repack(const void* blob_dev, int n, int k, int has_bias
   a16_repack_cells_kernel<<<(cells * 32 + 255) / 256, 256, 0, st>>>(
       b + bh.nibbles_off, reinterpret_cast<const float*>(b + bh.scales_off),
       reinterpret_cast<const float*>(b + a16_zeros_off(bh)), k, row_begin, row_count, (int)th.num_groups,
-      (int)th.num_panels, t + th.cells_off);
+      (int)th.num_panels, t + th.cells_off,
+      reinterpret_cast<unsigned int*>(t + offsetof(TiledHeaderA16, max_weight_bits)));
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int padded = (int)th.num_panels * kPanelRows;

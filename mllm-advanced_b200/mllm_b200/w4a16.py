@@ -78,8 +78,12 @@ class W4A16Weights:
         return W4A16Weights(tiled, row_count, k, hb, row_begin, n)
 
 
-def linear_forward(x, weights, out=None, workspace=None, stream=None):
-    """fp16 y = W4A16 linear of x (torch float32 or float16 [M,K] on the GPU, last dim contiguous)."""
+KERNEL_AUTO, KERNEL_DP4A, KERNEL_TC_F16 = 0, 2, 4
+
+
+def linear_forward(x, weights, out=None, workspace=None, stream=None, kernel=KERNEL_AUTO):
+    """fp16 y = W4A16 linear of x (torch float32 or float16 [M,K] on the GPU, last dim contiguous).
+    kernel: KERNEL_AUTO (dp4a below M = 128, tensor cores from there on), KERNEL_DP4A, KERNEL_TC_F16 (M >= 64)."""
     import torch
     assert x.is_cuda and x.dtype in (torch.float32, torch.float16) and x.dim() == 2 and x.stride(1) == 1
     m, k = x.shape
@@ -88,8 +92,8 @@ def linear_forward(x, weights, out=None, workspace=None, stream=None):
         out = torch.empty((m, weights.n), dtype=torch.float16, device=x.device)
     if workspace is None:
         workspace = torch.empty(workspace_size(m, k, weights.n), dtype=torch.uint8, device=x.device)
-    _check(lib().mllmb200_w4a16_linear_forward(x.data_ptr(), 1 if x.dtype == torch.float16 else 0,
-                                               weights.tiled.data_ptr(), out.data_ptr(), workspace.data_ptr(), m, k,
-                                               weights.n, x.stride(0), out.stride(0), _stream_ptr(stream)),
+    _check(lib().mllmb200_w4a16_linear_forward_ex(x.data_ptr(), 1 if x.dtype == torch.float16 else 0,
+                                                  weights.tiled.data_ptr(), out.data_ptr(), workspace.data_ptr(), m, k,
+                                                  weights.n, x.stride(0), out.stride(0), kernel, _stream_ptr(stream)),
            "w4a16_linear_forward")
     return out
