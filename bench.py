@@ -307,6 +307,9 @@ def run_gpu(args):
     if args.config4_only:
         print(json.dumps({"config4": run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)}), flush=True)
         return
+    if args.w4a16_only:
+        print(json.dumps({"w4a16": run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)}), flush=True)
+        return
 
     # ---- weights: 28 layers x 7 linears, each its own tiled buffer
     layers = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(LAYERS)]
@@ -620,6 +623,11 @@ def run_gpu(args):
                 line["config4"] = run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)
             except Exception as ex:
                 line["config4"] = {"error": str(ex)[:200]}
+        if world == 1 and not args.no_w4a16:
+            try:
+                line["w4a16"] = run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind)
+            except Exception as ex:
+                line["w4a16"] = {"error": str(ex)[:200]}
         if not args.no_decoder and world == 1:
             try:
                 cpu_ms = line.get("cpu_baseline", {}).get("ms_per_layer")
@@ -746,6 +754,93 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
     return out
 
 
+def make_random_weights_a16(mb, torch, n, k, gen):
+    """Random W4A16 weights (nibbles uniform, scales |N(0, 0.02)|/7, zero terms within +-8 scales), assembled as a
+    blob on the device and repacked there."""
+    from mllm_b200 import w4a16
+    dev = "cuda"
+    blob = torch.zeros(w4a16.prepack_size(n, k, False), dtype=torch.uint8, device=dev)
+    a, b, z, c = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+    mb.lib().mllmb200_w4a16_blob_offsets(n, k, 0, C.byref(a), C.byref(b), C.byref(z), C.byref(c))
+    nb = k // 32
+    blob[a.value:a.value + n * (k // 2)] = torch.randint(0, 256, (n * (k // 2),), dtype=torch.uint8, device=dev, generator=gen)
+    sc = torch.randn((n * nb,), device=dev, generator=gen).abs() * (0.02 / 7.0)
+    zr = (torch.rand((n * nb,), device=dev, generator=gen) * 16 - 8).round() * sc
+    blob[b.value:b.value + n * nb * 4] = sc.view(torch.uint8)
+    blob[z.value:z.value + n * nb * 4] = zr.view(torch.uint8)
+    tiled = torch.empty(w4a16.tiled_size(n, k), dtype=torch.uint8, device=dev)
+    st = mb.lib().mllmb200_w4a16_repack_device(blob.data_ptr(), n, k, 0, 0, n, tiled.data_ptr(),
+                                               C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0, mb.status_str(st)
+    torch.cuda.synchronize()
+    return w4a16.W4A16Weights(tiled, n, k, 0)
+
+
+def run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
+    """The W4A16 sibling path (fp16 activations in, fp16 out) on the same shapes: the 7 linears of the 28 layers
+    at M=1 (CUDA graph, distinct weights per layer) and at M=512, and BASELINE config 4's matrix."""
+    from mllm_b200 import w4a16
+
+    def a16_bytes(m, k, n):  # nibbles + fp32 scale and zero per group + fp16 x and y
+        return n * k // 2 + n * (k // 32) * 8 + m * k * 2 + m * n * 2
+
+    out = {"workload": "W4A16: 28 layers x 7 linears of Qwen2-1.5B at M=1 and M=512; config 4 matrix at M=1 and M=2048",
+           "dtype": "int4 weights (fp32 scale + zero per group of 32), int8 per-block activations, fp16 in/out"}
+    stream = torch.cuda.Stream()
+    layers = [[make_random_weights_a16(mb, torch, n, k, gen) for _, k, n, _ in LINEARS] for _ in range(LAYERS)]
+    for m, key in ((1, "decode_M1"), (PREFILL_M, "prefill_M512")):
+        xs = {k: torch.randn((m, k), device="cuda", generator=gen).half() for k in (1536, 8960)}
+        ys = {n: torch.empty((m, n), device="cuda", dtype=torch.float16) for n in (1536, 256, 8960)}
+        ws = torch.empty(max(w4a16.workspace_size(m, k, n) for _, k, n, _ in LINEARS), dtype=torch.uint8, device="cuda")
+
+        def one_pass():
+            for lw in layers:
+                for w in lw:
+                    w4a16.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream)
+        with torch.cuda.stream(stream):
+            one_pass()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            one_pass()
+        for _ in range(3):
+            g.replay()
+        ms = event_time_ms(torch, g.replay, 10 if m == 1 else 3)
+        by = sum(a16_bytes(m, k, n) for _, k, n, _ in LINEARS) * LAYERS
+        fl = sum(2.0 * m * k * n for _, k, n, _ in LINEARS) * LAYERS
+        out[key] = {"ms": ms, "GBs": by / (ms * 1e-3) / 1e9, "tflops": fl / (ms * 1e-3) / 1e12,
+                    "frac_hbm": by / (ms * 1e-3) / 1e9 / hbm_peak, "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tensor_peak,
+                    "peak_kind": f"of {peak_kind}", "how": "CUDA graph of 196 calls (activation quantization + kernel each)"}
+        del g
+    del layers
+    n, k = 28672, 8192
+    copies = [make_random_weights_a16(mb, torch, n, k, gen) for _ in range(3)]  # 3 x 176 MB > L2
+    for m, key in ((1, "config4_M1"), (2048, "config4_M2048")):
+        x = torch.randn((m, k), device="cuda", generator=gen).half()
+        y = torch.empty((m, n), device="cuda", dtype=torch.float16)
+        ws = torch.empty(w4a16.workspace_size(m, k, n), dtype=torch.uint8, device="cuda")
+
+        def big_pass():
+            for w in copies:
+                w4a16.linear_forward(x, w, out=y, workspace=ws, stream=stream)
+        with torch.cuda.stream(stream):
+            big_pass()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            big_pass()
+        for _ in range(3):
+            g.replay()
+        ms = event_time_ms(torch, g.replay, 10 if m == 1 else 3) / len(copies)
+        by, fl = a16_bytes(m, k, n), 2.0 * m * k * n
+        out[key] = {"ms": ms, "GBs": by / (ms * 1e-3) / 1e9, "tflops": fl / (ms * 1e-3) / 1e12,
+                    "frac_hbm": by / (ms * 1e-3) / 1e9 / hbm_peak, "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tensor_peak,
+                    "peak_kind": f"of {peak_kind}"}
+        del g
+    mb.check_device_status()
+    return out
+
+
 def run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
     """BASELINE config 4 on one GPU: W [28672, 8192] int4 g32 (132 MB).  The same kernels as the
     headline, at a size where fixed latencies no longer dominate: GEMV at M=1 (HBM roofline) and the
@@ -853,6 +948,8 @@ def main():
     ap.add_argument("--per-op", action="store_true", help="headline step with one call per linear instead of grouped calls")
     ap.add_argument("--config4-only", action="store_true", help="only the section on BASELINE config 4's large matrix")
     ap.add_argument("--no-config4", action="store_true", help="skip the single-GPU section on BASELINE config 4's large matrix")
+    ap.add_argument("--w4a16-only", action="store_true", help="only the section on the W4A16 sibling path")
+    ap.add_argument("--no-w4a16", action="store_true", help="skip the section on the W4A16 sibling path")
     ap.add_argument("--decoder-only", action="store_true", help="only the whole-model prefill + decode section")
     ap.add_argument("--decoder-prompt", type=int, default=512, help="prompt length of the decoder section")
     ap.add_argument("--decoder-steps", type=int, default=128, help="greedy steps of the decoder section (small values for ncu)")

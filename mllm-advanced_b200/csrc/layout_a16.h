@@ -69,7 +69,7 @@ inline TiledHeaderA16 make_tiled_header_a16(int n, int k, int has_bias) {
 }
 
 // ---- quantized activations ----
-// Per activation row m and K-group b a 48-byte record:
+// Per K-group b and activation row m a 48-byte record, ordered [group][row] (the rows of a tile are contiguous):
 //   words 0..3 : int8 a_q for k = 8i+{0,2,4,6}  (matches the low half-bytes of nibble word i)
 //   words 4..7 : int8 a_q for k = 8i+{1,3,5,7}  (matches the high half-bytes)
 //   word  8    : sum_{k in b} a_q[k]            (int32)

@@ -8,12 +8,15 @@
 // kernel for every M: a CTA owns one 32-row panel (lane = output row) and MT rows of x, its 8 warps split
 // the K groups, partial sums meet in shared memory; for small grids K is also split over gridDim.z with
 // fp32 partials in the workspace and a finishing kernel that adds them in slice order (deterministic).
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "../../include/mllmb200.h"
 #include "device_common.cuh"
 #include "layout_a16.h"
+
+namespace cg = cooperative_groups;
 
 namespace mllmb200 {
 
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(256) a16_act_quant_kernel(const T* __restrict_
   const uint32_t od = (uint32_t)(q[1] & 0xff) | ((uint32_t)(q[3] & 0xff) << 8);
   const uint32_t ev_p = __shfl_xor_sync(0xffffffffu, ev, 1), od_p = __shfl_xor_sync(0xffffffffu, od, 1);
   if (g >= num_groups) return;
-  uint32_t* rec = reinterpret_cast<uint32_t*>(recs + ((size_t)m * num_groups + g) * kActRecordBytesA16);
+  uint32_t* rec = reinterpret_cast<uint32_t*>(recs + ((size_t)g * gridDim.y + m) * kActRecordBytesA16);  // [group][row]
   if ((j & 1) == 0) rec[j >> 1] = ev | (ev_p << 16);
   else rec[4 + (j >> 1)] = od_p | (od << 16);
   if (j == 0) {
@@ -194,6 +197,7 @@ __global__ void __launch_bounds__(256) a16_linear_kernel(const uint8_t* __restri
                                                          int groups_per_slice, __half* __restrict__ y, int ldy,
                                                          float* __restrict__ partial, int n_pad) {
   __shared__ float red[8][MT][32];
+  __shared__ uint4 s_rec[8][MT * 3];  // per warp: the MT records of the group it works on
   const TiledHeaderA16* hdr = reinterpret_cast<const TiledHeaderA16*>(tiled);
   if (hdr->magic != kTiledMagicA16 || hdr->n != (uint32_t)n || hdr->k != (uint32_t)k) {
     if (threadIdx.x == 0) atomicOr(&g_device_status, kDevStatusBadHeader);
@@ -210,26 +214,51 @@ __global__ void __launch_bounds__(256) a16_linear_kernel(const uint8_t* __restri
 #pragma unroll
   for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
 
+  // The records of a group are laid out [group][row]: the MT rows of this tile are MT * 48 contiguous bytes,
+  // fetched by the warp with one coalesced load (two for MT = 16) and re-read from shared memory as broadcasts.
+  constexpr int kRecVecs = MT * 3;                       // 16-byte pieces per (group, row tile)
+  constexpr int kRecLoads = (kRecVecs + 31) / 32;
+  const int rows_here = min(MT, m - m0);
+  auto load_recs = [&](int gg, uint4 (&r)[kRecLoads]) {
+    const uint4* src = reinterpret_cast<const uint4*>(recs + ((size_t)gg * m + m0) * kActRecordBytesA16);
+#pragma unroll
+    for (int q = 0; q < kRecLoads; ++q) {
+      const int idx = q * 32 + lane;
+      r[q] = idx < rows_here * 3 ? __ldg(src + idx) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
   int g = g_begin + warp;
   A16Cell cur;
-  if (g < g_end) cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
+  uint4 rcur[kRecLoads];
+  if (g < g_end) {
+    cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
+    load_recs(g, rcur);
+  }
   for (; g < g_end; g += 8) {
     A16Cell nxt = cur;
-    if (g + 8 < g_end) nxt = a16_load_cell(cells + (size_t)(g + 8) * kCellBytesA16, lane);
+    uint4 rnxt[kRecLoads];
 #pragma unroll
-    for (int i = 0; i < MT; ++i) {
-      const int row = m0 + i;
-      if (row < m) {  // uniform over the CTA
-        const uint4* rec = reinterpret_cast<const uint4*>(recs + ((size_t)row * nb + g) * kActRecordBytesA16);
-        const uint4 r0 = __ldg(rec), r1 = __ldg(rec + 1);
-        const uint2 r2 = __ldg(reinterpret_cast<const uint2*>(rec + 2));
-        const int asum = (int)r2.x;
-        const int dot = a16_dot(cur.nw, r0, r1) - 8 * asum;
-        const float t = fmaf(cur.s, (float)dot, cur.z * (float)asum);
-        acc[i] = fmaf(__uint_as_float(r2.y), t, acc[i]);
-      }
+    for (int q = 0; q < kRecLoads; ++q) rnxt[q] = rcur[q];
+    if (g + 8 < g_end) {
+      nxt = a16_load_cell(cells + (size_t)(g + 8) * kCellBytesA16, lane);
+      load_recs(g + 8, rnxt);
+    }
+    __syncwarp();  // the previous group's reads of s_rec are done
+#pragma unroll
+    for (int q = 0; q < kRecLoads; ++q)
+      if (q * 32 + lane < kRecVecs) s_rec[warp][q * 32 + lane] = rcur[q];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {  // rows beyond M hold zero records: they add 0
+      const uint4 r0 = s_rec[warp][i * 3], r1 = s_rec[warp][i * 3 + 1], r2 = s_rec[warp][i * 3 + 2];
+      const int asum = (int)r2.x;
+      const int dot = a16_dot(cur.nw, r0, r1) - 8 * asum;
+      const float t = fmaf(cur.s, (float)dot, cur.z * (float)asum);
+      acc[i] = fmaf(__uint_as_float(r2.y), t, acc[i]);
     }
     cur = nxt;
+#pragma unroll
+    for (int q = 0; q < kRecLoads; ++q) rcur[q] = rnxt[q];
   }
 #pragma unroll
   for (int i = 0; i < MT; ++i) red[warp][i][lane] = acc[i];
@@ -250,6 +279,106 @@ __global__ void __launch_bounds__(256) a16_linear_kernel(const uint8_t* __restri
       y[(size_t)row * ldy + col + l] = __float2half_rn(s);
     }
   }
+}
+
+// M <= 4: ONE launch per linear.  The per-block activation quantization has no row-wide dependency (unlike the
+// W4A32 path's per-row min/max), so every warp quantizes the 32 activations of the group it is about to use
+// itself: lane = k, warp max and sum by shuffles, the eight record words assembled with two OR-shuffles and
+// eight broadcasts.  K is split over the CTAs of a thread-block cluster (gridDim.z = cluster size <= 8); their
+// partial sums meet in the first CTA's pass over distributed shared memory, in rank order (deterministic).
+template <int MT, typename T>
+__global__ void __launch_bounds__(256) a16_gemv_fused_kernel(const uint8_t* __restrict__ tiled, const T* __restrict__ x,
+                                                             int ldx, int m, int k, int n, int groups_per_slice,
+                                                             __half* __restrict__ y, int ldy) {
+  __shared__ float red[8][MT][32];
+  __shared__ float sum[MT][32];
+  cg::cluster_group cluster = cg::this_cluster();
+  const TiledHeaderA16* hdr = reinterpret_cast<const TiledHeaderA16*>(tiled);
+  if (hdr->magic != kTiledMagicA16 || hdr->n != (uint32_t)n || hdr->k != (uint32_t)k) {  // the same for every CTA
+    if (threadIdx.x == 0) atomicOr(&g_device_status, kDevStatusBadHeader);
+    return;
+  }
+  const int nb = (int)hdr->num_groups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int panel = blockIdx.x;
+  const int g_begin = blockIdx.z * groups_per_slice;
+  const int g_end = min(nb, g_begin + groups_per_slice);
+  const uint8_t* cells = tiled + hdr->cells_off + (size_t)panel * nb * kCellBytesA16;
+
+  float acc[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
+  auto load_x = [&](int gg, float (&xv)[MT]) {
+    const int kk = gg * kGroup + lane;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) xv[i] = (i < m && kk < k) ? a16_load<T>(x + (size_t)i * ldx + kk) : 0.0f;
+  };
+  int g = g_begin + warp;
+  A16Cell cur;
+  float xcur[MT];
+  if (g < g_end) {
+    cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
+    load_x(g, xcur);
+  }
+  for (; g < g_end; g += 8) {
+    A16Cell nxt = cur;
+    float xnxt[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) xnxt[i] = xcur[i];
+    if (g + 8 < g_end) {
+      nxt = a16_load_cell(cells + (size_t)(g + 8) * kCellBytesA16, lane);
+      load_x(g + 8, xnxt);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      float amax = fabsf(xcur[i]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float scale = __fdiv_rn(amax, 127.0f);
+      const float recip = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+      const int q = (int)fminf(fmaxf(roundf(__fmul_rn(xcur[i], recip)), -127.0f), 127.0f);
+      int asum = q;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) asum += __shfl_xor_sync(0xffffffffu, asum, o);
+      // word c (even k) / word 4 + c (odd k) of the record: byte j = k 8c + 2j (+ 1); lane = k
+      uint32_t v = (uint32_t)(q & 0xff) << (8 * ((lane & 7) >> 1));
+      v |= __shfl_xor_sync(0xffffffffu, v, 2);
+      v |= __shfl_xor_sync(0xffffffffu, v, 4);
+      uint4 r0, r1;
+      r0.x = __shfl_sync(0xffffffffu, v, 0), r0.y = __shfl_sync(0xffffffffu, v, 8);
+      r0.z = __shfl_sync(0xffffffffu, v, 16), r0.w = __shfl_sync(0xffffffffu, v, 24);
+      r1.x = __shfl_sync(0xffffffffu, v, 1), r1.y = __shfl_sync(0xffffffffu, v, 9);
+      r1.z = __shfl_sync(0xffffffffu, v, 17), r1.w = __shfl_sync(0xffffffffu, v, 25);
+      const int dot = a16_dot(cur.nw, r0, r1) - 8 * asum;
+      const float t = fmaf(cur.s, (float)dot, cur.z * (float)asum);
+      acc[i] = fmaf(scale, t, acc[i]);
+    }
+    cur = nxt;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) xcur[i] = xnxt[i];
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i) red[warp][i][lane] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < MT * 32) {
+    const int i = threadIdx.x >> 5;
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w][i][lane];
+    sum[i][lane] = s;
+  }
+  cluster.sync();  // every CTA's sums are written
+  if (cluster.block_rank() == 0 && threadIdx.x < MT * 32) {
+    const int i = threadIdx.x >> 5, col = panel * kPanelRows + lane;
+    float s = sum[i][lane];
+    for (unsigned r = 1; r < cluster.num_blocks(); ++r) s += *cluster.map_shared_rank(&sum[i][lane], r);
+    if (i < m && col < n) {
+      s += reinterpret_cast<const float*>(tiled + hdr->bias_off)[col];
+      s = fminf(fmaxf(s, -65504.0f), 65504.0f);
+      y[(size_t)i * ldy + col] = __float2half_rn(s);
+    }
+  }
+  cluster.sync();  // the other CTAs' shared memory stays alive until it has been read
 }
 
 __global__ void a16_finish_kernel(const float* __restrict__ partial, const uint8_t* __restrict__ tiled, int slices,
@@ -281,8 +410,8 @@ int a16_slices(int m, int k, int n) {
 int w4a16_gemm_tcf16_tile(int m, int n);
 cudaError_t launch_w4a16_gemm_tcf16(const uint8_t*, const void*, void*, int, int, int, int, cudaStream_t);
 
-// The tensor-core path (fp16 operands, one rounding each) from this M on; below it the exact-integer dp4a kernel.
-bool w4a16_tensor_path(int m, int kernel) { return kernel == 4 ? m >= 64 : (kernel == 0 && m >= 128); }
+// The tensor-core path (fp16 operands, one rounding each) from M = 64 on; below it the exact-integer dp4a kernel.
+bool w4a16_tensor_path(int m, int kernel) { return (kernel == 4 || kernel == 0) && m >= 64; }
 
 size_t a16_workspace_bytes(int m, int k, int n) {
   const size_t rec = align_up((size_t)m * blob_num_blocks(k) * kActRecordBytesA16, 256);
@@ -305,10 +434,48 @@ static cudaError_t a16_launch_mt(const uint8_t* tiled, const uint8_t* recs, int 
   return cudaGetLastError();
 }
 
+template <int MT, typename T>
+static cudaError_t a16_launch_fused(const uint8_t* tiled, const void* x, int ldx, int m, int k, int n, __half* y, int ldy,
+                                    cudaStream_t st) {
+  const int nb = (int)blob_num_blocks(k), panels = (n + kPanelRows - 1) / kPanelRows;
+  int slices = (296 + panels - 1) / panels;  // two CTAs per SM where K allows; a slice keeps >= 8 groups
+  slices = max(1, min(min(slices, nb / 8), 8));
+  const int gps = (nb + slices - 1) / slices;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)panels, 1, (unsigned)slices);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 1;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = (unsigned)slices;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, a16_gemv_fused_kernel<MT, T>, tiled, static_cast<const T*>(x), ldx, m, k, n, gps, y, ldy);
+}
+
 cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, void* y, void* ws, int m, int k, int n,
                                 int ldx, int ldy, int kernel, cudaStream_t st) {
   const int nb = (int)blob_num_blocks(k);
   uint8_t* recs = static_cast<uint8_t*>(ws);
+  // One launch (quantization inside the kernel, K split over a cluster) while the matrix is small enough that
+  // launches, not bytes, set the time; every CTA repeats the quantization, which costs more than a second
+  // launch on large matrices (measured: M = 1 wins up to 8192 x 8192 and loses at 28672 x 8192; M = 4 wins at
+  // 1536 x 1536 and loses from 1536 x 8960 on).
+  const long long weights = (long long)n * k;
+  if (kernel == 0 && (m == 1 ? weights <= (128ll << 20) : (m <= 4 && weights * m <= (16ll << 20)))) {
+    const uint8_t* t8 = static_cast<const uint8_t*>(tiled);
+    __half* y16 = static_cast<__half*>(y);
+    if (x_dtype == 1) {
+      if (m == 1) return a16_launch_fused<1, __half>(t8, x, ldx, m, k, n, y16, ldy, st);
+      if (m == 2) return a16_launch_fused<2, __half>(t8, x, ldx, m, k, n, y16, ldy, st);
+      return a16_launch_fused<4, __half>(t8, x, ldx, m, k, n, y16, ldy, st);
+    }
+    if (m == 1) return a16_launch_fused<1, float>(t8, x, ldx, m, k, n, y16, ldy, st);
+    if (m == 2) return a16_launch_fused<2, float>(t8, x, ldx, m, k, n, y16, ldy, st);
+    return a16_launch_fused<4, float>(t8, x, ldx, m, k, n, y16, ldy, st);
+  }
   if (w4a16_tensor_path(m, kernel)) {
     const int nt = w4a16_gemm_tcf16_tile(m, n), m_pad = (m + nt - 1) / nt * nt;
     if (x_dtype == 1)

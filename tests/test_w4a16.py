@@ -168,7 +168,8 @@ SHAPES = [
 # (m, k, n, kernel): the tensor-core kernel on every tile width, ragged M / N / K, and the dp4a kernel at large M
 TENSOR_SHAPES = [
     (64, 256, 128, 4), (100, 100, 33, 4), (130, 512, 320, 4), (200, 1176, 1280, 4), (512, 1536, 1536, 4),
-    (512, 1536, 8960, 4), (512, 8960, 1536, 4), (300, 1536, 8960, 0), (512, 1536, 256, 2), (130, 512, 320, 2),
+    (512, 1536, 8960, 4), (512, 8960, 1536, 4), (300, 1536, 8960, 0), (70, 256, 96, 0), (512, 1536, 256, 2), (130, 512, 320, 2), (63, 8192, 512, 0),
+    (1, 1536, 256, 2), (3, 100, 33, 2), (4, 8960, 1536, 2),   # the record-based dp4a kernel where auto takes the fused one
 ]
 
 
@@ -190,7 +191,7 @@ def test_gpu_tensor_core_kernel_matches_oracle(m, k, n, kernel):
     torch.cuda.synchronize()
     mb.check_device_status()
     got = y.cpu().numpy()
-    tensor = kernel == 4 or (kernel == 0 and m >= 128)
+    tensor = kernel == 4 or (kernel == 0 and m >= 64)
     diff = np.abs(got.astype(np.float32) - ref.astype(np.float32))
     assert (diff <= _bar(ref, tensor)).all(), f"max diff {diff.max()} at {np.unravel_index(diff.argmax(), diff.shape)}"
     rms = np.sqrt((ref.astype(np.float64) ** 2).mean())
@@ -225,7 +226,7 @@ def test_gpu_linear_matches_oracle(m, k, n, x_dtype):
     got = y.cpu().numpy()
     assert got.dtype == np.float16 and got.shape == (m, n)
     diff = np.abs(got.astype(np.float32) - ref.astype(np.float32))
-    tensor = m >= 128   # the automatic choice
+    tensor = m >= 64   # the automatic choice
     assert (diff <= _bar(ref, tensor)).all(), f"max diff {diff.max()} at {np.unravel_index(diff.argmax(), diff.shape)}"
     # most outputs are the same fp16 value
     assert (got == ref).mean() > (0.3 if tensor else 0.9)
