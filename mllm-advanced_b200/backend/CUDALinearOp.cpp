@@ -40,6 +40,15 @@ bool isW4A32ImplType(LinearOpImplType t) {
   }
 }
 
+bool isW4A16ImplType(LinearOpImplType t) {
+  switch (t) {
+    case LinearOpImplType::KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk_qsi8d32p1x8_qai4c32p4x8_1x4:
+    case LinearOpImplType::KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk_qsi8d32p4x4_qai4c32p4x4_8x4:
+    case LinearOpImplType::KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk_qsi8d32p4x8_qai4c32p4x8_8x4_i8mm: return true;
+    default: return false;
+  }
+}
+
 CUDAW4A32LinearOp::CUDAW4A32LinearOp(const LinearOpCargo& cargo) : LinearOp(cargo) {}
 
 CUDAW4A32LinearOp::~CUDAW4A32LinearOp() { releaseDevice(); }
@@ -91,11 +100,48 @@ void* uploadW4A32Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, in
   return tiled_dev;
 }
 
+void* uploadW4A16Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, int k, const std::string& name) {
+  std::vector<unsigned char> owned;
+  const void* blob = nullptr;
+  size_t blob_bytes = 0;
+  if (weight.dtype() == kInt8) {
+    blob = weight.ptr<unsigned char>();
+    blob_bytes = weight.numel();
+  } else if (weight.dtype() == kFp32) {
+    MLLM_RT_ASSERT_EQ((size_t)weight.numel(), (size_t)n * (size_t)k);
+    const bool has_bias = want_bias && bias.dtype() == kFp32 && (int)bias.numel() == n;
+    MLLMB200_CHECK(mllmb200_w4a16_prepack_size(n, k, has_bias, &blob_bytes));
+    owned.resize(blob_bytes);
+    MLLMB200_CHECK(mllmb200_w4a16_quant_prepack(weight.ptr<float>(), has_bias ? bias.ptr<float>() : nullptr, n, k,
+                                                owned.data()));
+    blob = owned.data();
+  } else {
+    MLLM_ERROR_EXIT(kError, "{}: weight dtype must be int8 (pre-packed) or fp32", name);
+  }
+  int bn = 0, bk = 0, has_bias = 0;
+  MLLMB200_CHECK(mllmb200_w4a16_blob_info(blob, blob_bytes, &bn, &bk, &has_bias));
+  if (bn != n || bk != k) { MLLM_ERROR_EXIT(kError, "{}: blob is {}x{} but the layer is {}x{}", name, bn, bk, n, k); }
+
+  auto stream = static_cast<cudaStream_t>(currentW4A32Stream());
+  void* blob_dev = nullptr;
+  void* tiled_dev = nullptr;
+  size_t tiled_bytes = 0;
+  MLLMB200_CHECK(mllmb200_w4a16_tiled_size(n, k, &tiled_bytes));
+  MLLMB200_CHECK_CUDA(cudaMalloc(&blob_dev, blob_bytes));
+  MLLMB200_CHECK_CUDA(cudaMalloc(&tiled_dev, tiled_bytes));
+  MLLMB200_CHECK_CUDA(cudaMemcpyAsync(blob_dev, blob, blob_bytes, cudaMemcpyHostToDevice, stream));
+  MLLMB200_CHECK(mllmb200_w4a16_repack_device(blob_dev, n, k, has_bias, 0, n, tiled_dev, stream));
+  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` and blob_dev go away below
+  MLLMB200_CHECK_CUDA(cudaFree(blob_dev));
+  return tiled_dev;
+}
+
 void CUDAW4A32LinearOp::load(const std::shared_ptr<ParameterLoader>& ploader) {
   LinearOp::load(ploader);  // weight_ / bias_ by name (mllm/Core/AOps/LinearOp.cpp:60-63)
-  if (!isW4A32ImplType(cargo_.impl_type_)) {
-    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: impl type {} is not a W4A32 type; this backend implements only those",
-                    name(), int(cargo_.impl_type_));
+  a16_ = isW4A16ImplType(cargo_.impl_type_);
+  if (!a16_ && !isW4A32ImplType(cargo_.impl_type_)) {
+    MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: impl type {} is neither a W4A32 nor a W4A16 Kai type; this backend "
+                    "implements only those", name(), int(cargo_.impl_type_));
   }
   releaseDevice();
   k_ = cargo_.in_channels;
@@ -106,7 +152,8 @@ void CUDAW4A32LinearOp::load(const std::shared_ptr<ParameterLoader>& ploader) {
     MLLM_RT_ASSERT_EQ(shape[0], n_);
     MLLM_RT_ASSERT_EQ(shape[1], k_);
   }
-  tiled_dev_ = uploadW4A32Weights(weight_, bias_, cargo_.bias, n_, k_, "CUDAW4A32LinearOp " + name());
+  tiled_dev_ = a16_ ? uploadW4A16Weights(weight_, bias_, cargo_.bias, n_, k_, "CUDAW4A32LinearOp " + name())
+                    : uploadW4A32Weights(weight_, bias_, cargo_.bias, n_, k_, "CUDAW4A32LinearOp " + name());
 }
 
 void CUDAW4A32LinearOp::reshape(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) {
@@ -114,14 +161,37 @@ void CUDAW4A32LinearOp::reshape(const std::vector<Tensor>& inputs, std::vector<T
   auto o_shape = i.shape();
   MLLM_RT_ASSERT_EQ(o_shape[o_shape.size() - 1], cargo_.in_channels);
   o_shape[o_shape.size() - 1] = cargo_.out_channels;
-  // W4A32: fp32 out whatever the tile (ArmLinearOp::reshape, LinearOp.cpp:252-259)
-  outputs.emplace_back(Tensor::empty(o_shape, kFp32, i.device()));
+  // W4A32: fp32 out whatever the tile; W4A16: fp16 out (ArmLinearOp::reshape, LinearOp.cpp:246-259).
+  // reshape can run before load: decide from the cargo, not from a16_
+  outputs.emplace_back(Tensor::empty(o_shape, isW4A16ImplType(cargo_.impl_type_) ? kFp16 : kFp32, i.device()));
 }
 
 void CUDAW4A32LinearOp::forward(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) {
   const auto& x = inputs[0];
   auto& y = outputs[0];
   if (!tiled_dev_) { MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: forward before load", name()); }
+  if (a16_) {
+    // fp16 activations (the reference's model configs) or fp32 (its second matmul overload, kai_linear.cpp:853-901)
+    if ((x.dtype() != kFp16 && x.dtype() != kFp32) || x.device() != kCUDA || y.dtype() != kFp16) {
+      MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: W4A16 needs an fp16 or fp32 input on the CUDA device and an fp16 output",
+                      name());
+    }
+    const int m = (int)(x.numel() / (size_t)k_);
+    size_t need = 0;
+    MLLMB200_CHECK(mllmb200_w4a16_workspace_size(m, k_, n_, &need));
+    if (need > workspace_bytes_) {
+      if (workspace_dev_) {
+        MLLMB200_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(currentW4A32Stream())));
+        MLLMB200_CHECK_CUDA(cudaFree(workspace_dev_));
+      }
+      MLLMB200_CHECK_CUDA(cudaMalloc(&workspace_dev_, need));
+      workspace_bytes_ = need;
+    }
+    MLLMB200_CHECK(mllmb200_w4a16_linear_forward(x.ptr<unsigned char>(), x.dtype() == kFp16 ? MLLMB200_DTYPE_F16 : MLLMB200_DTYPE_F32,
+                                                 tiled_dev_, y.ptr<unsigned char>(), workspace_dev_, m, k_, n_, k_, n_,
+                                                 currentW4A32Stream()));
+    return;
+  }
   if (x.dtype() != kFp32 || x.device() != kCUDA) {
     MLLM_ERROR_EXIT(kError, "CUDAW4A32LinearOp {}: input must be fp32 on the CUDA device", name());
   }

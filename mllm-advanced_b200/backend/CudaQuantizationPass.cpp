@@ -14,6 +14,8 @@ namespace mllm::cuda {
 
 namespace {
 constexpr const char* kFamily = "KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk";
+// the W4A16 sibling (KQP_linear_f16_qsi8d32p_qai4c32p_mxk_nxk, KaiQuantizationPass.cpp:301-392 of the reference)
+constexpr const char* kFamilyA16 = "KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk";
 
 // "family:tile" -> family
 std::string implFamily(const std::string& impl) {
@@ -24,7 +26,9 @@ std::string implFamily(const std::string& impl) {
 
 bool CudaQuantizationPass::quantizeLinear(const ir::op_ptr_t& op) {
   auto* linear = (LinearOp*)(op->cast_<ir::linalg::LinearOp>()->getAOp());
-  if (implFamily(cfg_.opImplType(linear->name())) != kFamily) return false;
+  const std::string family = implFamily(cfg_.opImplType(linear->name()));
+  const bool a16 = family == kFamilyA16;
+  if (family != kFamily && !a16) return false;
 
   const Tensor weight = linear->weight();
   const Tensor bias = linear->bias();
@@ -41,15 +45,18 @@ bool CudaQuantizationPass::quantizeLinear(const ir::op_ptr_t& op) {
   }
 
   size_t bytes = 0;
-  int st = mllmb200_w4a32_prepack_size(n, k, has_bias ? 1 : 0, &bytes);
+  int st = a16 ? mllmb200_w4a16_prepack_size(n, k, has_bias ? 1 : 0, &bytes)
+               : mllmb200_w4a32_prepack_size(n, k, has_bias ? 1 : 0, &bytes);
   if (st != MLLMB200_OK) {
     MLLM_WARN("CudaQuantizationPass: {}: {}", linear->name(), mllmb200_status_str(st));
     return false;
   }
   // a flat int8 buffer stands for the packed weight; it cannot be read as an ordinary tensor
   Tensor packed = Tensor::empty({(int32_t)bytes}, kInt8, kCPU).alloc();
-  st = mllmb200_w4a32_quant_prepack(weight.ptr<float>(), has_bias ? bias.ptr<float>() : nullptr, n, k,
-                                    MLLMB200_SCALE_BF16_TRUNC, packed.ptr<uint8_t>());
+  st = a16 ? mllmb200_w4a16_quant_prepack(weight.ptr<float>(), has_bias ? bias.ptr<float>() : nullptr, n, k,
+                                          packed.ptr<uint8_t>())
+           : mllmb200_w4a32_quant_prepack(weight.ptr<float>(), has_bias ? bias.ptr<float>() : nullptr, n, k,
+                                          MLLMB200_SCALE_BF16_TRUNC, packed.ptr<uint8_t>());
   if (st != MLLMB200_OK) {
     MLLM_WARN("CudaQuantizationPass: {}: {}", linear->name(), mllmb200_status_str(st));
     return false;

@@ -4,10 +4,12 @@
 // mllm/Backends/Arm/Kernels/kai_linear.cpp:680-951):
 //   y[m,n] = fp16( clamp( sum_b a_s[m,b] * ( s[n,b] * float(dot_b) + z[n,b] * float(sum_b) ) + bias[n] ) )
 //   dot_b = sum_{k in b} a_q[m,k] * (u[n,k] - 8),  sum_b = sum_{k in b} a_q[m,k]
-// Kernels: repack (blob -> 768-byte cells), activation quantization (48-byte records), and one dp4a
-// kernel for every M: a CTA owns one 32-row panel (lane = output row) and MT rows of x, its 8 warps split
-// the K groups, partial sums meet in shared memory; for small grids K is also split over gridDim.z with
-// fp32 partials in the workspace and a finishing kernel that adds them in slice order (deterministic).
+// Kernels here: the repack (blob -> 768-byte cells), and three ways through the product, chosen by M in
+// launch_w4a16_linear:
+//   a16_gemv_fused_kernel            M <= 4 on small matrices: one launch, quantization inside, cluster K-split
+//   a16_act_quant_kernel + a16_linear_kernel (+ a16_finish_kernel)   48-byte records, dp4a, any M
+//   a16_act_quant_blocks_f16_kernel + the tcgen05 fp16 GEMM of gemm_tcf16.cu (A16 instantiation)   M >= 64
+// In the dp4a kernels a CTA owns one 32-row panel (lane = output row) and its 8 warps split the K groups.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>

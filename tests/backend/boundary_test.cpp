@@ -9,6 +9,9 @@
 //      the int8 blob's nibble and scale sections must equal the oracle's quantizer bit for bit.
 //   2. model.load(blob) -> model.to(kCUDA) -> y = model(x): outputs within 1e-3 * rms of the oracle,
 //      for M = 1 (GEMV), a [2,3,K] batch (M = 6) and M = 64 (tcgen05 path).
+//   3. The same two steps for the W4A16 sibling format (impl type
+//      KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk:qsi8d32p4x8_qai4c32p4x8_8x4_i8mm): blob sections equal
+//      oracle/w4a16_oracle.c bit for bit, fp16 activations in, fp16 out.
 // Exit code 0 = all passed.
 #include <cuda_runtime.h>
 
@@ -37,6 +40,13 @@ extern "C" {  // oracle/w4a32_oracle.c
 void oracle_quant_nxk_qs4c32_f32(size_t n, size_t k, size_t bl, const float* rhs, uint8_t* q, uint16_t* s, int mode);
 void oracle_linear_w4a32(size_t m, size_t n, size_t k, const float* x, const uint8_t* q, const uint16_t* s, int mode,
                          const float* bias, float* y, void* workspace);
+// oracle/w4a16_oracle.c
+void oracle_w4a16_quant_nxk_qai4c32_f32(size_t n, size_t k, size_t bl, const float* rhs, uint8_t* q, float* zeros,
+                                        float* scales, int32_t* zp);
+void oracle_linear_w4a16(size_t m, size_t n, size_t k, const float* x, const uint8_t* q, const float* scales,
+                         const float* zeros, const float* bias, uint16_t* y_f16, void* ws);
+uint16_t oracle_cast_f16_f32(float f);
+float oracle_cast_f32_f16(uint16_t h);
 }
 
 using namespace mllm;
@@ -44,14 +54,15 @@ using namespace mllm;
 namespace {
 
 constexpr auto kImpl = LinearOpImplType::kKaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk_qai8dxp4x8_qsi4c32p4x8_8x4x32;
+constexpr auto kImplA16 = LinearOpImplType::KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk_qsi8d32p4x8_qai4c32p4x8_8x4_i8mm;
 
 class SingleLinear final : public nn::Module {
  public:
   nn::Linear fc_;
   SingleLinear() = default;
-  SingleLinear(const std::string& name, int k, int n, bool bias) {
+  SingleLinear(const std::string& name, int k, int n, bool bias, LinearOpImplType impl = kImpl) {
     selfAssignName(name);
-    fc_ = reg<nn::Linear>("fc", k, n, bias, false, kImpl);
+    fc_ = reg<nn::Linear>("fc", k, n, bias, false, impl);
   }
   std::vector<Tensor> forward(const std::vector<Tensor>& inputs) override { return {fc_(inputs[0])}; }
 };
@@ -199,6 +210,116 @@ void runCase(const std::string& model, int k, int n, bool with_bias, const std::
   }
 }
 
+// The W4A16 sibling format through the same plugin API: impl type 11, fp16 activations in, fp16 out.
+void runCaseA16(const std::string& model, int k, int n, bool with_bias, const std::vector<std::vector<int32_t>>& x_shapes) {
+  const std::string layer = model + ".fc";
+  auto& ctx = MllmEngineCtx::instance();
+  char label[256];
+  Tensor w = Tensor::empty({n, k}, kFp32, kCPU).alloc();
+  Tensor b = Tensor::empty({n}, kFp32, kCPU).alloc();
+  for (int i = 0; i < n * k; ++i) w.ptr<float>()[i] = frand() * 0.05f;
+  for (int i = 0; i < n; ++i) b.ptr<float>()[i] = frand() * 0.1f;
+  w.setName(layer + ".weight");
+  b.setName(layer + ".bias");
+
+  auto host_op = ctx.getBackend(kCPU)->createOp(
+      OpType::kLinear, LinearOpCargo{.in_channels = k, .out_channels = n, .bias = with_bias, .transpose = false});
+  host_op->setName(layer);
+  auto* host_linear = (LinearOp*)host_op.get();
+  host_linear->weight() = w;
+  if (with_bias) host_linear->bias() = b;
+  MllmModelCfg cfg;
+  cfg.rawJson()["Ops"][layer] = {{"type", "Linear"},
+                                 {"implType", "KaiLinear_f16_qsi8d32p_qai4c32p_mxk_nxk:qsi8d32p4x8_qai4c32p4x8_8x4_i8mm"}};
+  auto ir_ctx = flatModule(host_op);
+  auto pass = cuda::createCudaQuantizationPass(cfg);
+  ir::PassManager pm(ir_ctx);
+  pm.reg(pass);
+  const bool pm_ok = pm.run();
+  std::snprintf(label, sizeof(label), "W4A16 K=%d N=%d bias=%d: pass ran and quantized one linear", k, n, (int)with_bias);
+  check(pm_ok && pass->quantizedCount() == 1, label);
+  Tensor blob = host_linear->weight();
+  check(blob.dtype() == kInt8 && blob.shape().size() == 1 && blob.name() == layer + ".weight",
+        "  weight replaced by a 1-D int8 tensor of the same name");
+
+  const size_t ns = (size_t)(k + 1) / 2, nb = (size_t)(k + 31) / 32;
+  std::vector<uint8_t> q_ref(n * ns);
+  std::vector<float> s_ref(n * nb), z_ref(n * nb);
+  oracle_w4a16_quant_nxk_qai4c32_f32(n, k, 32, w.ptr<float>(), q_ref.data(), z_ref.data(), s_ref.data(), nullptr);
+  size_t off_q = 0, off_s = 0, off_z = 0, off_b = 0;
+  mllmb200_w4a16_blob_offsets(n, k, with_bias, &off_q, &off_s, &off_z, &off_b);
+  const uint8_t* blob_bytes = blob.ptr<uint8_t>();
+  check(std::memcmp(blob_bytes + off_q, q_ref.data(), q_ref.size()) == 0, "  nibbles bit-identical to the oracle");
+  check(std::memcmp(blob_bytes + off_s, s_ref.data(), s_ref.size() * 4) == 0, "  scales bit-identical to the oracle");
+  check(std::memcmp(blob_bytes + off_z, z_ref.data(), z_ref.size() * 4) == 0, "  zero terms bit-identical to the oracle");
+  if (with_bias) check(std::memcmp(blob_bytes + off_b, b.ptr<float>(), n * 4) == 0, "  bias carried inside the blob");
+
+  const std::string file = "/tmp/mllmb200_boundary_" + model + ".mllm";
+  {
+    std::unordered_map<std::string, Tensor> params;
+    params.insert({layer + ".weight", blob});
+    if (with_bias) params.insert({layer + ".bias", host_linear->bias()});
+    mllm::write(file, params, model);
+  }
+  auto ploader = mllm::load(file);
+  {
+    auto back = ploader->params().find(layer + ".weight");
+    bool ok = back != ploader->params().end();
+    if (ok) {
+      Tensor t(back->second);
+      ok = t.dtype() == kInt8 && (size_t)t.numel() == (size_t)blob.numel() &&
+           std::memcmp(t.ptr<uint8_t>(), blob.ptr<uint8_t>(), blob.numel()) == 0;
+    }
+    check(ok, "  .mllm round trip (reference ParameterWriter -> ParameterLoader): blob byte-identical");
+  }
+  if (g_host_only) {
+    std::remove(file.c_str());
+    return;
+  }
+  auto net = SingleLinear(model, k, n, with_bias, kImplA16);
+  net.load(ploader);
+  net.to(kCUDA);
+  auto stream = static_cast<cudaStream_t>(cuda::currentW4A32Stream());
+  for (const auto& shape : x_shapes) {
+    size_t numel = 1;
+    for (auto d : shape) numel *= (size_t)d;
+    const int m = (int)(numel / (size_t)k);
+    std::vector<uint16_t> x_half(numel), y_half((size_t)m * n), y_ref((size_t)m * n);
+    std::vector<float> x_wide(numel);
+    for (size_t i = 0; i < numel; ++i) {
+      x_half[i] = oracle_cast_f16_f32(frand() * 2.0f);
+      x_wide[i] = oracle_cast_f32_f16(x_half[i]);
+    }
+    Tensor x = Tensor::empty(shape, kFp16, kCUDA).alloc();
+    cudaMemcpyAsync(x.ptr<uint8_t>(), x_half.data(), numel * 2, cudaMemcpyHostToDevice, stream);
+    Tensor y = net(x)[0];
+    cudaMemcpyAsync(y_half.data(), y.ptr<uint8_t>(), y_half.size() * 2, cudaMemcpyDeviceToHost, stream);
+    const cudaError_t e = cudaStreamSynchronize(stream);
+    const int dev_status = mllmb200_check_device_status(stream);
+    std::vector<uint8_t> ws((size_t)m * nb * 36);
+    oracle_linear_w4a16(m, n, k, x_wide.data(), q_ref.data(), s_ref.data(), z_ref.data(),
+                        with_bias ? b.ptr<float>() : nullptr, y_ref.data(), ws.data());
+    double sq = 0;
+    for (size_t i = 0; i < y_ref.size(); ++i) sq += (double)oracle_cast_f32_f16(y_ref[i]) * oracle_cast_f32_f16(y_ref[i]);
+    const double rms = std::sqrt(sq / y_ref.size());
+    // dp4a kernels: 1e-3 * rms; tensor-core kernel (M >= 64, operands rounded to fp16): 4e-3 * rms; + 2 fp16 ulps
+    const double bar = m >= 64 ? 4e-3 : 1e-3;
+    double worst = 0;
+    bool within = true;
+    for (size_t i = 0; i < y_ref.size(); ++i) {
+      const double r = oracle_cast_f32_f16(y_ref[i]), g = oracle_cast_f32_f16(y_half[i]);
+      const double d = std::fabs(g - r);
+      worst = std::fmax(worst, d);
+      within = within && d <= bar * rms + 2.0 * std::fabs(r) / 1024.0;
+    }
+    auto y_shape = y.shape();
+    bool shape_ok = y_shape.size() == shape.size() && y_shape.back() == n && y.dtype() == kFp16 && y.device() == kCUDA;
+    for (size_t d = 0; d + 1 < shape.size(); ++d) shape_ok = shape_ok && y_shape[d] == shape[d];
+    std::snprintf(label, sizeof(label), "  W4A16 forward M=%d: max|diff| %.3e (rms %.3e), fp16 out, shape/device ok", m, worst, rms);
+    check(e == cudaSuccess && dev_status == 0 && shape_ok && within, label);
+  }
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -216,6 +337,8 @@ int main(int argc, char** argv) {
 
   runCase("model", 1536, 256, true, {{1, 1, 1536}, {2, 3, 1536}, {1, 64, 1536}});
   runCase("vit", 1176, 160, false, {{1, 1176}, {40, 1176}});  // K not a multiple of 32 (Qwen2VL patch embed width)
+  runCaseA16("a16", 1536, 256, true, {{1, 1, 1536}, {2, 3, 1536}, {1, 64, 1536}});
+  runCaseA16("a16vit", 1176, 160, false, {{1, 1176}, {40, 1176}});
 
   std::printf("%s (%d failures)\n", g_failures == 0 ? "BOUNDARY TEST PASSED" : "BOUNDARY TEST FAILED", g_failures);
   std::fflush(stdout);
