@@ -800,6 +800,9 @@ def run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
         with torch.cuda.stream(stream):
             one_pass()
         stream.synchronize()
+        if args.w4a16_once:  # launch-list runs under ncu: one eager pass per section, nothing timed
+            out[key] = {"passes": 1}
+            continue
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
             one_pass()
@@ -826,6 +829,9 @@ def run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
         with torch.cuda.stream(stream):
             big_pass()
         stream.synchronize()
+        if args.w4a16_once:
+            out[key] = {"passes": 1}
+            continue
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
             big_pass()
@@ -950,6 +956,7 @@ def main():
     ap.add_argument("--no-config4", action="store_true", help="skip the single-GPU section on BASELINE config 4's large matrix")
     ap.add_argument("--w4a16-only", action="store_true", help="only the section on the W4A16 sibling path")
     ap.add_argument("--no-w4a16", action="store_true", help="skip the section on the W4A16 sibling path")
+    ap.add_argument("--w4a16-once", action="store_true", help="with --w4a16-only: one untimed eager pass per section (for ncu launch lists)")
     ap.add_argument("--decoder-only", action="store_true", help="only the whole-model prefill + decode section")
     ap.add_argument("--decoder-prompt", type=int, default=512, help="prompt length of the decoder section")
     ap.add_argument("--decoder-steps", type=int, default=128, help="greedy steps of the decoder section (small values for ncu)")
