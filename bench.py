@@ -796,7 +796,7 @@ def run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
         def one_pass():
             for lw in layers:
                 for w in lw:
-                    w4a16.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream)
+                    w4a16.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream, pdl=not args.no_pdl)
         with torch.cuda.stream(stream):
             one_pass()
         stream.synchronize()

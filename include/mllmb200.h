@@ -229,7 +229,11 @@ MLLMB200_API int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, c
  * on), 2 dp4a kernel (exact int32 block sums, fp32 combination as written above), 4 tcgen05 fp16 kernel (M >= 64):
  * weight operand fp16(((u-8)*s + z) * 2^E) and activation operand fp16(a_q * a_s), one rounding each, fp32
  * accumulation over all of K in tensor memory - it differs from the formula above by those roundings
- * (about 3e-4 of the row's rms, the size of the fp16 output's own rounding). */
+ * (about 3e-4 of the row's rms, the size of the fp16 output's own rounding).
+ * OR 0x100 into `kernel` to launch the single-launch kernel (M <= 4) with programmatic dependent launch: it
+ * then fetches its first weights while the previous kernel of the stream drains, and reads x only after
+ * that kernel has completed.  Use it only when x and y are not written by anything else on the stream that
+ * could still be running (the usual chain of linears on one stream is fine). */
 MLLMB200_API int mllmb200_w4a16_linear_forward_ex(const void* x_dev, int x_dtype, const void* tiled_dev, void* y_dev,
                                                   void* ws_dev, int M, int K, int N, int ldx, int ldy, int kernel,
                                                   void* stream);

@@ -47,8 +47,9 @@ int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, const void* ti
 
 int mllmb200_w4a16_linear_forward_ex(const void* x_dev, int x_dtype, const void* tiled_dev, void* y_dev, void* ws_dev,
                                      int M, int K, int N, int ldx, int ldy, int kernel, void* stream) {
-  if (kernel != 0 && kernel != 2 && kernel != 4) return MLLMB200_INVALID_ARG;
-  if (kernel == 4 && M < 64) return MLLMB200_UNSUPPORTED;
+  const int family = kernel & 0xff;
+  if ((kernel & ~0x1ff) || (family != 0 && family != 2 && family != 4)) return MLLMB200_INVALID_ARG;
+  if (family == 4 && M < 64) return MLLMB200_UNSUPPORTED;
   if (!x_dev || !tiled_dev || !y_dev || !ws_dev || M <= 0 || K <= 0 || N <= 0 || ldx < K || ldy < N)
     return MLLMB200_INVALID_ARG;
   if (x_dtype != MLLMB200_DTYPE_F32 && x_dtype != MLLMB200_DTYPE_F16) return MLLMB200_INVALID_ARG;

@@ -68,12 +68,14 @@ struct TfSmem {
   static constexpr int kCell = A16 ? kCellBytesA16 : kCellBytes;
   // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
   // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
-  static constexpr int kGroups = (A16 || NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
+  static constexpr int kGroups = (NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
   // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
   // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
   // the number of tiles in flight, so both rings are as deep as shared memory allows.
-  static constexpr int kStages = A16 ? (NT >= 256 ? 4 : 5) : (NT >= 256 && ROWS == 128) ? 4 : 3;
-  static constexpr int kAStages = kStages;  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages)
+  static constexpr int kStages = (NT >= 256 && ROWS == 128) ? 4 : 3;
+  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages); the 768-byte cells of the
+  // W4A16 format leave room for two operand stages of 4 K-groups
+  static constexpr int kAStages = (A16 && NT < 256) ? 2 : kStages;
   static constexpr int kPanels = ROWS / kPanelRows;
   static constexpr int kGroupABytes = ROWS * kGroup * 2;  // one K-group of the A operand (8 or 16 KB)
   static constexpr int kRawBytes = kPanels * kGroups * kCell;

@@ -318,10 +318,12 @@ __global__ void __launch_bounds__(256) a16_gemv_fused_kernel(const uint8_t* __re
   int g = g_begin + warp;
   A16Cell cur;
   float xcur[MT];
-  if (g < g_end) {
-    cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
-    load_x(g, xcur);
-  }
+  // Under programmatic dependent launch the weights (never written by a kernel) are fetched while the
+  // previous kernel of the stream drains; the activations, which it may have produced, only after it is done.
+  pdl_launch_dependents();
+  if (g < g_end) cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
+  pdl_wait_prior();
+  if (g < g_end) load_x(g, xcur);
   for (; g < g_end; g += 8) {
     A16Cell nxt = cur;
     float xnxt[MT];
@@ -438,7 +440,7 @@ static cudaError_t a16_launch_mt(const uint8_t* tiled, const uint8_t* recs, int 
 
 template <int MT, typename T>
 static cudaError_t a16_launch_fused(const uint8_t* tiled, const void* x, int ldx, int m, int k, int n, __half* y, int ldy,
-                                    cudaStream_t st) {
+                                    bool pdl, cudaStream_t st) {
   const int nb = (int)blob_num_blocks(k), panels = (n + kPanelRows - 1) / kPanelRows;
   int slices = (296 + panels - 1) / panels;  // two CTAs per SM where K allows; a slice keeps >= 8 groups
   slices = max(1, min(min(slices, nb / 8), 8));
@@ -447,18 +449,22 @@ static cudaError_t a16_launch_fused(const uint8_t* tiled, const void* x, int ldx
   cfg.gridDim = dim3((unsigned)panels, 1, (unsigned)slices);
   cfg.blockDim = dim3(256, 1, 1);
   cfg.stream = st;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 1;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = (unsigned)slices;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)slices;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, a16_gemv_fused_kernel<MT, T>, tiled, static_cast<const T*>(x), ldx, m, k, n, gps, y, ldy);
 }
 
 cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, void* y, void* ws, int m, int k, int n,
-                                int ldx, int ldy, int kernel, cudaStream_t st) {
+                                int ldx, int ldy, int kernel_and_flags, cudaStream_t st) {
+  const int kernel = kernel_and_flags & 0xff;
+  const bool pdl = (kernel_and_flags & 0x100) != 0;  // only the single-launch kernel takes part
   const int nb = (int)blob_num_blocks(k);
   uint8_t* recs = static_cast<uint8_t*>(ws);
   // One launch (quantization inside the kernel, K split over a cluster) while the matrix is small enough that
@@ -470,13 +476,13 @@ cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, v
     const uint8_t* t8 = static_cast<const uint8_t*>(tiled);
     __half* y16 = static_cast<__half*>(y);
     if (x_dtype == 1) {
-      if (m == 1) return a16_launch_fused<1, __half>(t8, x, ldx, m, k, n, y16, ldy, st);
-      if (m == 2) return a16_launch_fused<2, __half>(t8, x, ldx, m, k, n, y16, ldy, st);
-      return a16_launch_fused<4, __half>(t8, x, ldx, m, k, n, y16, ldy, st);
+      if (m == 1) return a16_launch_fused<1, __half>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
+      if (m == 2) return a16_launch_fused<2, __half>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
+      return a16_launch_fused<4, __half>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
     }
-    if (m == 1) return a16_launch_fused<1, float>(t8, x, ldx, m, k, n, y16, ldy, st);
-    if (m == 2) return a16_launch_fused<2, float>(t8, x, ldx, m, k, n, y16, ldy, st);
-    return a16_launch_fused<4, float>(t8, x, ldx, m, k, n, y16, ldy, st);
+    if (m == 1) return a16_launch_fused<1, float>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
+    if (m == 2) return a16_launch_fused<2, float>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
+    return a16_launch_fused<4, float>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
   }
   if (w4a16_tensor_path(m, kernel)) {
     const int nt = w4a16_gemm_tcf16_tile(m, n), m_pad = (m + nt - 1) / nt * nt;

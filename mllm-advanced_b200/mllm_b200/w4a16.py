@@ -81,7 +81,7 @@ class W4A16Weights:
 KERNEL_AUTO, KERNEL_DP4A, KERNEL_TC_F16 = 0, 2, 4
 
 
-def linear_forward(x, weights, out=None, workspace=None, stream=None, kernel=KERNEL_AUTO):
+def linear_forward(x, weights, out=None, workspace=None, stream=None, kernel=KERNEL_AUTO, pdl=False):
     """fp16 y = W4A16 linear of x (torch float32 or float16 [M,K] on the GPU, last dim contiguous).
     kernel: KERNEL_AUTO (dp4a below M = 64, tensor cores from there on), KERNEL_DP4A, KERNEL_TC_F16 (M >= 64)."""
     import torch
@@ -94,6 +94,7 @@ def linear_forward(x, weights, out=None, workspace=None, stream=None, kernel=KER
         workspace = torch.empty(workspace_size(m, k, weights.n), dtype=torch.uint8, device=x.device)
     _check(lib().mllmb200_w4a16_linear_forward_ex(x.data_ptr(), 1 if x.dtype == torch.float16 else 0,
                                                   weights.tiled.data_ptr(), out.data_ptr(), workspace.data_ptr(), m, k,
-                                                  weights.n, x.stride(0), out.stride(0), kernel, _stream_ptr(stream)),
+                                                  weights.n, x.stride(0), out.stride(0), kernel | (0x100 if pdl else 0),
+                                                  _stream_ptr(stream)),
            "w4a16_linear_forward")
     return out

@@ -290,3 +290,31 @@ def test_gpu_strided_rows_and_bad_header():
     with pytest.raises(mb.MllmB200Error):
         mb.check_device_status()
     mb.check_device_status()   # the status word is cleared by the read
+
+
+@pytest.mark.gpu
+def test_gpu_chain_with_programmatic_dependent_launch():
+    """A chain of single-launch linears (each reads what the previous one wrote) gives the same bits with and
+    without programmatic dependent launch."""
+    import torch
+    from mllm_b200 import w4a16
+    import mllm_b200 as mb
+    rng = np.random.default_rng(21)
+    dims = [1536, 256, 1536, 512, 1536]
+    wts = [w4a16.W4A16Weights.from_blob(w4a16.quant_prepack(_weights(dims[i + 1], dims[i], 30 + i, spread=0.05)))
+           for i in range(len(dims) - 1)]
+    x0 = torch.from_numpy(rng.standard_normal((1, dims[0])).astype(np.float16)).cuda()
+    outs = {}
+    for pdl in (False, True):
+        bufs = [torch.zeros((1, d), dtype=torch.float16, device="cuda") for d in dims[1:]]
+        for _ in range(3):   # repeated so that a kernel could overtake the one before it if the ordering were wrong
+            cur = x0
+            for w, b in zip(wts, bufs):
+                w4a16.linear_forward(cur, w, out=b, pdl=pdl)
+                cur = b
+        torch.cuda.synchronize()
+        mb.check_device_status()
+        outs[pdl] = [b.cpu().numpy() for b in bufs]
+    for a, b in zip(outs[False], outs[True]):
+        assert np.array_equal(a, b)
+    assert np.abs(outs[True][-1].astype(np.float32)).max() > 0
