@@ -815,6 +815,30 @@ def run_w4a16(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
                     "frac_hbm": by / (ms * 1e-3) / 1e9 / hbm_peak, "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / tensor_peak,
                     "peak_kind": f"of {peak_kind}", "how": "CUDA graph of 196 calls (activation quantization + kernel each)"}
         del g
+        if m == 1 and not args.w4a16_once:
+            # the same step with (q,k,v) and (gate,up) as grouped calls: 4 launches per layer
+            ysb = {n: torch.empty((m, n), device="cuda", dtype=torch.float16) for n in (256, 8960)}
+
+            def grouped_pass():
+                for q, kk, v, o, gate, up, down in layers:
+                    w4a16.linear_forward_grouped(xs[1536], [q, kk, v], outs=[ys[1536], ys[256], ysb[256]], workspace=ws,
+                                                 stream=stream, pdl=not args.no_pdl)
+                    w4a16.linear_forward(xs[1536], o, out=ys[1536], workspace=ws, stream=stream, pdl=not args.no_pdl)
+                    w4a16.linear_forward_grouped(xs[1536], [gate, up], outs=[ys[8960], ysb[8960]], workspace=ws,
+                                                 stream=stream, pdl=not args.no_pdl)
+                    w4a16.linear_forward(xs[8960], down, out=ys[1536], workspace=ws, stream=stream, pdl=not args.no_pdl)
+            with torch.cuda.stream(stream):
+                grouped_pass()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                grouped_pass()
+            for _ in range(3):
+                g.replay()
+            msg = event_time_ms(torch, g.replay, 10)
+            out["decode_M1_grouped"] = {"ms": msg, "GBs": by / (msg * 1e-3) / 1e9, "frac_hbm": by / (msg * 1e-3) / 1e9 / hbm_peak,
+                                        "peak_kind": f"of {peak_kind}", "how": "CUDA graph of 112 launches: (q,k,v) (o) (gate,up) (down) per layer"}
+            del g
     del layers
     n, k = 28672, 8192
     copies = [make_random_weights_a16(mb, torch, n, k, gen) for _ in range(3)]  # 3 x 176 MB > L2

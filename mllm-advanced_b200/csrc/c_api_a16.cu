@@ -9,6 +9,8 @@ namespace mllmb200 {
 // w4a16.cu
 size_t a16_workspace_bytes(int m, int k, int n);
 cudaError_t launch_w4a16_linear(const void*, int, const void*, void*, void*, int, int, int, int, int, int, cudaStream_t);
+cudaError_t launch_w4a16_linear_grouped(const void*, int, int, int, int, int, const void* const*, void* const*, const int*,
+                                        const int*, void*, int, cudaStream_t);
 cudaError_t launch_w4a16_repack(const void*, int, int, int, int, int, void*, cudaStream_t);
 // c_api.cu
 int record_cuda_failure(cudaError_t e);
@@ -59,6 +61,24 @@ int mllmb200_w4a16_linear_forward_ex(const void* x_dev, int x_dtype, const void*
   if (M > 65535) return MLLMB200_UNSUPPORTED;  // rows of x ride on gridDim.y
   const cudaError_t e =
       launch_w4a16_linear(x_dev, x_dtype, tiled_dev, y_dev, ws_dev, M, K, N, ldx, ldy, kernel, (cudaStream_t)stream);
+  return e == cudaSuccess ? MLLMB200_OK : record_cuda_failure(e);
+}
+
+int mllmb200_w4a16_linear_forward_grouped(const void* x_dev, int x_dtype, int M, int K, int ldx, int count,
+                                          const void* const* tiled_dev, void* const* y_dev, const int* N, const int* ldy,
+                                          void* ws_dev, int flags, void* stream) {
+  if (!x_dev || !tiled_dev || !y_dev || !N || !ldy || !ws_dev || M <= 0 || K <= 0 || ldx < K || count < 1 || count > 4)
+    return MLLMB200_INVALID_ARG;
+  if (x_dtype != MLLMB200_DTYPE_F32 && x_dtype != MLLMB200_DTYPE_F16) return MLLMB200_INVALID_ARG;
+  if ((flags & ~0x100) || ((uintptr_t)ws_dev & 255) || ((uintptr_t)x_dev & (x_dtype == MLLMB200_DTYPE_F16 ? 1 : 3)))
+    return MLLMB200_INVALID_ARG;
+  if (M > 65535) return MLLMB200_UNSUPPORTED;
+  for (int i = 0; i < count; ++i) {
+    if (!tiled_dev[i] || !y_dev[i] || N[i] <= 0 || ldy[i] < N[i]) return MLLMB200_INVALID_ARG;
+    if (((uintptr_t)tiled_dev[i] & 15) || ((uintptr_t)y_dev[i] & 1)) return MLLMB200_INVALID_ARG;
+  }
+  const cudaError_t e = launch_w4a16_linear_grouped(x_dev, x_dtype, M, K, ldx, count, tiled_dev, y_dev, N, ldy, ws_dev,
+                                                    flags, (cudaStream_t)stream);
   return e == cudaSuccess ? MLLMB200_OK : record_cuda_failure(e);
 }
 

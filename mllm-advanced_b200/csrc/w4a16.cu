@@ -288,21 +288,41 @@ __global__ void __launch_bounds__(256) a16_linear_kernel(const uint8_t* __restri
 // itself: lane = k, warp max and sum by shuffles, the eight record words assembled with two OR-shuffles and
 // eight broadcasts.  K is split over the CTAs of a thread-block cluster (gridDim.z = cluster size <= 8); their
 // partial sums meet in the first CTA's pass over distributed shared memory, in rank order (deterministic).
+// Up to four matrices that read the same activations (q/k/v, gate/up) ride in one launch, their panels side
+// by side along gridDim.x.
+constexpr int kA16MaxProblems = 4;
+struct A16Problem {
+  const uint8_t* tiled;
+  __half* y;
+  int n, ldy, panel_begin;
+};
+struct A16Group {
+  A16Problem p[kA16MaxProblems];
+  int count;
+};
+
 template <int MT, typename T>
-__global__ void __launch_bounds__(256) a16_gemv_fused_kernel(const uint8_t* __restrict__ tiled, const T* __restrict__ x,
-                                                             int ldx, int m, int k, int n, int groups_per_slice,
-                                                             __half* __restrict__ y, int ldy) {
+__global__ void __launch_bounds__(256) a16_gemv_fused_kernel(const A16Group grp, const T* __restrict__ x, int ldx, int m,
+                                                             int k, int groups_per_slice) {
   __shared__ float red[8][MT][32];
   __shared__ float sum[MT][32];
   cg::cluster_group cluster = cg::this_cluster();
+  int pi = 0;
+#pragma unroll
+  for (int i = 1; i < kA16MaxProblems; ++i)
+    if (i < grp.count && (int)blockIdx.x >= grp.p[i].panel_begin) pi = i;
+  const uint8_t* __restrict__ tiled = grp.p[pi].tiled;
+  __half* __restrict__ y = grp.p[pi].y;
+  const int n = grp.p[pi].n, ldy = grp.p[pi].ldy;
   const TiledHeaderA16* hdr = reinterpret_cast<const TiledHeaderA16*>(tiled);
-  if (hdr->magic != kTiledMagicA16 || hdr->n != (uint32_t)n || hdr->k != (uint32_t)k) {  // the same for every CTA
+  // the CTAs of a cluster share blockIdx.x, hence the matrix: the early exit is taken by all of them or none
+  if (hdr->magic != kTiledMagicA16 || hdr->n != (uint32_t)n || hdr->k != (uint32_t)k) {
     if (threadIdx.x == 0) atomicOr(&g_device_status, kDevStatusBadHeader);
     return;
   }
   const int nb = (int)hdr->num_groups;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int panel = blockIdx.x;
+  const int panel = (int)blockIdx.x - grp.p[pi].panel_begin;
   const int g_begin = blockIdx.z * groups_per_slice;
   const int g_end = min(nb, g_begin + groups_per_slice);
   const uint8_t* cells = tiled + hdr->cells_off + (size_t)panel * nb * kCellBytesA16;
@@ -439,9 +459,9 @@ static cudaError_t a16_launch_mt(const uint8_t* tiled, const uint8_t* recs, int 
 }
 
 template <int MT, typename T>
-static cudaError_t a16_launch_fused(const uint8_t* tiled, const void* x, int ldx, int m, int k, int n, __half* y, int ldy,
-                                    bool pdl, cudaStream_t st) {
-  const int nb = (int)blob_num_blocks(k), panels = (n + kPanelRows - 1) / kPanelRows;
+static cudaError_t a16_launch_fused(const A16Group& grp, int panels, const void* x, int ldx, int m, int k, bool pdl,
+                                    cudaStream_t st) {
+  const int nb = (int)blob_num_blocks(k);
   int slices = (296 + panels - 1) / panels;  // two CTAs per SM where K allows; a slice keeps >= 8 groups
   slices = max(1, min(min(slices, nb / 8), 8));
   const int gps = (nb + slices - 1) / slices;
@@ -458,7 +478,57 @@ static cudaError_t a16_launch_fused(const uint8_t* tiled, const void* x, int ldx
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 2 : 1;
-  return cudaLaunchKernelEx(&cfg, a16_gemv_fused_kernel<MT, T>, tiled, static_cast<const T*>(x), ldx, m, k, n, gps, y, ldy);
+  return cudaLaunchKernelEx(&cfg, a16_gemv_fused_kernel<MT, T>, grp, static_cast<const T*>(x), ldx, m, k, gps);
+}
+
+// The size rule of the single-launch kernel: small enough that launches, not bytes, set the time; every CTA
+// repeats the quantization, which costs more than a second launch on large matrices (measured: M = 1 wins
+// up to 8192 x 8192 and loses at 28672 x 8192; M = 4 wins at 1536 x 1536 and loses from 1536 x 8960 on).
+static bool a16_fused_ok(int m, long long weights) {
+  return m == 1 ? weights <= (128ll << 20) : (m <= 4 && weights * m <= (16ll << 20));
+}
+
+static cudaError_t a16_dispatch_fused(const A16Group& grp, int panels, const void* x, int x_dtype, int ldx, int m, int k,
+                                      bool pdl, cudaStream_t st) {
+  if (x_dtype == 1) {
+    if (m == 1) return a16_launch_fused<1, __half>(grp, panels, x, ldx, m, k, pdl, st);
+    if (m == 2) return a16_launch_fused<2, __half>(grp, panels, x, ldx, m, k, pdl, st);
+    return a16_launch_fused<4, __half>(grp, panels, x, ldx, m, k, pdl, st);
+  }
+  if (m == 1) return a16_launch_fused<1, float>(grp, panels, x, ldx, m, k, pdl, st);
+  if (m == 2) return a16_launch_fused<2, float>(grp, panels, x, ldx, m, k, pdl, st);
+  return a16_launch_fused<4, float>(grp, panels, x, ldx, m, k, pdl, st);
+}
+
+cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, void* y, void* ws, int m, int k, int n,
+                                int ldx, int ldy, int kernel_and_flags, cudaStream_t st);
+
+// Several matrices on the same activations: one launch of the single-launch kernel when the group as a whole
+// passes its size rule, else one forward per matrix (the workspace is reused: the stream orders them).
+cudaError_t launch_w4a16_linear_grouped(const void* x, int x_dtype, int m, int k, int ldx, int count,
+                                        const void* const* tiled, void* const* y, const int* n, const int* ldy, void* ws,
+                                        int flags, cudaStream_t st) {
+  long long weights = 0;
+  for (int i = 0; i < count; ++i) weights += (long long)n[i] * k;
+  if (count <= kA16MaxProblems && a16_fused_ok(m, weights)) {
+    A16Group grp = {};
+    int panels = 0;
+    for (int i = 0; i < count; ++i) {
+      grp.p[i].tiled = static_cast<const uint8_t*>(tiled[i]);
+      grp.p[i].y = static_cast<__half*>(y[i]);
+      grp.p[i].n = n[i];
+      grp.p[i].ldy = ldy[i];
+      grp.p[i].panel_begin = panels;
+      panels += (n[i] + kPanelRows - 1) / kPanelRows;
+    }
+    grp.count = count;
+    return a16_dispatch_fused(grp, panels, x, x_dtype, ldx, m, k, (flags & 0x100) != 0, st);
+  }
+  for (int i = 0; i < count; ++i) {
+    const cudaError_t e = launch_w4a16_linear(x, x_dtype, tiled[i], y[i], ws, m, k, n[i], ldx, ldy[i], flags & 0x100, st);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, void* y, void* ws, int m, int k, int n,
@@ -467,22 +537,15 @@ cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, v
   const bool pdl = (kernel_and_flags & 0x100) != 0;  // only the single-launch kernel takes part
   const int nb = (int)blob_num_blocks(k);
   uint8_t* recs = static_cast<uint8_t*>(ws);
-  // One launch (quantization inside the kernel, K split over a cluster) while the matrix is small enough that
-  // launches, not bytes, set the time; every CTA repeats the quantization, which costs more than a second
-  // launch on large matrices (measured: M = 1 wins up to 8192 x 8192 and loses at 28672 x 8192; M = 4 wins at
-  // 1536 x 1536 and loses from 1536 x 8960 on).
-  const long long weights = (long long)n * k;
-  if (kernel == 0 && (m == 1 ? weights <= (128ll << 20) : (m <= 4 && weights * m <= (16ll << 20)))) {
-    const uint8_t* t8 = static_cast<const uint8_t*>(tiled);
-    __half* y16 = static_cast<__half*>(y);
-    if (x_dtype == 1) {
-      if (m == 1) return a16_launch_fused<1, __half>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
-      if (m == 2) return a16_launch_fused<2, __half>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
-      return a16_launch_fused<4, __half>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
-    }
-    if (m == 1) return a16_launch_fused<1, float>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
-    if (m == 2) return a16_launch_fused<2, float>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
-    return a16_launch_fused<4, float>(t8, x, ldx, m, k, n, y16, ldy, pdl, st);
+  if (kernel == 0 && a16_fused_ok(m, (long long)n * k)) {  // one launch: quantization inside, K split over a cluster
+    A16Group grp = {};
+    grp.p[0].tiled = static_cast<const uint8_t*>(tiled);
+    grp.p[0].y = static_cast<__half*>(y);
+    grp.p[0].n = n;
+    grp.p[0].ldy = ldy;
+    grp.p[0].panel_begin = 0;
+    grp.count = 1;
+    return a16_dispatch_fused(grp, (n + kPanelRows - 1) / kPanelRows, x, x_dtype, ldx, m, k, pdl, st);
   }
   if (w4a16_tensor_path(m, kernel)) {
     const int nt = w4a16_gemm_tcf16_tile(m, n), m_pad = (m + nt - 1) / nt * nt;

@@ -67,6 +67,7 @@ def lib():
         "mllmb200_w4a16_workspace_size": ([C.c_int, C.c_int, C.c_int, sz_p], C.c_int),
         "mllmb200_w4a16_linear_forward": ([vp, C.c_int, vp, vp, vp] + [C.c_int] * 5 + [vp], C.c_int),
         "mllmb200_w4a16_linear_forward_ex": ([vp, C.c_int, vp, vp, vp] + [C.c_int] * 6 + [vp], C.c_int),
+        "mllmb200_w4a16_linear_forward_grouped": ([vp] + [C.c_int] * 5 + [vp, vp, vp, vp, vp, C.c_int, vp], C.c_int),
     }
     for name, (args, res) in sig.items():
         fn = getattr(L, name)

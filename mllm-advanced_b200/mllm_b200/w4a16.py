@@ -98,3 +98,25 @@ def linear_forward(x, weights, out=None, workspace=None, stream=None, kernel=KER
                                                   _stream_ptr(stream)),
            "w4a16_linear_forward")
     return out
+
+
+def linear_forward_grouped(x, weights_list, outs=None, workspace=None, stream=None, pdl=False):
+    """Several W4A16 linears on the same activations in one call (one launch for M <= 4 on small matrices)."""
+    import torch
+    assert x.is_cuda and x.dtype in (torch.float32, torch.float16) and x.dim() == 2 and x.stride(1) == 1
+    m, k = x.shape
+    cnt = len(weights_list)
+    assert 1 <= cnt <= 4 and all(w.k == k for w in weights_list)
+    if outs is None:
+        outs = [torch.empty((m, w.n), dtype=torch.float16, device=x.device) for w in weights_list]
+    if workspace is None:
+        workspace = torch.empty(max(workspace_size(m, k, w.n) for w in weights_list), dtype=torch.uint8, device=x.device)
+    tiled = (C.c_void_p * cnt)(*[w.tiled.data_ptr() for w in weights_list])
+    ys = (C.c_void_p * cnt)(*[o.data_ptr() for o in outs])
+    ns = (C.c_int * cnt)(*[w.n for w in weights_list])
+    ldy = (C.c_int * cnt)(*[o.stride(0) for o in outs])
+    _check(lib().mllmb200_w4a16_linear_forward_grouped(x.data_ptr(), 1 if x.dtype == torch.float16 else 0, m, k,
+                                                       x.stride(0), cnt, tiled, ys, ns, ldy, workspace.data_ptr(),
+                                                       0x100 if pdl else 0, _stream_ptr(stream)),
+           "w4a16_linear_forward_grouped")
+    return outs

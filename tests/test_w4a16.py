@@ -318,3 +318,29 @@ def test_gpu_chain_with_programmatic_dependent_launch():
     for a, b in zip(outs[False], outs[True]):
         assert np.array_equal(a, b)
     assert np.abs(outs[True][-1].astype(np.float32)).max() > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,ns", [(1, 1536, (1536, 256, 256)), (1, 1536, (8960, 8960)), (3, 100, (33, 5, 64, 40)),
+                                    (4, 1536, (8960, 8960)), (40, 256, (96, 64)), (130, 512, (320, 64))])
+def test_gpu_grouped_calls_match_oracle(m, k, ns):
+    """q/k/v- and gate/up-style groups: one launch at small M, per-matrix forwards otherwise; each output
+    against the oracle, and (same kernels, same order of additions within a matrix's own launch or not) within
+    the bar of the single calls."""
+    import torch
+    from mllm_b200 import w4a16
+    import mllm_b200 as mb
+    o = OracleW4A16()
+    rng = np.random.default_rng(m + k + sum(ns))
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    blobs = [w4a16.quant_prepack(_weights(n, k, 50 + i), (rng.standard_normal(n) * 0.1).astype(np.float32) if i % 2 == 0 else None)
+             for i, n in enumerate(ns)]
+    wts = [w4a16.W4A16Weights.from_blob(b) for b in blobs]
+    outs = w4a16.linear_forward_grouped(torch.from_numpy(x).cuda(), wts, pdl=True)
+    torch.cuda.synchronize()
+    mb.check_device_status()
+    for blob, y in zip(blobs, outs):
+        nib, sc, zr, bias = w4a16.blob_sections(blob)
+        ref = o.linear(x, nib.copy(), sc.copy(), zr.copy(), None if bias is None else bias.copy())
+        diff = np.abs(y.cpu().numpy().astype(np.float32) - ref.astype(np.float32))
+        assert (diff <= _bar(ref, m >= 64)).all(), f"max diff {diff.max()}"
