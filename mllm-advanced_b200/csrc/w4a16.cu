@@ -284,9 +284,9 @@ __global__ void __launch_bounds__(256) a16_linear_kernel(const uint8_t* __restri
 }
 
 // M <= 4: ONE launch per linear.  The per-block activation quantization has no row-wide dependency (unlike the
-// W4A32 path's per-row min/max), so every warp quantizes the 32 activations of the group it is about to use
-// itself: lane = k, warp max and sum by shuffles, the eight record words assembled with two OR-shuffles and
-// eight broadcasts.  K is split over the CTAs of a thread-block cluster (gridDim.z = cluster size <= 8); their
+// W4A32 path's per-row min/max), so every CTA quantizes the activations of its own K slice into shared memory
+// first (a version in which each warp quantized the group it was about to use, with shuffles for the record
+// words, spent ~800 cycles per group in dependent shuffles: 0.70 ms for the grouped 28-layer step).  K is split over the CTAs of a thread-block cluster (gridDim.z = cluster size <= 8); their
 // partial sums meet in the first CTA's pass over distributed shared memory, in rank order (deterministic).
 // Up to four matrices that read the same activations (q/k/v, gate/up) ride in one launch, their panels side
 // by side along gridDim.x.
@@ -306,6 +306,7 @@ __global__ void __launch_bounds__(256) a16_gemv_fused_kernel(const A16Group grp,
                                                              int k, int groups_per_slice) {
   __shared__ float red[8][MT][32];
   __shared__ float sum[MT][32];
+  extern __shared__ uint4 s_rec[];  // [MT][groups_per_slice] records of 3 x 16 bytes
   cg::cluster_group cluster = cg::this_cluster();
   int pi = 0;
 #pragma unroll
@@ -330,56 +331,76 @@ __global__ void __launch_bounds__(256) a16_gemv_fused_kernel(const A16Group grp,
   float acc[MT];
 #pragma unroll
   for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
-  auto load_x = [&](int gg, float (&xv)[MT]) {
-    const int kk = gg * kGroup + lane;
-#pragma unroll
-    for (int i = 0; i < MT; ++i) xv[i] = (i < m && kk < k) ? a16_load<T>(x + (size_t)i * ldx + kk) : 0.0f;
-  };
   int g = g_begin + warp;
   A16Cell cur;
-  float xcur[MT];
   // Under programmatic dependent launch the weights (never written by a kernel) are fetched while the
   // previous kernel of the stream drains; the activations, which it may have produced, only after it is done.
   pdl_launch_dependents();
   if (g < g_end) cur = a16_load_cell(cells + (size_t)g * kCellBytesA16, lane);
   pdl_wait_prior();
-  if (g < g_end) load_x(g, xcur);
-  for (; g < g_end; g += 8) {
-    A16Cell nxt = cur;
-    float xnxt[MT];
+
+  // Phase 1: the CTA quantizes the activations of its K slice once, into 48-byte records in shared memory
+  // (8 lanes per group, 4 consecutive k per lane - the arithmetic of a16_act_quant_kernel).
+  const int gcount = g_end - g_begin;
+  for (int base = 0; base < gcount; base += 32) {  // uniform trip count: whole warps take part in the shuffles
+    const int gi = base + warp * 4 + (lane >> 3), j = lane & 7;
+    const int kk0 = (g_begin + gi) * kGroup + j * 4;
+    float vv[MT][4];  // all rows' loads are issued before the first dependent shuffle
 #pragma unroll
-    for (int i = 0; i < MT; ++i) xnxt[i] = xcur[i];
-    if (g + 8 < g_end) {
-      nxt = a16_load_cell(cells + (size_t)(g + 8) * kCellBytesA16, lane);
-      load_x(g + 8, xnxt);
-    }
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        vv[i][t] = (gi < gcount && i < m && kk0 + t < k) ? a16_load<T>(x + (size_t)i * ldx + kk0 + t) : 0.0f;
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
-      float amax = fabsf(xcur[i]);
+      float v[4], amax = 0.0f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      for (int t = 0; t < 4; ++t) {
+        v[t] = vv[i][t];
+        amax = fmaxf(amax, fabsf(v[t]));
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       const float scale = __fdiv_rn(amax, 127.0f);
       const float recip = scale != 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
-      const int q = (int)fminf(fmaxf(roundf(__fmul_rn(xcur[i], recip)), -127.0f), 127.0f);
-      int asum = q;
+      int q[4], asum = 0;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) asum += __shfl_xor_sync(0xffffffffu, asum, o);
-      // word c (even k) / word 4 + c (odd k) of the record: byte j = k 8c + 2j (+ 1); lane = k
-      uint32_t v = (uint32_t)(q & 0xff) << (8 * ((lane & 7) >> 1));
-      v |= __shfl_xor_sync(0xffffffffu, v, 2);
-      v |= __shfl_xor_sync(0xffffffffu, v, 4);
-      uint4 r0, r1;
-      r0.x = __shfl_sync(0xffffffffu, v, 0), r0.y = __shfl_sync(0xffffffffu, v, 8);
-      r0.z = __shfl_sync(0xffffffffu, v, 16), r0.w = __shfl_sync(0xffffffffu, v, 24);
-      r1.x = __shfl_sync(0xffffffffu, v, 1), r1.y = __shfl_sync(0xffffffffu, v, 9);
-      r1.z = __shfl_sync(0xffffffffu, v, 17), r1.w = __shfl_sync(0xffffffffu, v, 25);
+      for (int t = 0; t < 4; ++t) {
+        q[t] = (int)fminf(fmaxf(roundf(__fmul_rn(v[t], recip)), -127.0f), 127.0f);
+        asum += q[t];
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) asum += __shfl_xor_sync(0xffffffffu, asum, o);
+      const uint32_t ev = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[2] & 0xff) << 8);
+      const uint32_t od = (uint32_t)(q[1] & 0xff) | ((uint32_t)(q[3] & 0xff) << 8);
+      const uint32_t ev_p = __shfl_xor_sync(0xffffffffu, ev, 1), od_p = __shfl_xor_sync(0xffffffffu, od, 1);
+      if (gi < gcount) {
+        uint32_t* rec = reinterpret_cast<uint32_t*>(s_rec + ((size_t)i * groups_per_slice + gi) * 3);
+        if ((j & 1) == 0) rec[j >> 1] = ev | (ev_p << 16);
+        else rec[4 + (j >> 1)] = od_p | (od << 16);
+        if (j == 0) {
+          rec[8] = (uint32_t)asum;
+          rec[9] = __float_as_uint(scale);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // Phase 2: lane = output row, the warps take the slice's groups in turn; records come back as broadcasts.
+  for (; g < g_end; g += 8) {
+    A16Cell nxt = cur;
+    if (g + 8 < g_end) nxt = a16_load_cell(cells + (size_t)(g + 8) * kCellBytesA16, lane);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const uint4* rec = s_rec + ((size_t)i * groups_per_slice + (g - g_begin)) * 3;
+      const uint4 r0 = rec[0], r1 = rec[1], r2 = rec[2];
+      const int asum = (int)r2.x;
       const int dot = a16_dot(cur.nw, r0, r1) - 8 * asum;
       const float t = fmaf(cur.s, (float)dot, cur.z * (float)asum);
-      acc[i] = fmaf(scale, t, acc[i]);
+      acc[i] = fmaf(__uint_as_float(r2.y), t, acc[i]);
     }
     cur = nxt;
-#pragma unroll
-    for (int i = 0; i < MT; ++i) xcur[i] = xnxt[i];
   }
 #pragma unroll
   for (int i = 0; i < MT; ++i) red[warp][i][lane] = acc[i];
@@ -469,6 +490,16 @@ static cudaError_t a16_launch_fused(const A16Group& grp, int panels, const void*
   cfg.gridDim = dim3((unsigned)panels, 1, (unsigned)slices);
   cfg.blockDim = dim3(256, 1, 1);
   cfg.stream = st;
+  const size_t rec_bytes = (size_t)MT * gps * kActRecordBytesA16;
+  if (rec_bytes > 160 * 1024) return cudaErrorInvalidConfiguration;  // not reachable under the size rule of this kernel
+  static size_t configured = 48 * 1024 - sizeof(float) * (8 * MT * 32 + MT * 32);
+  if (rec_bytes > configured) {
+    const cudaError_t e = cudaFuncSetAttribute(a16_gemv_fused_kernel<MT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)(160 * 1024));
+    if (e != cudaSuccess) return e;
+    configured = 160 * 1024;
+  }
+  cfg.dynamicSmemBytes = rec_bytes;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
@@ -481,11 +512,13 @@ static cudaError_t a16_launch_fused(const A16Group& grp, int panels, const void*
   return cudaLaunchKernelEx(&cfg, a16_gemv_fused_kernel<MT, T>, grp, static_cast<const T*>(x), ldx, m, k, gps);
 }
 
-// The size rule of the single-launch kernel: small enough that launches, not bytes, set the time; every CTA
-// repeats the quantization, which costs more than a second launch on large matrices (measured: M = 1 wins
-// up to 8192 x 8192 and loses at 28672 x 8192; M = 4 wins at 1536 x 1536 and loses from 1536 x 8960 on).
+// The size rule of the single-launch kernel: small enough that launches, not bytes, set the time.  Every CTA
+// repeats the quantization of its K slice for all M rows, which costs more than a second launch on large
+// matrices and at M > 1 (measured per linear, fused vs records + dp4a: M = 1 wins from 1536 x 256 (3.7 vs 5.4 us)
+// to 8192 x 8192 (17.6 vs 24.5) and ties at 28672 x 8192; M = 4 wins only at 1536 x 256 (5.0 vs 5.6) and loses at
+// 1536 x 1536 (9.7 vs 6.2)).
 static bool a16_fused_ok(int m, long long weights) {
-  return m == 1 ? weights <= (128ll << 20) : (m <= 4 && weights * m <= (16ll << 20));
+  return m == 1 ? weights <= (128ll << 20) : (m <= 4 && weights * m <= (2ll << 20));
 }
 
 static cudaError_t a16_dispatch_fused(const A16Group& grp, int panels, const void* x, int x_dtype, int ldx, int m, int k,
