@@ -225,8 +225,8 @@ MLLMB200_API int mllmb200_w4a16_repack_device(const void* blob_dev, int N, int K
 MLLMB200_API int mllmb200_w4a16_workspace_size(int M, int K, int N, size_t* bytes);
 MLLMB200_API int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, const void* tiled_dev, void* y_dev,
                                                void* ws_dev, int M, int K, int N, int ldx, int ldy, void* stream);
-/* Same with the kernel family forced: 0 auto (the dp4a kernel below M = 64, the tensor-core kernel from there
- * on), 2 dp4a kernel (exact int32 block sums, fp32 combination as written above), 4 tcgen05 fp16 kernel (M >= 64):
+/* Same with the kernel family forced: 0 auto (the tensor-core kernel for M >= 128, and for M >= 32 when
+ * N >= 8192; else the dp4a kernel), 2 dp4a kernel (exact int32 block sums, fp32 combination as written above), 4 tcgen05 fp16 kernel (M >= 8):
  * weight operand fp16(((u-8)*s + z) * 2^E) and activation operand fp16(a_q * a_s), one rounding each, fp32
  * accumulation over all of K in tensor memory - it differs from the formula above by those roundings
  * (about 3e-4 of the row's rms, the size of the fp16 output's own rounding).

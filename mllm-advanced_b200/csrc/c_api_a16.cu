@@ -51,7 +51,7 @@ int mllmb200_w4a16_linear_forward_ex(const void* x_dev, int x_dtype, const void*
                                      int M, int K, int N, int ldx, int ldy, int kernel, void* stream) {
   const int family = kernel & 0xff;
   if ((kernel & ~0x1ff) || (family != 0 && family != 2 && family != 4)) return MLLMB200_INVALID_ARG;
-  if (family == 4 && M < 64) return MLLMB200_UNSUPPORTED;
+  if (family == 4 && M < 8) return MLLMB200_UNSUPPORTED;
   if (!x_dev || !tiled_dev || !y_dev || !ws_dev || M <= 0 || K <= 0 || N <= 0 || ldx < K || ldy < N)
     return MLLMB200_INVALID_ARG;
   if (x_dtype != MLLMB200_DTYPE_F32 && x_dtype != MLLMB200_DTYPE_F16) return MLLMB200_INVALID_ARG;

@@ -455,8 +455,14 @@ int a16_slices(int m, int k, int n) {
 int w4a16_gemm_tcf16_tile(int m, int n);
 cudaError_t launch_w4a16_gemm_tcf16(const uint8_t*, const void*, void*, int, int, int, int, cudaStream_t);
 
-// The tensor-core path (fp16 operands, one rounding each) from M = 64 on; below it the exact-integer dp4a kernel.
-bool w4a16_tensor_path(int m, int kernel) { return (kernel == 4 || kernel == 0) && m >= 64; }
+// The tensor-core path (fp16 operands, one rounding each) for large M; otherwise the exact-integer dp4a kernel.
+// Measured (us per linear, dp4a vs tensor-core path incl. its quantization): 1536 -> 8960: M = 32 18 / 19, M = 48
+// 24 / 20; 8192 -> 28672: M = 16 120 / 136, M = 24 212 / 137; 8960 -> 1536 (12 weight tiles): M = 63 40 / 76;
+// 1536 -> 1536: M = 63 10.5 / 18.  With few weight tiles the tensor-core kernel needs several row tiles to pay.
+bool w4a16_tensor_path(int m, int n, int kernel) {
+  if (kernel == 4) return m >= 8;
+  return kernel == 0 && (m >= 128 || (m >= 32 && n >= 8192));
+}
 
 size_t a16_workspace_bytes(int m, int k, int n) {
   const size_t rec = align_up((size_t)m * blob_num_blocks(k) * kActRecordBytesA16, 256);
@@ -464,7 +470,7 @@ size_t a16_workspace_bytes(int m, int k, int n) {
   const size_t n_pad = (size_t)((n + kPanelRows - 1) / kPanelRows) * kPanelRows;
   const size_t simt = rec + (s > 1 ? align_up((size_t)s * m * n_pad * 4, 256) : 0);
   // operand blocks of the tensor-core path: 64 bytes per row and K-group, rows padded to its widest tile
-  const size_t blk = m >= 64 ? align_up((size_t)((m + 255) / 256 * 256) * blob_num_blocks(k) * 64, 256) : 0;
+  const size_t blk = m >= 8 ? align_up((size_t)((m + 255) / 256 * 256) * blob_num_blocks(k) * 64, 256) : 0;
   return simt > blk ? simt : blk;
 }
 
@@ -580,7 +586,7 @@ cudaError_t launch_w4a16_linear(const void* x, int x_dtype, const void* tiled, v
     grp.count = 1;
     return a16_dispatch_fused(grp, (n + kPanelRows - 1) / kPanelRows, x, x_dtype, ldx, m, k, pdl, st);
   }
-  if (w4a16_tensor_path(m, kernel)) {
+  if (w4a16_tensor_path(m, n, kernel)) {
     const int nt = w4a16_gemm_tcf16_tile(m, n), m_pad = (m + nt - 1) / nt * nt;
     if (x_dtype == 1)
       a16_act_quant_blocks_f16_kernel<__half><<<m_pad, 256, 0, st>>>(static_cast<const __half*>(x), m, k, ldx, nb, m_pad / 8, recs);

@@ -83,7 +83,7 @@ KERNEL_AUTO, KERNEL_DP4A, KERNEL_TC_F16 = 0, 2, 4
 
 def linear_forward(x, weights, out=None, workspace=None, stream=None, kernel=KERNEL_AUTO, pdl=False):
     """fp16 y = W4A16 linear of x (torch float32 or float16 [M,K] on the GPU, last dim contiguous).
-    kernel: KERNEL_AUTO (dp4a below M = 64, tensor cores from there on), KERNEL_DP4A, KERNEL_TC_F16 (M >= 64)."""
+    kernel: KERNEL_AUTO (tensor cores for M >= 128, or M >= 32 with N >= 8192; else dp4a), KERNEL_DP4A, KERNEL_TC_F16 (M >= 8)."""
     import torch
     assert x.is_cuda and x.dtype in (torch.float32, torch.float16) and x.dim() == 2 and x.stride(1) == 1
     m, k = x.shape
