@@ -239,8 +239,9 @@ MLLMB200_API int mllmb200_w4a16_linear_forward_ex(const void* x_dev, int x_dtype
                                                   void* stream);
 /* Several W4A16 linears that read the SAME activations (q/k/v, gate/up of a decoder layer,
  * mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:47-54,106-112) in one call: count in [1,4], all with the same K.
- * For M <= 4 on small matrices this is ONE kernel launch (their row panels side by side in the grid); otherwise one
- * forward per matrix.  ws_dev must hold the largest workspace_size(M, K, N[i]).  flags: 0 or 0x100 (programmatic
+ * For M <= 4 on small matrices this is ONE kernel launch (their row panels side by side in the grid); where the
+ * tensor-core kernel applies (M >= 128, or M >= 32 with sum(N) >= 8192) one quantization and ONE launch; otherwise
+ * one forward per matrix.  ws_dev must hold the largest workspace_size(M, K, N[i]).  flags: 0 or 0x100 (programmatic
  * dependent launch, as above). */
 MLLMB200_API int mllmb200_w4a16_linear_forward_grouped(const void* x_dev, int x_dtype, int M, int K, int ldx, int count,
                                                        const void* const* tiled_dev, void* const* y_dev, const int* N,

@@ -417,34 +417,45 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
   }
 }
 
-// W4A16: 128-row tiles; the activation blocks must be padded to a multiple of w4a16_gemm_tcf16_tile(m, n) rows.
-int w4a16_gemm_tcf16_tile(int m, int n) {
-  const long long t128 = (n + 127) / 128;
+// W4A16: 128-row tiles; the activation blocks must be padded to a multiple of w4a16_gemm_tcf16_tile_grouped(...)
+// rows.  Up to four matrices that share x ride in one launch (their weight tiles side by side in the grid).
+int w4a16_gemm_tcf16_tile_grouped(int m, int count, const int* n) {
+  long long t128 = 0;
+  for (int i = 0; i < count; ++i) t128 += (n[i] + 127) / 128;
   return (m >= 256 && t128 * ((m + 255) / 256) >= 100) ? 256 : (m >= 128 ? 128 : 64);
 }
-cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, void* y_f16, int m, int k, int n, int ldy,
-                                    cudaStream_t stream) {
-  const int nt = w4a16_gemm_tcf16_tile(m, n);
+int w4a16_gemm_tcf16_tile(int m, int n) { return w4a16_gemm_tcf16_tile_grouped(m, 1, &n); }
+cudaError_t launch_w4a16_gemm_tcf16_grouped(const uint8_t* a_blocks, int m, int k, int count, const void* const* tiled,
+                                            void* const* y_f16, const int* n, const int* ldy, cudaStream_t stream) {
+  if (count < 1 || count > kTfMaxProblems) return cudaErrorInvalidValue;
+  const int nt = w4a16_gemm_tcf16_tile_grouped(m, count, n);
   TfParams prm = {};
   prm.a_blocks = a_blocks;
   prm.a_hdr = nullptr;
   prm.m = m, prm.k = k;
   prm.num_groups = (k + kGroup - 1) / kGroup;
   prm.m8_pad = (m + nt - 1) / nt * nt / 8;
-  prm.num_problems = 1;
-  prm.prob[0].tiled = static_cast<const uint8_t*>(tiled);
-  prm.prob[0].y = y_f16;
-  prm.prob[0].n = n;
-  prm.prob[0].ldy = ldy;
-  prm.prob[0].num_panels = (n + kPanelRows - 1) / kPanelRows;
-  prm.prob[0].tile_begin = 0;
-  prm.prob[0].bias_off = make_tiled_header_a16(n, k, 0).bias_off;
-  const int tiles = (n + 127) / 128;
+  prm.num_problems = count;
+  int tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    prm.prob[i].tiled = static_cast<const uint8_t*>(tiled[i]);
+    prm.prob[i].y = y_f16[i];
+    prm.prob[i].n = n[i];
+    prm.prob[i].ldy = ldy[i];
+    prm.prob[i].num_panels = (n[i] + kPanelRows - 1) / kPanelRows;
+    prm.prob[i].tile_begin = tiles;
+    prm.prob[i].bias_off = make_tiled_header_a16(n[i], k, 0).bias_off;
+    tiles += (n[i] + 127) / 128;
+  }
   switch (nt) {
     case 256: return launch_tf_t<256, 128, true>(prm, tiles, stream);
     case 128: return launch_tf_t<128, 128, true>(prm, tiles, stream);
     default: return launch_tf_t<64, 128, true>(prm, tiles, stream);
   }
+}
+cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, void* y_f16, int m, int k, int n, int ldy,
+                                    cudaStream_t stream) {
+  return launch_w4a16_gemm_tcf16_grouped(a_blocks, m, k, 1, &tiled, &y_f16, &n, &ldy, stream);
 }
 
 cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,

@@ -453,6 +453,9 @@ int a16_slices(int m, int k, int n) {
 
 // gemm_tcf16.cu
 int w4a16_gemm_tcf16_tile(int m, int n);
+int w4a16_gemm_tcf16_tile_grouped(int m, int count, const int* n);
+cudaError_t launch_w4a16_gemm_tcf16_grouped(const uint8_t*, int, int, int, const void* const*, void* const*, const int*,
+                                            const int*, cudaStream_t);
 cudaError_t launch_w4a16_gemm_tcf16(const uint8_t*, const void*, void*, int, int, int, int, cudaStream_t);
 
 // The tensor-core path (fp16 operands, one rounding each) for large M; otherwise the exact-integer dp4a kernel.
@@ -562,6 +565,21 @@ cudaError_t launch_w4a16_linear_grouped(const void* x, int x_dtype, int m, int k
     }
     grp.count = count;
     return a16_dispatch_fused(grp, panels, x, x_dtype, ldx, m, k, (flags & 0x100) != 0, st);
+  }
+  long long n_sum = 0;
+  for (int i = 0; i < count; ++i) n_sum += n[i];
+  if (count <= 4 && w4a16_tensor_path(m, (int)(n_sum > 0x7fffffff ? 0x7fffffff : n_sum), 0)) {
+    // one quantization into operand blocks and ONE tensor-core launch for the whole group
+    const int nb = (int)blob_num_blocks(k);
+    const int nt = w4a16_gemm_tcf16_tile_grouped(m, count, n), m_pad = (m + nt - 1) / nt * nt;
+    uint8_t* blocks = static_cast<uint8_t*>(ws);
+    if (x_dtype == 1)
+      a16_act_quant_blocks_f16_kernel<__half><<<m_pad, 256, 0, st>>>(static_cast<const __half*>(x), m, k, ldx, nb, m_pad / 8, blocks);
+    else
+      a16_act_quant_blocks_f16_kernel<float><<<m_pad, 256, 0, st>>>(static_cast<const float*>(x), m, k, ldx, nb, m_pad / 8, blocks);
+    const cudaError_t qe = cudaGetLastError();
+    if (qe != cudaSuccess) return qe;
+    return launch_w4a16_gemm_tcf16_grouped(blocks, m, k, count, tiled, y, n, ldy, st);
   }
   for (int i = 0; i < count; ++i) {
     const cudaError_t e = launch_w4a16_linear(x, x_dtype, tiled[i], y[i], ws, m, k, n[i], ldx, ldy[i], flags & 0x100, st);

@@ -327,7 +327,8 @@ def test_gpu_chain_with_programmatic_dependent_launch():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("m,k,ns", [(1, 1536, (1536, 256, 256)), (1, 1536, (8960, 8960)), (3, 100, (33, 5, 64, 40)),
-                                    (4, 1536, (8960, 8960)), (40, 256, (96, 64)), (130, 512, (320, 64))])
+                                    (4, 1536, (8960, 8960)), (40, 256, (96, 64)), (130, 512, (320, 64)),
+                                    (40, 256, (4200, 4100)), (512, 1536, (1536, 256, 256))])
 def test_gpu_grouped_calls_match_oracle(m, k, ns):
     """q/k/v- and gate/up-style groups: one launch at small M, per-matrix forwards otherwise; each output
     against the oracle, and (same kernels, same order of additions within a matrix's own launch or not) within
@@ -348,4 +349,4 @@ def test_gpu_grouped_calls_match_oracle(m, k, ns):
         nib, sc, zr, bias = w4a16.blob_sections(blob)
         ref = o.linear(x, nib.copy(), sc.copy(), zr.copy(), None if bias is None else bias.copy())
         diff = np.abs(y.cpu().numpy().astype(np.float32) - ref.astype(np.float32))
-        assert (diff <= _bar(ref, _auto_is_tensor(m, ref.shape[1]))).all(), f"max diff {diff.max()}"
+        assert (diff <= _bar(ref, _auto_is_tensor(m, sum(ns)))).all(), f"max diff {diff.max()}"   # the group decides as a whole
