@@ -996,10 +996,18 @@ def main():
     ap.add_argument("--prefill-f16", action="store_true", help="with --prefill-only: use the fp16 tensor-core path (kernel 4)")
     ap.add_argument("--fast-prefill", action="store_true", help="time the prefill linears on 2 layers instead of 28")
     args = ap.parse_args()
+    # Libraries write to file descriptor 1 behind Python's back (NCCL prints its version banner there when a
+    # communicator is created); stdout must carry the result lines only, so everything that is not printed
+    # through `print` in this file goes to stderr.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(result_fd, "w", buffering=1)
     if args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
+    sys.stdout.flush()
 
 
 if __name__ == "__main__":
