@@ -350,3 +350,49 @@ def test_gpu_grouped_calls_match_oracle(m, k, ns):
         ref = o.linear(x, nib.copy(), sc.copy(), zr.copy(), None if bias is None else bias.copy())
         diff = np.abs(y.cpu().numpy().astype(np.float32) - ref.astype(np.float32))
         assert (diff <= _bar(ref, _auto_is_tensor(m, sum(ns)))).all(), f"max diff {diff.max()}"   # the group decides as a whole
+
+
+@pytest.mark.gpu
+def test_gpu_full_size_matrix():
+    """BASELINE config 4's matrix (28672 x 8192): M = 2 against the oracle (records + dp4a path: the matrix is past
+    the single-launch kernel's size rule), and at M = 2048 the tensor-core kernel against the dp4a kernel on the
+    same inputs (the oracle would need minutes there); 8 row shards reproduce the whole within the same bar."""
+    import torch
+    from mllm_b200 import w4a16
+    import mllm_b200 as mb
+    o = OracleW4A16()
+    n, k = 28672, 8192
+    rng = np.random.default_rng(77)
+    w = (rng.standard_normal((n, k), dtype=np.float32) * 0.02)
+    blob = w4a16.quant_prepack(w)
+    del w
+    nib, sc, zr, _ = w4a16.blob_sections(blob)
+    wts = w4a16.W4A16Weights.from_blob(blob)
+    x2 = rng.standard_normal((2, k)).astype(np.float16)
+    ref = o.linear(x2, nib.copy(), sc.copy(), zr.copy())
+    y2 = w4a16.linear_forward(torch.from_numpy(x2).cuda(), wts)
+    torch.cuda.synchronize()
+    mb.check_device_status()
+    diff = np.abs(y2.cpu().numpy().astype(np.float32) - ref.astype(np.float32))
+    assert (diff <= _bar(ref)).all(), f"max diff {diff.max()}"
+    # shards
+    per = n // 8
+    parts = [w4a16.linear_forward(torch.from_numpy(x2).cuda(),
+                                  w4a16.W4A16Weights.from_blob(blob, row_begin=r * per, row_count=per)) for r in range(8)]
+    # a shard has 112 row panels and splits K over three slices where the whole matrix (896 panels) uses one:
+    # the fp32 additions are ordered differently, so the shards match within the dp4a bar, not bit for bit
+    got = torch.cat(parts, dim=1).cpu().numpy()
+    diff = np.abs(got.astype(np.float32) - ref.astype(np.float32))
+    assert (diff <= _bar(ref)).all(), f"shards: max diff {diff.max()}"
+    assert (got == y2.cpu().numpy()).mean() > 0.99
+    # tensor-core kernel vs the exact dp4a kernel at the bench's M
+    xm = torch.from_numpy(rng.standard_normal((2048, k)).astype(np.float16)).cuda()
+    y_tc = w4a16.linear_forward(xm, wts)                       # auto: tensor cores
+    y_dp = w4a16.linear_forward(xm, wts, kernel=w4a16.KERNEL_DP4A)
+    torch.cuda.synchronize()
+    mb.check_device_status()
+    a, b = y_tc.float(), y_dp.float()
+    rms = b.pow(2).mean(dim=1, keepdim=True).sqrt()
+    ulp = torch.from_numpy(np.spacing(np.abs(y_dp.cpu().numpy())).astype(np.float32)).cuda()
+    assert bool(((a - b).abs() <= 2 * ulp + 4e-3 * rms).all())
+    assert float((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()) < 8e-4
