@@ -14,7 +14,9 @@ device time (CUDA events on the launching stream, max over ranks).
 
 Extra objects in the JSON line: `roofline` (GEMV kernel vs the measured HBM copy bandwidth),
 `prefill` (the same seven linears at M=512, TFLOP/s), `e2e` (host buffers in, host buffers out),
-`cpu_baseline` (the reference's X86 int4 kernels on the host cores), `per_shape`, `clocks`.
+`cpu_baseline` (the reference's X86 int4 kernels on the host cores), `per_shape`, `clocks`, and on one GPU
+`config4` (the 28672 x 8192 matrix: GEMV at M=1, GEMM at M=2048), `w4a16` (the W4A16 sibling path on the same
+shapes) and `decoder` (512-token prefill + 128 greedy steps of the whole model).
 
 With N > 1 ranks (torchrun) every rank serves its own token (independent replicas, weak scaling,
 no collective on the data path), and rank 0 adds a `tp` object: the column-sharded large linear of
