@@ -230,6 +230,8 @@ MLLMB200_API int mllmb200_w4a16_linear_forward(const void* x_dev, int x_dtype, c
  * weight operand fp16(((u-8)*s + z) * 2^E) and activation operand fp16(a_q * a_s), one rounding each, fp32
  * accumulation over all of K in tensor memory - it differs from the formula above by those roundings
  * (about 3e-4 of the row's rms, the size of the fp16 output's own rounding).
+ * Its activation operand is fp16: fp32 activations beyond the fp16 range (|x| > 65504) overflow there - force
+ * kernel 2 for such inputs (fp16 activations cannot exceed it).
  * OR 0x100 into `kernel` to launch the single-launch kernel (M <= 4) with programmatic dependent launch: it
  * then fetches its first weights while the previous kernel of the stream drains, and reads x only after
  * that kernel has completed.  Use it only when x and y are not written by anything else on the stream that
