@@ -2,15 +2,21 @@
 """Benchmark of the W4A32 quantized-linear path on B200.
 
 Headline workload ("qwen2-1.5b-decode-linears"): one decode token's worth of quantized linears of
-the Qwen2-1.5B architecture - 28 decoder layers x the seven linears q,k,v,o,gate,up,down at M=1 -
-every layer with its own weights (737 MB of int4+scales per step, larger than the 126 MB L2, so
-no flush is needed between steps).  A step is one pass over those 196 linears, launched through the
-C ABI and replayed as a CUDA graph.  By default linears that read the same activations share a call
-(mllmb200_w4a32_linear_forward_grouped: q/k/v and gate/up, 4 calls per layer); `--per-op` issues one
-mllmb200_w4a32_linear_forward per linear instead (7 per layer), and the other structure is reported
-beside the headline.  The metric is algorithmic HBM bytes per second: nibbles + scales + bias +
-fp32 x + fp32 y of every linear, divided by the
-device time (CUDA events on the launching stream, max over ranks).
+the Qwen2-1.5B architecture - 28 decoder layers x the seven linears q,k,v,o,gate,up,down at M=1
+(BASELINE config 1 at decode, once per layer) - every layer with its own weights (737 MB of
+int4+scales per step, larger than the 126 MB L2, so no flush is needed between steps) and every
+linear with its own input and output buffer.  A step is one pass over those 196 linears through the
+C ABI, replayed as a CUDA graph.  Three call structures are measured in every run:
+  layer   (default headline) one mllmb200_w4a32_linear_forward_multi call per layer: the seven
+          independent linears of config 1 in ONE launch (28 launches per step);
+  grouped the calls a decoder makes: (q,k,v) (o) (gate,up) (down), linears that share their
+          activations sharing a call (mllmb200_w4a32_linear_forward_grouped; 112 launches per step);
+  per-op  one mllmb200_w4a32_linear_forward per linear, as the reference's engine dispatches ops
+          (196 launches per step).
+`--calls grouped|per-op` makes one of the others the headline; all three are always reported
+(`call_structures`).  The metric is algorithmic HBM bytes per second: nibbles + scales + bias +
+fp32 x + fp32 y of every linear, divided by the device time (CUDA events on the launching stream,
+median over at least 5 timed regions of --steps steps each, max over ranks).
 
 Extra objects in the JSON line: `roofline` (GEMV kernel vs the measured HBM copy bandwidth),
 `prefill` (the same seven linears at M=512, TFLOP/s), `e2e` (host buffers in, host buffers out),
@@ -43,13 +49,20 @@ LAYERS = 28
 LINEARS = [("q", 1536, 1536, True), ("k", 1536, 256, True), ("v", 1536, 256, True), ("o", 1536, 1536, False),
            ("gate", 1536, 8960, False), ("up", 1536, 8960, False), ("down", 8960, 1536, False)]
 PREFILL_M = 512
-NCU_GEMV_DRAM_BYTES_PER_LAYER = 26.61e6
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
 
 def algorithmic_bytes(m, k, n, has_bias):
     return n * k // 2 + n * (k // 32) * 2 + m * k * 4 + m * n * 4 + (n * 4 if has_bias else 0)
+
+
+def workload_config():
+    """The `config` object both arms print: it names the workload, nothing arm-specific."""
+    step_bytes = LAYERS * sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
+    return {"workload": "qwen2-1.5b-decode-linears", "layers": LAYERS, "linears_per_layer": len(LINEARS), "M": 1,
+            "weight_bytes_per_step": LAYERS * 26320896, "algorithmic_bytes_per_step": step_bytes,
+            "l2": "737 MB of weights per step > 126 MB L2: no flush between steps"}
 
 
 def measured_peaks():
@@ -146,7 +159,7 @@ def load_x86_ref():
     return None, None
 
 
-def time_reference_cpu(budget_s=12.0, steps=None, warmup=1):
+def time_reference_cpu(budget_s=12.0, steps=None, warmup=1, max_threads=None):
     """One decoder layer's seven linears at M=1 on the reference's X86 int4 kernels (Q4_K x Q8_K -
     a different int4 format from the Arm W4A32 path, same 0.5625 bytes per weight), all host threads.
     Returns (GB/s over the algorithmic W4A32 bytes of those linears, info dict)."""
@@ -155,6 +168,8 @@ def time_reference_cpu(budget_s=12.0, steps=None, warmup=1):
         return None, {"why": "oracle/_ref/libx86q4k_ref_*.so not built"}
     rng = np.random.default_rng(0)
     threads = L.x86ref_max_threads()
+    if max_threads:
+        threads = min(threads, max_threads)
     variant = 1 if L.x86ref_has_avx512() else 0
     mats = []
     for name, k, n, hb in LINEARS:
@@ -232,8 +247,8 @@ def run_reference(args):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32 -> f32",
             "data": "synthetic",
-            "config": {"workload": "qwen2-1.5b-decode-linears", "layers": LAYERS, "M": 1,
-                       "note": "each step of this arm is a bounded sample: one layer's 7 linears; ms_per_step scales it to 28 layers"},
+            "config": workload_config(),
+            "run": {"note": "each step of this arm is a bounded sample: one layer's 7 linears; ms_per_step scales it to 28 layers"},
             "cpu_baseline": {"value": val, "unit": "GB/s", "cores": info["cores"], "kind": "reference",
                              "sample": info["sample"], "variant": info["variant"]},
             "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -318,40 +333,58 @@ def run_gpu(args):
     if args.decoder_only:
         print(json.dumps({"decoder": run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind)}), flush=True)
         return
-    xs = {k: torch.randn((1, k), device="cuda", generator=gen) for k in (1536, 8960)}
-    ys = {n: torch.empty((1, n), device="cuda") for n in (1536, 256, 8960)}
+    # every linear of a layer has its own activations and output (BASELINE config 1); they are slices of one
+    # buffer each so that the end-to-end leg can move a layer's inputs and outputs with one copy per direction
+    x_all = torch.randn((sum(k for _, k, _, _ in LINEARS),), device="cuda", generator=gen)
+    y_all = torch.empty((sum(n for _, _, n, _ in LINEARS),), device="cuda")
+    xs7, ys7, xo, yo = [], [], 0, 0
+    for _, k, n, _ in LINEARS:
+        xs7.append(x_all[xo:xo + k].view(1, k))
+        ys7.append(y_all[yo:yo + n].view(1, n))
+        xo, yo = xo + k, yo + n
+    xs = {1536: xs7[0], 8960: xs7[6]}
+    ys = {1536: ys7[0], 256: ys7[1], 8960: ys7[4]}
     stream = torch.cuda.Stream()
     pdl = not args.no_pdl
     ws = torch.empty(mb.workspace_size(PREFILL_M, 8960), dtype=torch.uint8, device="cuda")
 
-    ys256b, ys8960b = torch.empty((1, 256), device="cuda"), torch.empty((1, 8960), device="cuda")
-
-    def per_op_pass():  # one C-ABI call per linear: 7 per layer
+    def layer_pass():  # one call per layer: the seven independent linears in one launch
         for lw in layers:
-            for w in lw:
-                mb.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream, pdl=pdl)
+            mb.linear_forward_multi(xs7, lw, outs=ys7, stream=stream, pdl=pdl)
 
     def grouped_pass():  # linears that read the same activations share a call: (q,k,v) (o) (gate,up) (down)
         for lw in layers:
-            mb.linear_forward_grouped(xs[1536], lw[0:3], outs=[ys[1536], ys[256], ys256b], workspace=ws, stream=stream, pdl=pdl)
-            mb.linear_forward(xs[1536], lw[3], out=ys[1536], workspace=ws, stream=stream, pdl=pdl)
-            mb.linear_forward_grouped(xs[1536], lw[4:6], outs=[ys[8960], ys8960b], workspace=ws, stream=stream, pdl=pdl)
-            mb.linear_forward(xs[8960], lw[6], out=ys[1536], workspace=ws, stream=stream, pdl=pdl)
+            mb.linear_forward_grouped(xs7[0], lw[0:3], outs=ys7[0:3], workspace=ws, stream=stream, pdl=pdl)
+            mb.linear_forward(xs7[3], lw[3], out=ys7[3], workspace=ws, stream=stream, pdl=pdl)
+            mb.linear_forward_grouped(xs7[4], lw[4:6], outs=ys7[4:6], workspace=ws, stream=stream, pdl=pdl)
+            mb.linear_forward(xs7[6], lw[6], out=ys7[6], workspace=ws, stream=stream, pdl=pdl)
 
-    decode_pass = per_op_pass if args.per_op else grouped_pass
-    calls_per_step = LAYERS * (len(LINEARS) if args.per_op else 4)
-    launches_per_step = 2 * calls_per_step  # every call = activation-quantization kernel + GEMV kernel
+    def per_op_pass():  # one C-ABI call per linear: 7 per layer
+        for lw in layers:
+            for i, w in enumerate(lw):
+                mb.linear_forward(xs7[i], w, out=ys7[i], workspace=ws, stream=stream, pdl=pdl)
+
+    structures = {"layer": (layer_pass, 1, "one call per layer: the seven independent linears of BASELINE config 1 in one launch"),
+                  "grouped": (grouped_pass, 4, "calls per layer: (q,k,v) (o) (gate,up) (down) - linears sharing their activations share a call"),
+                  "per-op": (per_op_pass, len(LINEARS), "one call per linear (7 per layer), as the reference's engine dispatches ops")}
+    decode_pass, calls_per_layer, structure_note = structures[args.calls]
+    calls_per_step = LAYERS * calls_per_layer
+    launches_per_step = calls_per_step  # every call is ONE launch: the GEMV quantizes the activations itself
     step_bytes = LAYERS * sum(algorithmic_bytes(1, k, n, hb) for _, k, n, hb in LINEARS)
 
-    with torch.cuda.stream(stream):
-        decode_pass()  # configures kernel attributes before capture
-    stream.synchronize()
-    mb.check_device_status(stream)
-    graph = None
-    if not args.no_graph:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            decode_pass()
+    def capture(fn):
+        with torch.cuda.stream(stream):
+            fn()  # configures kernel attributes before capture
+        stream.synchronize()
+        mb.check_device_status(stream)
+        if args.no_graph:
+            return None
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        return g
+
+    graph = capture(decode_pass)
 
     def step():
         if graph is not None:
@@ -367,27 +400,38 @@ def run_gpu(args):
     for _ in range(max(3, args.warmup)):
         step()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
     # graph.replay() launches on torch's current stream: time on that stream
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     timing_stream = torch.cuda.current_stream() if graph is not None else stream
+    # Timed regions of exactly --steps steps each, bracketed by a barrier and a synchronize on both sides.  At
+    # least 5 of them, and as many more as it takes to keep the GPU under this load for ~0.7 s, so that the clock
+    # sampler (one sample per 50 ms) sees the timed work at least ten times.  The reported time is the median region.
+    regions = []
     t_wall0 = time.time()
-    e0.record(timing_stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(timing_stream)
-    torch.cuda.synchronize()
+    while len(regions) < 5 or (time.time() - t_wall0 < 0.7 and len(regions) < 400):
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(timing_stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(timing_stream)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms_region = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms_region, float(len(regions) >= 4 and time.time() - t_wall0 >= 0.7)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the slowest rank's time; and every rank stops in the same round
+            ms_region = float(t[0].item())
+            regions.append(ms_region)
+            if t[1].item() > 0:
+                break
+        else:
+            regions.append(ms_region)
     t_wall1 = time.time()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms_total = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    ms_total = float(np.median(regions))
     ms_per_step = ms_total / args.steps
     mb.check_device_status()
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
@@ -396,33 +440,56 @@ def run_gpu(args):
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "frac_of_8TBs_spec": achieved / 8000.0, "peak_kind": f"of {peak_kind}", "traffic": None,
-                "kernel": "w4a32_gemv_kernel<1>", "gemv_launches_per_step": calls_per_step,
-                "avg_gemv_launch_us": ms_per_step * 1e3 / calls_per_step,
-                "algorithmic_bytes_per_gemv_launch": step_bytes / calls_per_step,
-                "note": "achieved = algorithmic bytes of the step / device time of the step; each GEMV launch is "
-                        "preceded by its activation-quantization kernel, whose time is inside the step"}
-    # dram__bytes_read + dram__bytes_write of the four GEMV launches of one layer, from the ncu capture
-    # summarized in profiles/gemv_decode_qwen2_1p5b.md (26.61 MB per layer vs 26.49 MB algorithmic)
-    if not args.per_op:
-        roofline["traffic"] = NCU_GEMV_DRAM_BYTES_PER_LAYER / 4.0
-        roofline["traffic_note"] = "ncu dram bytes per GEMV launch, average over the 4 launches of a layer"
+                "kernel": "w4a32_gemv_stream_kernel<1>", "gemv_launches_per_step": launches_per_step,
+                "avg_gemv_launch_us": ms_per_step * 1e3 / launches_per_step,
+                "algorithmic_bytes_per_gemv_launch": step_bytes / launches_per_step,
+                "note": "achieved = algorithmic bytes of the step / device time of the step; a launch quantizes its "
+                        "activations itself (no separate kernel)"}
+    # dram__bytes_read + dram__bytes_write per launch of the layer call, from the ncu capture summarized in
+    # profiles/gemv_decode_qwen2_1p5b.md (kept as numbers in the .json beside it)
+    try:
+        prof = json.load(open(os.path.join(ROOT, "profiles", "gemv_decode_qwen2_1p5b.json")))
+        if args.calls in prof.get("dram_bytes_per_launch", {}):
+            roofline["traffic"] = prof["dram_bytes_per_launch"][args.calls]
+            roofline["traffic_note"] = prof.get("note")
+    except Exception as ex:
+        roofline["traffic_note"] = f"profiles/gemv_decode_qwen2_1p5b.json unreadable: {str(ex)[:80]}"
 
     line = {"metric": "W4A32 decode-linear HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32 -> f32", "data": "synthetic",
-            "config": {"workload": "qwen2-1.5b-decode-linears", "layers": LAYERS, "linears_per_layer": len(LINEARS),
-                       "M": 1, "weight_bytes_per_step": LAYERS * 26320896, "algorithmic_bytes_per_step": step_bytes,
-                       "l2": "737 MB of weights per step > 126 MB L2: no flush between steps",
-                       "launch": ("cuda-graph replay" if graph is not None else "stream launches") + (", PDL" if pdl else "")
-                                 + (", one call per linear (7 per layer)" if args.per_op else
-                                    ", calls per layer: (q,k,v) (o) (gate,up) (down) - linears sharing their activations share a call"),
-                       "parallelism": "replicas (one token per GPU)" if world > 1 else "single GPU"},
+            "config": workload_config(),
+            "run": {"calls": args.calls, "calls_per_step": calls_per_step,
+                    "launch": ("cuda-graph replay" if graph is not None else "stream launches") + (", PDL" if pdl else "")
+                              + ", " + structure_note,
+                    "timing": f"median of {len(regions)} regions of {args.steps} steps",
+                    "parallelism": "replicas (one token per GPU)" if world > 1 else "single GPU"},
             "roofline": roofline, "gpu_launches": args.steps * launches_per_step,
+            "timed_regions_ms": [round(r, 4) for r in regions[:12]],
             "tokens_per_s_linears_only": world * 1e3 / ms_per_step}
 
     if rank == 0:
         sampler.stop()
         line["clocks"] = sampler.summary(t_wall0, t_wall1)
+
+    if rank == 0:
+        # the other call structures over the same weights (device time, graph replay, median of 5 x 10 steps)
+        cs = {args.calls: {"calls_per_layer": calls_per_layer, "ms_per_step": ms_per_step, "GBs": achieved,
+                           "frac": achieved / hbm_peak}}
+        for name, (fn, cpl, _) in structures.items():
+            if name == args.calls or (args.quick and not args.all_structures):
+                continue
+            gg = capture(fn)
+            run = gg.replay if gg is not None else (lambda fn=fn: fn())
+            for _ in range(3):
+                run()
+            ms_g = float(np.median([event_time_ms(torch, run, 10) for _ in range(5)]))
+            cs[name] = {"calls_per_layer": cpl, "ms_per_step": ms_g, "GBs": step_bytes / (ms_g * 1e-3) / 1e9,
+                        "frac": step_bytes / (ms_g * 1e-3) / 1e9 / hbm_peak}
+            del gg
+        line["call_structures"] = cs
+        for name, v in cs.items():
+            roofline[f"frac_{name.replace('-', '_')}_calls"] = v["frac"]
 
     if rank == 0 and not args.quick:
         # per-shape GEMV numbers, each over its 28 distinct weight copies
@@ -441,22 +508,6 @@ def run_gpu(args):
             per_shape[f"{name}_{k}x{n}"] = {"us": ms * 1e3 / LAYERS, "GBs": by * LAYERS / (ms * 1e-3) / 1e9}
             del g
         line["per_shape"] = per_shape
-
-        # the other call structure, for comparison
-        other = grouped_pass if args.per_op else per_op_pass
-        with torch.cuda.stream(stream):
-            other()
-        stream.synchronize()
-        gg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gg, stream=stream):
-            other()
-        for _ in range(3):
-            gg.replay()
-        ms_g = event_time_ms(torch, gg.replay, max(5, args.steps))
-        line["grouped" if args.per_op else "per_op"] = {
-            "calls_per_layer": 4 if args.per_op else 7, "ms_per_step": ms_g, "GBs": step_bytes / (ms_g * 1e-3) / 1e9,
-            "frac": step_bytes / (ms_g * 1e-3) / 1e9 / hbm_peak}
-        del gg
 
         # prefill: the same seven linears at M=512 (one layer after another, all 28 layers)
         xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
@@ -546,60 +597,58 @@ def run_gpu(args):
         except Exception as ex:
             line["prefill_fastest_grouped"] = {"error": str(ex)[:160]}
 
-        # e2e: the same step with HOST buffers (pinned), through the C ABI, one graph per step, and a host
-        # synchronize after every step because the host reads y.  Two ways to move the bytes:
-        #  "memcpy": per linear cudaMemcpyAsync H2D of x, forward, cudaMemcpyAsync D2H of y;
-        #  "mapped": the kernels read x from and write y to the pinned host buffers directly (unified
-        #            addressing): the same bytes cross PCIe inside the timed region, without copy nodes.
-        hx = {k: torch.randn((1, k)).pin_memory() for k in (1536, 8960)}
-        hy = {n: torch.empty((1, n)).pin_memory() for n in (1536, 256, 8960)}
-        sp = C.c_void_p(stream.cuda_stream)
+        # e2e: the same step with HOST buffers (pinned) through the C ABI: per layer one cudaMemcpyAsync H2D of the
+        # seven inputs, the layer call, one cudaMemcpyAsync D2H of the seven outputs; one CUDA graph per step and a host
+        # synchronize after every step because the host reads y.  Host wall clock: launch and synchronize included.
+        hx_all = torch.randn(x_all.shape).pin_memory()
+        hy_all = torch.empty(y_all.shape).pin_memory()
 
-        def e2e_pass(mode):
+        def e2e_pass():
             for lw in layers:
-                for w in lw:
-                    if mode == "memcpy":
-                        xs[w.k].copy_(hx[w.k], non_blocking=True)
-                        mb.linear_forward(xs[w.k], w, out=ys[w.n], workspace=ws, stream=stream, pdl=pdl)
-                        hy[w.n].copy_(ys[w.n], non_blocking=True)
-                    else:
-                        st = mb.lib().mllmb200_w4a32_linear_forward_ex(hx[w.k].data_ptr(), w.tiled.data_ptr(), hy[w.n].data_ptr(),
-                                                                       ws.data_ptr(), 1, w.k, w.n, w.k, w.n,
-                                                                       mb.KERNEL_AUTO | (0x100 if pdl else 0), sp)
-                        assert st == 0, mb.status_str(st)
+                x_all.copy_(hx_all, non_blocking=True)
+                if args.calls == "layer":
+                    mb.linear_forward_multi(xs7, lw, outs=ys7, stream=stream, pdl=pdl)
+                elif args.calls == "grouped":
+                    mb.linear_forward_grouped(xs7[0], lw[0:3], outs=ys7[0:3], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward(xs7[3], lw[3], out=ys7[3], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward_grouped(xs7[4], lw[4:6], outs=ys7[4:6], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward(xs7[6], lw[6], out=ys7[6], workspace=ws, stream=stream, pdl=pdl)
+                else:
+                    for i, w in enumerate(lw):
+                        mb.linear_forward(xs7[i], w, out=ys7[i], workspace=ws, stream=stream, pdl=pdl)
+                hy_all.copy_(y_all, non_blocking=True)
 
-        h2d = LAYERS * sum(k * 4 for _, k, n, _ in LINEARS)
-        d2h = LAYERS * sum(n * 4 for _, k, n, _ in LINEARS)
-        e2e_res = {}
-        for mode in ("memcpy", "mapped"):
-            try:
-                with torch.cuda.stream(stream):
-                    e2e_pass(mode)
-                stream.synchronize()
-                mb.check_device_status(stream)
-                g2 = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g2, stream=stream):
-                    e2e_pass(mode)
-                for _ in range(3):
-                    g2.replay()
-                torch.cuda.synchronize()
-                iters = max(5, args.steps)
+        h2d = LAYERS * x_all.numel() * 4
+        d2h = LAYERS * y_all.numel() * 4
+        try:
+            with torch.cuda.stream(stream):
+                e2e_pass()
+            stream.synchronize()
+            mb.check_device_status(stream)
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=stream):
+                e2e_pass()
+            for _ in range(3):
+                g2.replay()
+            torch.cuda.synchronize()
+            iters = max(5, args.steps)
+            samples = []
+            for _ in range(5):
                 t0 = time.perf_counter()
                 for _ in range(iters):
                     g2.replay()
                     torch.cuda.current_stream().synchronize()  # the host reads y after every step
-                    _ = float(hy[1536][0, 0])
-                e2e_res[mode] = (time.perf_counter() - t0) * 1e3 / iters  # host wall clock: includes launch + sync
-                del g2
-            except Exception as ex:  # mapped access needs unified addressing; keep the other number
-                e2e_res[mode + "_error"] = str(ex)[:120]
-        best = min((m for m in ("memcpy", "mapped") if m in e2e_res), key=lambda m: e2e_res[m])
-        ms_e2e = e2e_res[best]
-        line["e2e"] = {"value": step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
-                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "transfer": best,
-                       "ms_per_step_by_transfer": {k: v for k, v in e2e_res.items()},
-                       "how": "per linear: x in pinned host memory -> C-ABI forward -> y in pinned host memory; "
-                              "one CUDA graph per step; host synchronizes and reads y every step; host wall clock"}
+                    _ = float(hy_all[0])
+                samples.append((time.perf_counter() - t0) * 1e3 / iters)
+            ms_e2e = float(np.median(samples))
+            del g2
+            line["e2e"] = {"value": step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "transfer": "cudaMemcpyAsync, pinned host memory",
+                           "how": "per layer: the seven x in pinned host memory -> one H2D copy -> C-ABI call(s) -> one D2H copy "
+                                  "of the seven y into pinned host memory; one CUDA graph per step; host synchronizes and "
+                                  "reads y every step; host wall clock, median of 5 x %d steps" % iters}
+        except Exception as ex:
+            line["e2e"] = {"error": str(ex)[:200]}
 
         # CPU baselines on this box's host cores (single-process runs only: under a multi-process launcher
         # every rank is pinned to one OpenMP thread, which would misstate the host)
@@ -608,6 +657,11 @@ def run_gpu(args):
             line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": info["cores"], "kind": "reference",
                                     "sample": info["sample"], "variant": info["variant"],
                                     "ms_per_layer": info["ms_per_layer"]}
+            # the reference engine's default is 4 threads (mllm/Engine/Context.cpp:29): the same sample with 4
+            v4, i4 = time_reference_cpu(budget_s=4.0, max_threads=4)
+            if v4 is not None:
+                line["cpu_baseline"]["value_4_threads"] = v4
+                line["cpu_baseline"]["ms_per_layer_4_threads"] = i4["ms_per_layer"]
         try:
             if world != 1:
                 raise RuntimeError("single-process runs only")
@@ -644,6 +698,25 @@ def run_gpu(args):
         if rank == 0 and tp is not None:
             line["tp"] = tp
     if rank == 0:
+        # compact copies of the secondary results inside `roofline`, next to the headline fraction
+        def pick(obj, *path):
+            for key in path:
+                if not isinstance(obj, dict) or key not in obj:
+                    return None
+                obj = obj[key]
+            return obj
+        extras = {"config4_gemv_frac": pick(line, "config4", "gemv_M1", "frac"),
+                  "config4_gemm_fp16_frac_of_bf16": pick(line, "config4", "gemm_M2048_fp16", "frac_of_bf16_peak"),
+                  "prefill_frac_of_bf16": max([v for v in (pick(line, key, "frac_of_bf16_peak") for key in
+                                                          ("prefill", "prefill_f16", "prefill_fastest", "prefill_fastest_grouped"))
+                                               if v is not None], default=None),
+                  "decode_tokens_per_s": pick(line, "decoder", "decode_tokens_per_s"),
+                  "decode_distinct_tokens": pick(line, "decoder", "distinct_tokens"),
+                  "e2e_GBs": pick(line, "e2e", "value"),
+                  "tp_checked": pick(line, "tp", "checked"),
+                  "tp_gemm_speedup_vs_1gpu": pick(line, "tp", "gemm", "speedup_vs_1gpu"),
+                  "tp_gemv_speedup_vs_1gpu": pick(line, "tp", "gemv", "speedup_vs_1gpu")}
+        roofline.update({k: v for k, v in extras.items() if v is not None})
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -902,7 +975,7 @@ def run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
     ms = event_time_ms(torch, g.replay, 20) / len(copies)
     by = algorithmic_bytes(1, k, n, False)
     out["gemv_M1"] = {"us": ms * 1e3, "GBs": by / (ms * 1e-3) / 1e9, "frac": by / (ms * 1e-3) / 1e9 / hbm_peak,
-                      "peak_kind": f"of {peak_kind}", "how": "graph of 4 calls (quantization + GEMV each) over 4 weight copies"}
+                      "peak_kind": f"of {peak_kind}", "how": "graph of 4 single-launch GEMV calls over 4 weight copies, programmatic dependent launch"}
     del g
     m = 2048
     xm = torch.randn((m, k), device="cuda", generator=gen)
@@ -980,7 +1053,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch on the stream instead of replaying a CUDA graph")
     ap.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch between linears")
-    ap.add_argument("--per-op", action="store_true", help="headline step with one call per linear instead of grouped calls")
+    ap.add_argument("--calls", default="layer", choices=["layer", "grouped", "per-op"],
+                    help="call structure of the headline step: one multi call per layer, the decoder's four calls per layer, or one call per linear")
+    ap.add_argument("--all-structures", action="store_true", help="with --quick: still time the other two call structures")
     ap.add_argument("--config4-only", action="store_true", help="only the section on BASELINE config 4's large matrix")
     ap.add_argument("--no-config4", action="store_true", help="skip the single-GPU section on BASELINE config 4's large matrix")
     ap.add_argument("--w4a16-only", action="store_true", help="only the section on the W4A16 sibling path")

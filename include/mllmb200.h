@@ -127,10 +127,15 @@ MLLMB200_API int mllmb200_w4a32_linear_forward(const float* x_dev, const void* t
                                                void* stream);
 
 /* Same, with the kernel family forced (tests and benchmarks):
- * 0 auto, 1 streaming GEMV (M <= 4), 2 SIMT dp4a GEMM, 3 tcgen05 kind::i8 GEMM (exact int32 group
- * sums, as the reference), 4 tcgen05 fp16 GEMM (M >= 64: group scales folded into an exact fp16 weight
- * operand, fp32 accumulation over all of K in tensor memory; same 1e-3*rms bound; auto never picks
- * it), 5 fastest: kernel 4 for M >= 128, else auto. */
+ * 0 auto, 1 streaming GEMV (M <= 4: ONE launch, x quantized inside it, ws_dev unused), 2 SIMT dp4a GEMM,
+ * 3 tcgen05 kind::i8 GEMM (exact int32 group sums, as the reference), 4 tcgen05 fp16 GEMM (M >= 64: group
+ * scales folded into an fp16 weight operand - exact for bf16-encoded scales, rounded to fp16's 11 bits
+ * (relative error <= 2^-11 per weight) for MLLMB200_SCALE_FP16 - fp32 accumulation over all of K in
+ * tensor memory; same 1e-3*rms bound; auto never picks it), 5 fastest: kernel 4 for M >= 128, else auto,
+ * 6 the two-launch GEMV (activation-quantization kernel + one-shot GEMV), kept for comparison.
+ * OR 0x100 into `kernel` to allow programmatic dependent launch for the GEMV kernels: the kernel then
+ * requests its (constant) weights while the previous kernel of the stream still runs and reads x only
+ * after that kernel has completed. */
 MLLMB200_API int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, float* y_dev,
                                                   void* ws_dev, int M, int K, int N, int ldx, int ldy,
                                                   int kernel, void* stream);
@@ -140,8 +145,8 @@ MLLMB200_API int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void
  * [1,4], all with the same K.  For M <= 4 this is a single kernel launch that quantizes x once per
  * CTA and streams all the weight matrices; for larger M the matrices share one quantization of x
  * when they take the same tensor-core path, else it is `count` ordinary forwards.
- * flags: bit 8 = allow programmatic dependent launch; low byte = kernel policy for larger M: 0 auto or
- * 5 fastest (as linear_forward_ex's kernel argument). */
+ * flags: bit 8 = allow programmatic dependent launch; low byte = kernel policy: 0 auto, 5 fastest
+ * (as linear_forward_ex's kernel argument), 6 the two-launch GEMV (M <= 4 only). */
 MLLMB200_API int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int ldx, int count,
                                                        const void* const* tiled_dev, float* const* y_dev,
                                                        const int* N, const int* ldy, void* ws_dev, int flags,
@@ -149,6 +154,41 @@ MLLMB200_API int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M
 
 /* Which kernel family `kernel = 0` picks for a shape (1, 2 or 3 as above). */
 MLLMB200_API int mllmb200_w4a32_select_kernel(int M, int K, int N);
+
+/* Several INDEPENDENT linears in one launch: count in [1,8] matrices [N[i], K[i]], each with its own
+ * activations x_dev[i] [M, ldx[i]] (pointers may repeat) and output y_dev[i] [M, ldy[i]], M <= 4.  The
+ * seven linears of one decoder layer at decode (BASELINE config 1) are such a set.  Every matrix gets a
+ * share of the grid in proportion to its size; each CTA quantizes the activations of its own matrix.
+ * (No counterpart in the reference, which dispatches one op at a time: mllm/Engine/Context.cpp:65-122.)
+ * MLLMB200_UNSUPPORTED when M > 4, count > 8 or the set has no GEMV plan: call the linears one by one.
+ * flags: bit 8 = allow programmatic dependent launch. */
+MLLMB200_API int mllmb200_w4a32_linear_forward_multi(int count, const float* const* x_dev, const int* ldx,
+                                                     const int* K, const void* const* tiled_dev,
+                                                     float* const* y_dev, const int* N, const int* ldy, int M,
+                                                     int flags, void* stream);
+
+/* Host-only (no GPU needed): the streaming GEMV's work decomposition for a call of `count` matrices
+ * [N[i], K[i]] with activations [M, K[i]] - clusters, CTAs per cluster, shared-memory ring shape - and
+ * a replay of it with the kernel's own integer arithmetic that verifies every weight cell is
+ * requested and consumed exactly once, every consumed cell's activation group is quantized by its
+ * CTA, and every 32-row panel is finished exactly once.  (The reference has no counterpart:
+ * KleidiAI's ukernel takes m/n steps from a table, kai_linear.cpp:123-218.)
+ * MLLMB200_OK, MLLMB200_UNSUPPORTED when the call has no GEMV plan, 100 + c when check c fails.
+ * Output pointers may be NULL. */
+MLLMB200_API int mllmb200_w4a32_gemv_plan_check(int M, int count, const int* K, const int* N, int* clusters,
+                                                int* cluster_size, int* cells_per_stage, int* stages,
+                                                size_t* smem_bytes);
+
+/* Profiling aid for the streaming GEMV (no counterpart in the reference): while dev_buf is set, the
+ * next capacity_launches GEMV launches of this process each record 20 words (8 bytes each) at
+ * dev_buf[1 + 20 * launch_index ...]: for thread 0 of the first CTA, then of the last CTA, eight
+ * global-timer values (ns) - kernel entry, prologue done (first weight copies requested), previous
+ * kernel complete (programmatic dependent launch), activations quantized, main loop done, partial
+ * sums visible, cluster peers started, outputs stored - then the clock cycles that thread spent
+ * waiting for weights to land, then one unused word.  dev_buf must hold 1 + 20 * capacity_launches
+ * words and stay alive.  A launch replayed from a CUDA graph overwrites the slot it was captured
+ * with.  dev_buf = NULL switches the trace off.  Calls cudaMemcpyToSymbol: not during stream capture. */
+MLLMB200_API int mllmb200_w4a32_gemv_trace(void* dev_buf, int capacity_launches);
 
 /* Activation quantization alone (rows -> int8 + {recip scale, -zero point} headers in the
  * reference's row layout of k + 8 bytes, tests/Arm/KaiLinearTest.hpp:163-230), for parity tests.

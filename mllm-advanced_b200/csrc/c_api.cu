@@ -18,6 +18,13 @@ cudaError_t launch_act_quant_records(const float*, int, int, int, uint8_t*, floa
 int w4a32_gemm_tc_m_pad(int m);
 // gemv.cu / gemm_simt.cu / gemm_tc.cu
 bool w4a32_gemv_supported(int m, int k, int n);
+// gemv_stream.cu: the single-launch GEMV (quantizes x itself; up to 8 matrices, each with its own activations)
+bool w4a32_gemv_stream_supported(int m, int count, const int* k, const int* n);
+cudaError_t launch_w4a32_gemv_stream(int count, const float* const* x, const int* ldx, const uint8_t* const* a_rec,
+                                     const float2* const* a_hdr, int m, const int* k, const void* const* tiled,
+                                     float* const* y, const int* n, const int* ldy, int use_pdl, cudaStream_t stream);
+int w4a32_gemv_stream_plan_check(int, int, const int*, const int*, int*, int*, int*, int*, size_t*);
+cudaError_t w4a32_gemv_stream_set_trace(unsigned long long*, int);
 cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
                                       const int*, const int*, int, cudaStream_t);
 cudaError_t launch_w4a32_gemm_simt(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
@@ -142,7 +149,7 @@ int mllmb200_w4a32_quant_activations(const float* x_dev, int M, int K, int ldx, 
 }
 
 int mllmb200_w4a32_select_kernel(int M, int K, int N) {
-  if (w4a32_gemv_supported(M, K, N)) return 1;
+  if (M > 0 && K > 0 && N > 0 && w4a32_gemv_stream_supported(M, 1, &K, &N)) return 1;
   if (w4a32_gemm_tc_supported(M, K, N)) return 3;
   return 2;
 }
@@ -167,10 +174,16 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int use_pdl = (kernel >> 8) & 1;
   kernel &= 0xFF;
-  if (kernel < 0 || kernel > 5) return MLLMB200_INVALID_ARG;
+  if (kernel < 0 || kernel > 6) return MLLMB200_INVALID_ARG;
   if (kernel == 5) kernel = w4a32_gemm_tcf16_preferred(M, K, N) ? 4 : 0;  // "fastest": fp16 path where it wins
   if (kernel == 0) kernel = mllmb200_w4a32_select_kernel(M, K, N);
-  if (kernel == 1 && !w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
+  if (kernel == 1) {  // single launch: x is quantized inside the GEMV, no workspace
+    if (!w4a32_gemv_stream_supported(M, 1, &K, &N)) return MLLMB200_UNSUPPORTED;
+    const cudaError_t e1 =
+        launch_w4a32_gemv_stream(1, &x_dev, &ldx, nullptr, nullptr, M, &K, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
+    return e1 == cudaSuccess ? MLLMB200_OK : cuda_fail(e1);
+  }
+  if (kernel == 6 && !w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   if (kernel == 3 && !w4a32_gemm_tc_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   if (kernel == 4) {  // fp16 tensor-core path: its own activation layout
     if (!w4a32_gemm_tcf16_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
@@ -185,7 +198,7 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
   float2* a_hdr;
   if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, use_pdl & 1, st, &a_rec, &a_hdr, kernel == 3)) return s;
   cudaError_t e;
-  if (kernel == 1) e = launch_w4a32_gemv_grouped(a_rec, a_hdr, M, K, 1, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
+  if (kernel == 6) e = launch_w4a32_gemv_grouped(a_rec, a_hdr, M, K, 1, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
   else if (kernel == 3) e = launch_w4a32_gemm_tc(a_rec, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);
   else e = launch_w4a32_gemm_simt(a_rec, a_hdr, tiled_dev, y_dev, M, K, N, ldy, st);
   return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
@@ -201,22 +214,31 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
                                           const int* ldy, void* ws_dev, int flags, void* stream) {
   if (!x_dev || !tiled_dev || !y_dev || !N || !ldy || count < 1 || count > 4 || M <= 0 || K <= 0 || ldx < K)
     return MLLMB200_INVALID_ARG;
-  bool gemv = true;
+  const float* xs[4];
+  int ldxs[4], ks[4];
   for (int i = 0; i < count; ++i) {
     if (!tiled_dev[i] || !y_dev[i] || N[i] <= 0 || ldy[i] < N[i]) return MLLMB200_INVALID_ARG;
     if ((reinterpret_cast<uintptr_t>(tiled_dev[i]) & 15u) || (reinterpret_cast<uintptr_t>(y_dev[i]) & 3u))
       return MLLMB200_INVALID_ARG;
-    gemv = gemv && w4a32_gemv_supported(M, K, N[i]);
+    xs[i] = x_dev;
+    ldxs[i] = ldx;
+    ks[i] = K;
   }
+  if ((flags & 0xFF) != 6 && w4a32_gemv_stream_supported(M, count, ks, N)) {
+    const cudaError_t e = launch_w4a32_gemv_stream(count, xs, ldxs, nullptr, nullptr, M, ks, tiled_dev, y_dev, N, ldy,
+                                                   (flags >> 8) & 1, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+  }
+  bool gemv = (flags & 0xFF) == 6;  // the two-launch path (quantization kernel + one-shot GEMV), kept for comparison
+  for (int i = 0; i < count && gemv; ++i) gemv = w4a32_gemv_supported(M, K, N[i]);
+  if ((flags & 0xFF) == 6 && !gemv) return MLLMB200_UNSUPPORTED;
   if (gemv) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* a_rec;
     float2* a_hdr;
     if (int s = quantize_into_ws(x_dev, ws_dev, M, K, ldx, (flags >> 8) & 1, st, &a_rec, &a_hdr)) return s;
     cudaError_t e = launch_w4a32_gemv_grouped(a_rec, a_hdr, M, K, count, tiled_dev, y_dev, N, ldy, (flags >> 8) & 1, st);
-    if (e == cudaSuccess) return MLLMB200_OK;
-    if (e != cudaErrorInvalidValue) return cuda_fail(e);
-    // no joint plan (too much shared memory for the group): fall through to one call per matrix
+    return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
   }
   // Larger M: the matrices share ONE quantization of x.  With the "fastest" policy (5) and M >= 128 they
   // also share ONE launch of the fp16 tensor-core kernel (their tiles side by side in the grid: q, k, v
@@ -255,6 +277,40 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
     if (st != MLLMB200_OK) return st;
   }
   return MLLMB200_OK;
+}
+
+int mllmb200_w4a32_linear_forward_multi(int count, const float* const* x_dev, const int* ldx, const int* K,
+                                        const void* const* tiled_dev, float* const* y_dev, const int* N, const int* ldy,
+                                        int M, int flags, void* stream) {
+  if (!x_dev || !ldx || !K || !tiled_dev || !y_dev || !N || !ldy || count < 1 || M <= 0) return MLLMB200_INVALID_ARG;
+  if (count > 8 || M > 4) return MLLMB200_UNSUPPORTED;
+  for (int i = 0; i < count; ++i) {
+    if (!x_dev[i] || !tiled_dev[i] || !y_dev[i] || K[i] <= 0 || N[i] <= 0 || ldx[i] < K[i] || ldy[i] < N[i])
+      return MLLMB200_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(tiled_dev[i]) & 15u) || (reinterpret_cast<uintptr_t>(x_dev[i]) & 3u) ||
+        (reinterpret_cast<uintptr_t>(y_dev[i]) & 3u))
+      return MLLMB200_INVALID_ARG;
+  }
+  if (!w4a32_gemv_stream_supported(M, count, K, N)) return MLLMB200_UNSUPPORTED;
+  const cudaError_t e = launch_w4a32_gemv_stream(count, x_dev, ldx, nullptr, nullptr, M, K, tiled_dev, y_dev, N, ldy,
+                                                 (flags >> 8) & 1, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+}
+
+int mllmb200_w4a32_gemv_plan_check(int M, int count, const int* K, const int* N, int* clusters, int* cluster_size,
+                                   int* cells_per_stage, int* stages, size_t* smem_bytes) {
+  if (!N || !K || count < 1 || count > 8 || M <= 0) return MLLMB200_INVALID_ARG;
+  for (int i = 0; i < count; ++i)
+    if (N[i] <= 0 || K[i] <= 0) return MLLMB200_INVALID_ARG;
+  const int r = w4a32_gemv_stream_plan_check(M, count, K, N, clusters, cluster_size, cells_per_stage, stages, smem_bytes);
+  if (r < 0) return MLLMB200_UNSUPPORTED;
+  return r == 0 ? MLLMB200_OK : 100 + r;
+}
+
+int mllmb200_w4a32_gemv_trace(void* dev_buf, int capacity_launches) {
+  if (dev_buf && (capacity_launches <= 0 || (reinterpret_cast<uintptr_t>(dev_buf) & 7u))) return MLLMB200_INVALID_ARG;
+  const cudaError_t e = w4a32_gemv_stream_set_trace(static_cast<unsigned long long*>(dev_buf), dev_buf ? capacity_launches : 0);
+  return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
 }
 
 int mllmb200_check_device_status(void* stream) {

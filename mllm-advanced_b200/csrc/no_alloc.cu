@@ -13,8 +13,9 @@
 // is a fixed capacity and a shared buffer:
 //  - every GPU that loads the library holds kStaticScratchBytes (1 MiB) until the process exits;
 //  - a call whose workspace (mllmb200_w4a32_workspace_size(M, K)) exceeds that is refused with
-//    MLLMB200_TOO_LARGE - decode-sized calls fit (M = 64 at K = 1536, M = 16 at K = 8960), prefill
-//    does not;
+//    MLLMB200_TOO_LARGE - batched-decode sizes fit (up to M = 256 at K = 1536, M = 63 at K = 8960),
+//    a 512-token prefill does not.  Calls with M <= 4 take the single-launch GEMV, which quantizes
+//    the activations in shared memory and does not touch the array at all;
 //  - all calls on a device share the one array and it keeps whatever the last call left.  Nothing
 //    in it has to start at zero (the quantization kernel overwrites every byte the matrix kernel
 //    reads), but two calls that overlap on the GPU (different streams) race on it: serialize them.
@@ -26,6 +27,10 @@
 
 #include "../../include/mllmb200.h"
 
+namespace mllmb200 {
+int record_cuda_failure(cudaError_t e);  // c_api.cu: remembers the code for mllmb200_last_cuda_error()
+}
+
 namespace {
 
 constexpr size_t kStaticScratchBytes = 1u << 20;
@@ -33,7 +38,9 @@ constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-// device address of g_static_scratch per device ordinal; filled on first use
+// Device address of g_static_scratch per device ordinal; filled on first use.  Not locked: two host
+// threads that make the first call on a device at the same time both look the address up and both
+// store the same value, and an aligned pointer store is not torn - a benign race.
 void* g_scratch_addr[kMaxDevices] = {};
 
 // Returns the device address of the scratch array on the current device (nullptr on failure).
@@ -74,7 +81,7 @@ int mllmb200_w4a32_linear_forward_static(const float* x_dev, const void* tiled_d
   if (need > kStaticScratchBytes) return MLLMB200_TOO_LARGE;
   int cuda_error = 0;
   void* scratch = scratch_address(&cuda_error);
-  if (scratch == nullptr) return MLLMB200_CUDA_ERROR;
+  if (scratch == nullptr) return mllmb200::record_cuda_failure((cudaError_t)cuda_error);
   // same kernels as the ordinary forward; only the workspace comes from the static array
   return mllmb200_w4a32_linear_forward(x_dev, tiled_dev, y_dev, scratch, M, K, N, ldx, ldy, stream);
 }

@@ -4,7 +4,7 @@ import os
 import numpy as np
 
 SCALE_BF16_TRUNC, SCALE_BF16_RNE, SCALE_FP16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_F16, KERNEL_FASTEST = 0, 1, 2, 3, 4, 5
+KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_F16, KERNEL_FASTEST, KERNEL_GEMV_2LAUNCH = 0, 1, 2, 3, 4, 5, 6
 KERNEL_FLAG_PDL = 0x100
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -54,6 +54,9 @@ def lib():
         "mllmb200_w4a32_linear_forward_grouped": ([vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp, C.c_int,
                                                    vp], C.c_int),
         "mllmb200_w4a32_select_kernel": ([C.c_int, C.c_int, C.c_int], C.c_int),
+        "mllmb200_w4a32_gemv_trace": ([vp, C.c_int], C.c_int),
+        "mllmb200_w4a32_gemv_plan_check": ([C.c_int, C.c_int, int_p, int_p, int_p, int_p, int_p, int_p, sz_p], C.c_int),
+        "mllmb200_w4a32_linear_forward_multi": ([C.c_int, vp, int_p, int_p, vp, vp, int_p, int_p, C.c_int, C.c_int, vp], C.c_int),
         "mllmb200_w4a32_quant_activations": ([vp, C.c_int, C.c_int, C.c_int, vp, vp], C.c_int),
         "mllmb200_check_device_status": ([vp], C.c_int),
         "mllmb200_conv3d_w4a32_plan": ([int_p, int_p, int_p, C.c_int, int_p, int_p, sz_p], C.c_int),
@@ -232,6 +235,45 @@ def linear_forward_grouped(x, weights_list, outs=None, workspace=None, stream=No
     _check(lib().mllmb200_w4a32_linear_forward_grouped(x.data_ptr(), m, k, x.stride(0), cnt, tiled, ys, ns, ldy,
                                                        workspace.data_ptr(), (KERNEL_FLAG_PDL if pdl else 0) | policy,
                                                        _stream_ptr(stream)), "linear_forward_grouped")
+    return outs
+
+
+def gemv_plan_check(m, ks, ns):
+    """Host-only replay of the streaming GEMV's work decomposition for matrices [ns[i], ks[i]] with activations
+    [m, ks[i]] (ks may be one int for all).  Returns a dict (clusters, cluster_size, cells_per_stage, stages, smem)
+    or None when the call has no GEMV plan; raises when the replay finds a cell or panel not covered exactly once."""
+    cnt = len(ns)
+    if isinstance(ks, int):
+        ks = [ks] * cnt
+    karr = (C.c_int * cnt)(*ks)
+    arr = (C.c_int * cnt)(*ns)
+    c, s, cpc, st, sm = C.c_int(), C.c_int(), C.c_int(), C.c_int(), C.c_size_t()
+    r = lib().mllmb200_w4a32_gemv_plan_check(m, cnt, karr, arr, C.byref(c), C.byref(s), C.byref(cpc), C.byref(st), C.byref(sm))
+    if r == 2:
+        return None
+    if r != 0:
+        raise MllmB200Error(r, f"gemv_plan_check failed check {r - 100}")
+    return {"clusters": c.value, "cluster_size": s.value, "cells_per_stage": cpc.value, "stages": st.value, "smem": sm.value}
+
+
+def linear_forward_multi(xs, weights_list, outs=None, stream=None, pdl=False):
+    """Several independent linears (each its own x [M, K_i]) in one launch; M <= 4, at most 8 of them."""
+    import torch
+    cnt = len(weights_list)
+    m = xs[0].shape[0]
+    assert len(xs) == cnt and all(x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and
+                                   x.shape[0] == m and x.shape[1] == w.k for x, w in zip(xs, weights_list))
+    if outs is None:
+        outs = [torch.empty((m, w.n), dtype=torch.float32, device=xs[0].device) for w in weights_list]
+    xp = (C.c_void_p * cnt)(*[x.data_ptr() for x in xs])
+    ldx = (C.c_int * cnt)(*[x.stride(0) for x in xs])
+    ks = (C.c_int * cnt)(*[w.k for w in weights_list])
+    tiled = (C.c_void_p * cnt)(*[w.tiled.data_ptr() for w in weights_list])
+    ys = (C.c_void_p * cnt)(*[o.data_ptr() for o in outs])
+    ns = (C.c_int * cnt)(*[w.n for w in weights_list])
+    ldy = (C.c_int * cnt)(*[o.stride(0) for o in outs])
+    _check(lib().mllmb200_w4a32_linear_forward_multi(cnt, xp, ldx, ks, tiled, ys, ns, ldy, m, KERNEL_FLAG_PDL if pdl else 0,
+                                                     _stream_ptr(stream)), "linear_forward_multi")
     return outs
 
 

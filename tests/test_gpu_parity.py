@@ -139,6 +139,101 @@ def test_gemv_vs_oracle(orc, m, k, n):
     assert np.array_equal(y, y2)
 
 
+@pytest.mark.parametrize("k,n", QWEN_SHAPES + [(64, 40), (1176, 1280)])
+@pytest.mark.parametrize("m", [1, 4])
+def test_gemv_two_launch_path_vs_oracle(orc, m, k, n):
+    """The activation-quantization kernel + one-shot GEMV pair (kernel 6; what the decoder's graph mode is built
+    from) against the oracle, and against the single-launch kernel within the same bar."""
+    rng = np.random.default_rng(k * 5 + n + m)
+    x, w, b = make_case(rng, m, n, k, bias=(n % 512 == 0))
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    y = gpu_forward(x, blob, mb.KERNEL_GEMV_2LAUNCH)
+    assert_close(y, ref, f"two-launch gemv m={m} k={k} n={n}")
+    assert_close(gpu_forward(x, blob, mb.KERNEL_GEMV), y, "single launch vs two launches")
+
+
+LAYER7 = [(1536, 1536, True), (1536, 256, True), (1536, 256, True), (1536, 1536, False), (1536, 8960, False),
+          (1536, 8960, False), (8960, 1536, False)]  # K, N, bias of q k v o gate up down
+
+
+@pytest.mark.parametrize("m", [1, 3])
+def test_gemv_multi_layer_vs_oracle(orc, m):
+    """BASELINE config 1 at decode: the seven linears of a decoder layer, each with its OWN activations, in ONE
+    launch (mllmb200_w4a32_linear_forward_multi), every output against the oracle; with programmatic dependent
+    launch the result is the same bit for bit."""
+    rng = np.random.default_rng(700 + m)
+    xs, wts, refs = [], [], []
+    for k, n, bias in LAYER7:
+        x, w, b = make_case(rng, m, n, k, bias=bias)
+        blob = mb.quant_prepack(w, b)
+        q, s, _ = mb.blob_sections(blob)
+        refs.append(orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b))
+        xs.append(torch.from_numpy(x).cuda())
+        wts.append(mb.W4A32Weights.from_blob(blob))
+    outs = mb.linear_forward_multi(xs, wts)
+    torch.cuda.synchronize()
+    mb.check_device_status()
+    for (k, n, _), o, ref in zip(LAYER7, outs, refs):
+        assert_close(o.cpu().numpy(), ref, f"multi m={m} k={k} n={n}")
+    outs2 = mb.linear_forward_multi(xs, wts, pdl=True)
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(outs, outs2))
+
+
+def test_gemv_multi_ragged_vs_oracle(orc):
+    """Odd sizes side by side in one launch: K with a short last group, odd K, N below a panel, one matrix twice."""
+    rng = np.random.default_rng(811)
+    shapes = [(33, 40, True), (1176, 1280, False), (64, 7, True), (4096, 96, False), (71, 9, True), (32, 32, False),
+              (257, 33, True), (8960, 64, False)]
+    m = 2
+    xs, wts, refs = [], [], []
+    for k, n, bias in shapes:
+        x, w, b = make_case(rng, m, n, k, bias=bias)
+        blob = mb.quant_prepack(w, b)
+        q, s, _ = mb.blob_sections(blob)
+        refs.append(orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b))
+        xs.append(torch.from_numpy(x).cuda())
+        wts.append(mb.W4A32Weights.from_blob(blob))
+    outs = mb.linear_forward_multi(xs, wts)
+    torch.cuda.synchronize()
+    mb.check_device_status()
+    for (k, n, _), o, ref in zip(shapes, outs, refs):
+        assert_close(o.cpu().numpy(), ref, f"multi ragged k={k} n={n}")
+
+
+def test_gemv_multi_refuses_what_it_cannot_do():
+    rng = np.random.default_rng(5)
+    x, w, b = make_case(rng, 5, 64, 64)
+    wt = mb.W4A32Weights.from_blob(mb.quant_prepack(w, b))
+    with pytest.raises(mb.MllmB200Error) as e:
+        mb.linear_forward_multi([torch.from_numpy(x).cuda()], [wt])  # M = 5: not a GEMV
+    assert e.value.status == 2  # MLLMB200_UNSUPPORTED
+
+
+def test_gemv_trace_records_ordered_stamps():
+    """The profiling aid: with a trace buffer set, a launch leaves increasing global-timer values."""
+    import ctypes as C
+    rng = np.random.default_rng(6)
+    x, w, b = make_case(rng, 1, 1536, 1536)
+    wt = mb.W4A32Weights.from_blob(mb.quant_prepack(w, b))
+    xd = torch.from_numpy(x).cuda()
+    buf = torch.zeros(1 + 20 * 2, dtype=torch.int64, device="cuda")
+    assert mb.lib().mllmb200_w4a32_gemv_trace(C.c_void_p(buf.data_ptr()), 2) == 0
+    try:
+        for _ in range(3):  # the third launch finds the buffer full and records nothing
+            mb.linear_forward(xd, wt, kernel=mb.KERNEL_GEMV)
+        torch.cuda.synchronize()
+    finally:
+        assert mb.lib().mllmb200_w4a32_gemv_trace(None, 0) == 0
+    t = buf.cpu().numpy()[1:].reshape(2, 2, 10)
+    for launch in range(2):
+        first = t[launch, 0, :8]
+        assert first[0] > 0 and np.all(np.diff(first) >= 0), first
+    mb.check_device_status()
+
+
 def test_cfg0_int4_uniform_fp16_scales(orc):
     """BASELINE config 0: x ~ N(0,1) [1,1536]; q uniform in [-8,7]; scales |N(0,0.02)|/7 as fp16."""
     g = torch.Generator().manual_seed(0)

@@ -99,3 +99,29 @@ def test_sizes():
     assert mb.tiled_size(8960, 1536) == 256 + 280 * 48 * 576 + 2 * 8960 * 4
     assert mb.tiled_size(33, 40) == 256 + 2 * 2 * 576 + 2 * 64 * 4
     assert mb.workspace_size(512, 1536) >= 512 * 1536 + 512 * 8
+
+
+def test_gemv_plan_replay_covers_every_cell_once():
+    """The streaming GEMV's work decomposition, replayed on the host with the kernel's own walk: every weight
+    cell requested and consumed once, every activation group a CTA reads quantized by it, every panel finished
+    once - for the BASELINE shapes (single, grouped, the seven linears of a layer, the 28672 x 8192 matrix and
+    its tensor-parallel shards) and for a seeded sweep of odd ones."""
+    import random
+    layer_k = [1536] * 6 + [8960]
+    layer_n = [1536, 256, 256, 1536, 8960, 8960, 1536]
+    cases = [(1, [1536], [1536]), (1, [1536] * 3, [1536, 256, 256]), (1, [1536] * 2, [8960, 8960]), (1, [8960], [1536]),
+             (1, layer_k, layer_n), (4, layer_k, layer_n), (1, [8192], [28672]), (4, [8192], [28672]),
+             (1, [8192], [28672 // 8]), (1, [8192], [28672 // 2]), (2, [1176], [1280]), (1, [33], [40]), (1, [32], [1])]
+    for m, ks, ns in cases:
+        plan = mb.gemv_plan_check(m, ks, ns)
+        assert plan is not None and plan["clusters"] >= 1, (m, ks, ns)
+        assert plan["smem"] <= 200 * 1024
+    rnd = random.Random(7)
+    planned = 0
+    for _ in range(300):
+        m = rnd.randint(1, 4)
+        cnt = rnd.randint(1, 8)
+        ks = [rnd.choice([32, 33, 64, 96, 100, 256, 1000, 1536, 4096, 8960, 12000, 20000]) for _ in range(cnt)]
+        ns = [rnd.choice([1, 7, 31, 32, 33, 64, 100, 256, 1000, 1536, 5000, 20000]) for _ in range(cnt)]
+        planned += mb.gemv_plan_check(m, ks, ns) is not None  # raises when the replay finds a fault
+    assert planned > 200

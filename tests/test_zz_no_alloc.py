@@ -6,7 +6,9 @@ synchronization is not acceptable.  For them the library keeps the activation wo
 1 MiB array of its own.  This test drives that entry point through the C ABI, twice in a row (the
 array is shared and keeps the previous call's contents, so the second call must not be disturbed by
 the first), and requires the same output as mllmb200_w4a32_linear_forward - bit for bit, since both
-run the same kernels, and in any case within the 1e-3 * rms bound the other GPU tests use.
+run the same kernels, and in any case within the 1e-3 * rms bound the other GPU tests use; one case
+is also compared with the CPU oracle so that this file stands on its own.  The second call of every
+case must leave the device's free memory where it was (nothing allocated, nothing freed).
 It also checks that an oversized request is refused instead of overrunning the array.
 
 The file name sorts last so that a run that stops at the first failure has already run every
@@ -35,23 +37,37 @@ def _static_forward(x, wt, y):
 def test_static_forward_matches_ordinary_forward_twice():
     assert torch.cuda.is_available()
     rng = np.random.default_rng(2024)
-    cases = [(1, 1536, 2048), (4, 8960, 1536), (48, 1536, 256)]  # GEMV, GEMV (M=4), tensor-core path
+    from oracle_lib import Oracle
+    orc = Oracle()
+    # kernels that keep the quantized activations in the scratch array: dp4a GEMM (M = 8), tensor-core GEMM
+    # (M = 48, M = 200); and the single-launch GEMV (M = 1, 4), which needs no scratch but shares the entry point
+    cases = [(8, 1536, 2048), (48, 1536, 256), (200, 1536, 256), (1, 1536, 2048), (4, 8960, 1536)]
     for m, k, n in cases:
         w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
         b = (rng.standard_normal(n) * 0.1).astype(np.float32)
-        wt = mb.W4A32Weights.from_blob(mb.quant_prepack(w, b))
+        blob = mb.quant_prepack(w, b)
+        wt = mb.W4A32Weights.from_blob(blob)
         for call in range(2):  # two calls in a row, different activations each time
-            x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+            x_np = rng.standard_normal((m, k)).astype(np.float32)
+            x = torch.from_numpy(x_np).cuda()
             ref = mb.linear_forward(x, wt)
             y = torch.full((m, n), float("nan"), device="cuda")
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
             st = _static_forward(x, wt, y)
             assert st == 0, mb.status_str(st)
             torch.cuda.synchronize()
+            if call == 1:  # the first call of the process may load the kernels' code
+                assert torch.cuda.mem_get_info()[0] == free_before, (m, k, n)
             mb.check_device_status()
             ref_np, y_np = ref.cpu().numpy(), y.cpu().numpy()
             rms = float(np.sqrt(np.mean(ref_np.astype(np.float64) ** 2)))
             assert np.max(np.abs(y_np - ref_np)) <= 1e-3 * rms, (m, k, n, call)
             assert np.array_equal(y_np, ref_np), (m, k, n, call)
+            if m == 8:  # and against the CPU oracle
+                q, s, _ = mb.blob_sections(blob)
+                want = orc.linear(x_np, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+                assert np.max(np.abs(y_np - want)) <= 1e-3 * rms, (m, k, n, call)
 
 
 def test_static_forward_rejects_requests_beyond_its_capacity():
