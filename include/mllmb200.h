@@ -341,6 +341,14 @@ MLLMB200_API int mllmb200_qwen2_phase_cycles(void* handle, long long* out, int c
 /* The decoder's CUDA stream (cudaStream_t), for event timing. */
 MLLMB200_API void* mllmb200_qwen2_stream(void* handle);
 
+/* Self-test of the bounded device-side waits (no counterpart in the reference).  Every wait on an
+ * mbarrier in this library has a tick limit; when it runs out the kernel raises the timeout bit of the
+ * status word and returns instead of hanging the GPU.  This launches one warp that waits, with the
+ * given limit (1 .. 2^31 clock ticks), for 16 bytes that are never sent: afterwards
+ * mllmb200_check_device_status reports MLLMB200_TIMEOUT once, and *gave_up_dev (device int, may be
+ * NULL) is 1.  The kernel returns normally; nothing faults. */
+MLLMB200_API int mllmb200_selftest_wait_timeout(long long limit_ticks, int* gave_up_dev, void* stream);
+
 /* Device-side status word (bounded waits that ran out, bad tile headers).  Synchronizes `stream`,
  * reads and clears the word.  0 = clean. */
 MLLMB200_API int mllmb200_check_device_status(void* stream);

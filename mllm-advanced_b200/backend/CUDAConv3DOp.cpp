@@ -27,8 +27,11 @@ CUDAW4A32Conv3DOp::CUDAW4A32Conv3DOp(const Conv3DOpCargo& cargo) : Conv3DOp(carg
 CUDAW4A32Conv3DOp::~CUDAW4A32Conv3DOp() { releaseDevice(); }
 
 void CUDAW4A32Conv3DOp::releaseDevice() {
-  if (tiled_dev_) cudaFree(tiled_dev_);
-  if (workspace_dev_) cudaFree(workspace_dev_);
+  if (tiled_dev_ || workspace_dev_) {
+    auto& be = registeredW4A32Backend();
+    be.deviceFree(tiled_dev_);
+    be.deviceFree(workspace_dev_);
+  }
   tiled_dev_ = workspace_dev_ = nullptr;
   workspace_bytes_ = 0;
 }
@@ -60,11 +63,9 @@ void CUDAW4A32Conv3DOp::forward(const std::vector<Tensor>& inputs, std::vector<T
   int st = mllmb200_conv3d_w4a32_plan(in_shape, kernel, stride, n_, nullptr, nullptr, &need);
   if (st != MLLMB200_OK) { MLLM_ERROR_EXIT(kError, "CUDAW4A32Conv3DOp {}: {}", name(), mllmb200_status_str(st)); }
   if (need > workspace_bytes_) {
-    if (workspace_dev_) {
-      cudaStreamSynchronize(static_cast<cudaStream_t>(currentW4A32Stream()));
-      cudaFree(workspace_dev_);
-    }
-    if (cudaMalloc(&workspace_dev_, need) != cudaSuccess) { MLLM_ERROR_EXIT(kCudaError, "CUDAW4A32Conv3DOp {}: out of device memory", name()); }
+    auto& be = registeredW4A32Backend();
+    be.deviceFree(workspace_dev_);  // stream order protects work that still reads it
+    workspace_dev_ = be.deviceAlloc(need);
     workspace_bytes_ = need;
   }
   st = mllmb200_conv3d_w4a32_forward(x.ptr<float>(), tiled_dev_, y.ptr<float>(), workspace_dev_, in_shape, kernel, stride, n_,

@@ -54,10 +54,22 @@ CUDAW4A32LinearOp::CUDAW4A32LinearOp(const LinearOpCargo& cargo) : LinearOp(carg
 CUDAW4A32LinearOp::~CUDAW4A32LinearOp() { releaseDevice(); }
 
 void CUDAW4A32LinearOp::releaseDevice() {
-  if (tiled_dev_) cudaFree(tiled_dev_);
-  if (workspace_dev_) cudaFree(workspace_dev_);
+  if (tiled_dev_ || workspace_dev_) {
+    auto& be = registeredW4A32Backend();
+    be.deviceFree(tiled_dev_);
+    be.deviceFree(workspace_dev_);
+  }
   tiled_dev_ = workspace_dev_ = nullptr;
   workspace_bytes_ = 0;
+}
+
+void CUDAW4A32LinearOp::growWorkspace(size_t need) {
+  // the old block goes back to the backend's cache; work that still reads it was enqueued on the backend's
+  // stream before this call and the next user of the block launches on the same stream
+  auto& be = registeredW4A32Backend();
+  be.deviceFree(workspace_dev_);
+  workspace_dev_ = be.deviceAlloc(need);
+  workspace_bytes_ = need;
 }
 
 void* uploadW4A32Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, int k, const std::string& name) {
@@ -86,17 +98,16 @@ void* uploadW4A32Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, in
   MLLMB200_CHECK(mllmb200_w4a32_blob_info(blob, blob_bytes, &bn, &bk, &scale_mode, &has_bias));
   if (bn != n || bk != k) { MLLM_ERROR_EXIT(kError, "{}: blob is {}x{} but the layer is {}x{}", name, bn, bk, n, k); }
 
-  auto stream = static_cast<cudaStream_t>(currentW4A32Stream());
-  void* blob_dev = nullptr;
-  void* tiled_dev = nullptr;
+  auto& be = registeredW4A32Backend();
+  auto stream = static_cast<cudaStream_t>(be.stream());
   size_t tiled_bytes = 0;
   MLLMB200_CHECK(mllmb200_w4a32_tiled_size(n, k, &tiled_bytes));
-  MLLMB200_CHECK_CUDA(cudaMalloc(&blob_dev, blob_bytes));
-  MLLMB200_CHECK_CUDA(cudaMalloc(&tiled_dev, tiled_bytes));
+  void* blob_dev = be.deviceAlloc(blob_bytes);
+  void* tiled_dev = be.deviceAlloc(tiled_bytes);
   MLLMB200_CHECK_CUDA(cudaMemcpyAsync(blob_dev, blob, blob_bytes, cudaMemcpyHostToDevice, stream));
   MLLMB200_CHECK(mllmb200_w4a32_repack_device(blob_dev, n, k, scale_mode, has_bias, 0, n, tiled_dev, stream));
-  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` and blob_dev go away below
-  MLLMB200_CHECK_CUDA(cudaFree(blob_dev));
+  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` (host) goes away below
+  be.deviceFree(blob_dev);
   return tiled_dev;
 }
 
@@ -122,17 +133,16 @@ void* uploadW4A16Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, in
   MLLMB200_CHECK(mllmb200_w4a16_blob_info(blob, blob_bytes, &bn, &bk, &has_bias));
   if (bn != n || bk != k) { MLLM_ERROR_EXIT(kError, "{}: blob is {}x{} but the layer is {}x{}", name, bn, bk, n, k); }
 
-  auto stream = static_cast<cudaStream_t>(currentW4A32Stream());
-  void* blob_dev = nullptr;
-  void* tiled_dev = nullptr;
+  auto& be = registeredW4A32Backend();
+  auto stream = static_cast<cudaStream_t>(be.stream());
   size_t tiled_bytes = 0;
   MLLMB200_CHECK(mllmb200_w4a16_tiled_size(n, k, &tiled_bytes));
-  MLLMB200_CHECK_CUDA(cudaMalloc(&blob_dev, blob_bytes));
-  MLLMB200_CHECK_CUDA(cudaMalloc(&tiled_dev, tiled_bytes));
+  void* blob_dev = be.deviceAlloc(blob_bytes);
+  void* tiled_dev = be.deviceAlloc(tiled_bytes);
   MLLMB200_CHECK_CUDA(cudaMemcpyAsync(blob_dev, blob, blob_bytes, cudaMemcpyHostToDevice, stream));
   MLLMB200_CHECK(mllmb200_w4a16_repack_device(blob_dev, n, k, has_bias, 0, n, tiled_dev, stream));
-  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` and blob_dev go away below
-  MLLMB200_CHECK_CUDA(cudaFree(blob_dev));
+  MLLMB200_CHECK_CUDA(cudaStreamSynchronize(stream));  // `owned` (host) goes away below
+  be.deviceFree(blob_dev);
   return tiled_dev;
 }
 
@@ -179,14 +189,7 @@ void CUDAW4A32LinearOp::forward(const std::vector<Tensor>& inputs, std::vector<T
     const int m = (int)(x.numel() / (size_t)k_);
     size_t need = 0;
     MLLMB200_CHECK(mllmb200_w4a16_workspace_size(m, k_, n_, &need));
-    if (need > workspace_bytes_) {
-      if (workspace_dev_) {
-        MLLMB200_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(currentW4A32Stream())));
-        MLLMB200_CHECK_CUDA(cudaFree(workspace_dev_));
-      }
-      MLLMB200_CHECK_CUDA(cudaMalloc(&workspace_dev_, need));
-      workspace_bytes_ = need;
-    }
+    if (need > workspace_bytes_) growWorkspace(need);
     MLLMB200_CHECK(mllmb200_w4a16_linear_forward(x.ptr<unsigned char>(), x.dtype() == kFp16 ? MLLMB200_DTYPE_F16 : MLLMB200_DTYPE_F32,
                                                  tiled_dev_, y.ptr<unsigned char>(), workspace_dev_, m, k_, n_, k_, n_,
                                                  currentW4A32Stream()));
@@ -200,17 +203,11 @@ void CUDAW4A32LinearOp::forward(const std::vector<Tensor>& inputs, std::vector<T
   const int m = (int)(x.numel() / (size_t)k_);
   size_t need = 0;
   MLLMB200_CHECK(mllmb200_w4a32_workspace_size(m, k_, &need));
-  if (need > workspace_bytes_) {
-    // grow once and keep: the reference allocates a workspace tensor on every call (LinearOp.cpp:41-43)
-    if (workspace_dev_) {
-      MLLMB200_CHECK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(currentW4A32Stream())));
-      MLLMB200_CHECK_CUDA(cudaFree(workspace_dev_));
-    }
-    MLLMB200_CHECK_CUDA(cudaMalloc(&workspace_dev_, need));
-    workspace_bytes_ = need;
-  }
-  MLLMB200_CHECK(mllmb200_w4a32_linear_forward(x.ptr<float>(), tiled_dev_, y.ptr<float>(), workspace_dev_, m, k_, n_, k_,
-                                               n_, currentW4A32Stream()));
+  // grow once and keep: the reference allocates a workspace tensor on every call (LinearOp.cpp:41-43)
+  if (need > workspace_bytes_) growWorkspace(need);
+  auto& be = registeredW4A32Backend();
+  MLLMB200_CHECK(mllmb200_w4a32_linear_forward_ex(x.ptr<float>(), tiled_dev_, y.ptr<float>(), workspace_dev_, m, k_, n_, k_,
+                                                  n_, be.linearKernelPolicy(), be.stream()));
 }
 
 }  // namespace mllm::cuda

@@ -27,8 +27,9 @@ class CUDAW4A32LinearOp final : public LinearOp {
 
  private:
   void releaseDevice();
+  void growWorkspace(size_t need);
 
-  void* tiled_dev_ = nullptr;      // weights in the tile layout
+  void* tiled_dev_ = nullptr;      // weights in the tile layout (from the backend's allocator)
   void* workspace_dev_ = nullptr;  // quantized activations, grown on demand, reused across calls
   size_t workspace_bytes_ = 0;
   int n_ = 0, k_ = 0;
@@ -43,7 +44,7 @@ class CUDALinearOpFactory : public TypedOpFactory<OpType::kLinear, LinearOpCargo
 };
 
 // Pre-pack blob (int8 tensor) or fp32 weight of an [n, k] matrix -> device buffer in the tile layout
-// (cudaMalloc'ed; the caller frees it).  Shared with the Conv3D op.
+// (from the registered backend's allocator; the caller returns it with deviceFree).  Shared with the Conv3D op.
 void* uploadW4A32Weights(Tensor& weight, Tensor& bias, bool want_bias, int n, int k, const std::string& name);
 
 // True for the impl types this op implements (the six f32 W4 Kai tiles; the tile choice is an

@@ -10,6 +10,8 @@
 #include <mutex>
 #include <vector>
 
+#include "mllm/Core/AOps/D2HOp.hpp"
+#include "mllm/Core/Tensor.hpp"
 #include "mllm/Engine/Allocator.hpp"
 #include "mllm/Engine/BackendBase.hpp"
 
@@ -44,16 +46,51 @@ class CUDAW4A32Backend final : public BackendBase {
   CUDAW4A32Backend();
   ~CUDAW4A32Backend();
 
-  // The stream every op of this backend launches on.
+  // The stream every op of this backend launches on (one per backend instance).
   [[nodiscard]] void* stream() const { return stream_; }
+
+  // Device memory for the ops' own buffers (packed weights, activation workspaces): the backend's caching
+  // allocator, so steady-state inference calls neither cudaMalloc nor cudaFree.
+  void* deviceAlloc(size_t bytes);
+  void deviceFree(void* ptr);
+
+  // Kernel policy of CUDAW4A32LinearOp::forward for M >= 17 (the `kernel` argument of
+  // mllmb200_w4a32_linear_forward_ex): 0 = the exact int8 tensor-core path (default: the reference's
+  // arithmetic), 5 = the fastest path (fp16 tensor-core kernel for M >= 128, same 1e-3 * rms bound).
+  void setLinearKernelPolicy(int policy) { linear_policy_ = policy; }
+  [[nodiscard]] int linearKernelPolicy() const { return linear_policy_; }
 
  private:
   void* stream_ = nullptr;  // cudaStream_t
+  int linear_policy_ = 0;
 };
 
 std::shared_ptr<CUDAW4A32Backend> createCUDAW4A32Backend();
 
-// Stream of the registered backend (nullptr = default stream when none is registered yet).
+// The backend registered with the engine for kCUDA (exits when none is, as every backend lookup of the engine does).
+CUDAW4A32Backend& registeredW4A32Backend();
+
+// Its stream.
 void* currentW4A32Stream();
+
+// Device -> host copy as an engine op (reference: mllm/Backends/CUDA/Ops/D2HOp.cpp:18-22; reached through
+// Tensor::cpu(), mllm/Core/Tensor.cpp:120-126).  Copies on the backend's stream and waits for it: the host reads
+// the result right after (mllm/Models/AutoLLM.hpp:70-85).
+class CUDAW4A32D2HOp final : public D2HOp {
+ public:
+  explicit CUDAW4A32D2HOp(const D2HOpCargo& cargo) : D2HOp(cargo) {}
+  void forward(const std::vector<Tensor>& inputs, std::vector<Tensor>& outputs) override;
+};
+
+class CUDAW4A32D2HOpFactory final : public TypedOpFactory<OpType::kD2H, D2HOpCargo> {
+ public:
+  std::shared_ptr<BaseOp> createOpImpl(const D2HOpCargo& cargo) override { return std::make_shared<CUDAW4A32D2HOp>(cargo); }
+};
+
+// Host -> device: a new kCUDA tensor of the same shape and dtype, allocated by the engine's memory manager and
+// filled on the backend's stream.  The reference has an OpType for this direction but no op
+// (mllm/Core/Tensor.cpp:128-132 "TODO Host 2 Device"), and the engine picks an op's backend from its INPUT's
+// device, i.e. the host's - so this is a function of the CUDA backend, not an op of it.
+Tensor toDevice(const Tensor& host);
 
 }  // namespace mllm::cuda

@@ -2,6 +2,7 @@
 
 #include <string>
 
+#include "mllm/Core/AOps/Conv3DOp.hpp"
 #include "mllm/Core/AOps/LinearOp.hpp"
 #include "mllm/IR/Builtin/Op.hpp"
 #include "mllm/IR/Graph/Op.hpp"
@@ -69,6 +70,44 @@ bool CudaQuantizationPass::quantizeLinear(const ir::op_ptr_t& op) {
   return true;
 }
 
+bool CudaQuantizationPass::quantizeConv3D(const ir::op_ptr_t& op) {
+  auto* conv = (Conv3DOp*)(op->cast_<ir::linalg::Conv3DOp>()->getAOp());
+  if (implFamily(cfg_.opImplType(conv->name())) != kFamily) return false;
+  const auto& cargo = conv->cargo();
+  const Tensor weight = conv->weight();
+  const Tensor bias = conv->bias();
+  if (weight.dtype() != kFp32 || (cargo.bias && bias.dtype() != kFp32)) {
+    MLLM_WARN("CudaQuantizationPass: {} needs an fp32 kernel (and bias); left unquantized", conv->name());
+    return false;
+  }
+  if (cargo.kernel_size.size() != 3) return false;
+  const int n = cargo.out_channels;
+  const int k = cargo.in_channels * cargo.kernel_size[0] * cargo.kernel_size[1] * cargo.kernel_size[2];
+  if ((size_t)weight.numel() != (size_t)n * (size_t)k) {
+    MLLM_WARN("CudaQuantizationPass: {} kernel must be [out, in, kt, kh, kw]; left unquantized", conv->name());
+    return false;
+  }
+  // The kernel is used as it lies: row o of the matrix is kernel[o] flattened in (c, kt, kh, kw) order, the column
+  // order of the op's im2col (mllm/Backends/Arm/Kernels/conv3d.cpp:49-62 of the reference).  The reference's own
+  // pattern first permutes the kernel to [out, kt, kh, kw, in] (KaiQuantizationPass.cpp:461-465), which does not
+  // match that column order when in_channels > 1; the pairing kept here is the one that computes the convolution.
+  size_t bytes = 0;
+  int st = mllmb200_w4a32_prepack_size(n, k, cargo.bias ? 1 : 0, &bytes);
+  if (st != MLLMB200_OK) return false;
+  Tensor packed = Tensor::empty({(int32_t)bytes}, kInt8, kCPU).alloc();
+  st = mllmb200_w4a32_quant_prepack(weight.ptr<float>(), cargo.bias ? bias.ptr<float>() : nullptr, n, k,
+                                    MLLMB200_SCALE_BF16_TRUNC, packed.ptr<uint8_t>());
+  if (st != MLLMB200_OK) {
+    MLLM_WARN("CudaQuantizationPass: {}: {}", conv->name(), mllmb200_status_str(st));
+    return false;
+  }
+  packed.setName(weight.name());
+  conv->weight() = packed;
+  conv->bias() = Tensor::empty({1}, kInt8, kCPU).alloc();
+  ++quantized_;
+  return true;
+}
+
 void CudaQuantizationPass::visitGraph(const ir::op_ptr_t& subgraph) {
   auto region = subgraph->cast_<ir::graph::SubGraphOp>()->getTopRegion();
   for (auto& node : region->ops()) {
@@ -78,6 +117,11 @@ void CudaQuantizationPass::visitGraph(const ir::op_ptr_t& subgraph) {
     } else if (node->isa_<ir::linalg::LinearOp>()) {
       if (!quantizeLinear(node)) {
         MLLM_WARN("CudaQuantizationPass: linear {} not quantized (no matching impl type in the config)",
+                  node->cast_<ir::linalg::LinalgIROp>()->getAOp()->name());
+      }
+    } else if (node->isa_<ir::linalg::Conv3DOp>()) {
+      if (!quantizeConv3D(node)) {
+        MLLM_WARN("CudaQuantizationPass: conv3d {} not quantized (no matching impl type in the config)",
                   node->cast_<ir::linalg::LinalgIROp>()->getAOp()->name());
       }
     }

@@ -1,6 +1,7 @@
 // Offline quantization pass for the B200 W4A32 linear: the counterpart of the reference's
-// KaiQuantizationPass (mllm/Backends/Arm/Passes/KaiQuantizationPass.{hpp,cpp}) for Linear ops whose
-// configured impl type is a KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk tile.  It replaces the op's
+// KaiQuantizationPass (mllm/Backends/Arm/Passes/KaiQuantizationPass.{hpp,cpp}) for Linear ops - and
+// Conv3D ops run as a linear (KaiQuantizationPass.cpp:402-495) - whose configured impl type is a
+// KaiLinear_f32_qai8dxp_qsi4c32p_mxk_nxk tile.  It replaces the op's
 // fp32 [N,K] weight by the 1-D int8 pre-pack blob of include/mllmb200.h (same tensor name) and the
 // bias by a 1-byte int8 placeholder, exactly the convention the reference writes into .mllm files.
 #pragma once
@@ -21,6 +22,10 @@ class CudaQuantizationPass final : public ir::Pass {
 
   // Quantizes one linalg LinearOp if the config asks for it; false when it was left untouched.
   bool quantizeLinear(const ir::op_ptr_t& op);
+
+  // The same for a linalg Conv3DOp: the fp32 kernel [O, C, kt, kh, kw] is the [O, C*kt*kh*kw] matrix of the
+  // implied linear, its rows in the (c, kt, kh, kw) order the im2col of the op produces.
+  bool quantizeConv3D(const ir::op_ptr_t& op);
 
   [[nodiscard]] int quantizedCount() const { return quantized_; }
 

@@ -63,6 +63,20 @@ static inline size_t ws_rec_bytes(int m, int k) {
 
 using namespace mllmb200;
 
+// Self-test of the bounded waits: one CTA arms an mbarrier for 16 bytes that nobody ever copies and waits for
+// them with the given tick limit.  The wait gives up, raises the timeout bit of the status word and the kernel
+// returns normally - nothing faults, nothing spins without bound.
+__global__ void selftest_wait_timeout_kernel(long long limit_ticks, int* gave_up) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    mbar_arrive_expect_tx(&bar, 16);  // the phase now needs 16 bytes that are never sent
+    const bool landed = mbar_wait_bounded(&bar, 0, limit_ticks);
+    if (gave_up) *gave_up = landed ? 0 : 1;
+  }
+}
+
 extern "C" {
 
 int mllmb200_last_cuda_error(void) { return t_last_cuda_error; }
@@ -310,6 +324,13 @@ int mllmb200_w4a32_gemv_plan_check(int M, int count, const int* K, const int* N,
 int mllmb200_w4a32_gemv_trace(void* dev_buf, int capacity_launches) {
   if (dev_buf && (capacity_launches <= 0 || (reinterpret_cast<uintptr_t>(dev_buf) & 7u))) return MLLMB200_INVALID_ARG;
   const cudaError_t e = w4a32_gemv_stream_set_trace(static_cast<unsigned long long*>(dev_buf), dev_buf ? capacity_launches : 0);
+  return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
+}
+
+int mllmb200_selftest_wait_timeout(long long limit_ticks, int* gave_up_dev, void* stream) {
+  if (limit_ticks < 1 || limit_ticks > (1ll << 31)) return MLLMB200_INVALID_ARG;
+  selftest_wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ticks, gave_up_dev);
+  const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
 }
 

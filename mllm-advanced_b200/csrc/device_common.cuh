@@ -50,11 +50,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity, at most ~2^31 clock ticks (about a second).
 // Returns false and raises the timeout bit in the status word when the wait runs out, so a
 // lost copy shows up as an error code on the host instead of a hung GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, long long limit_ticks = 1ll << 31) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > (1ll << 31)) {
+    if (clock64() - t0 > limit_ticks) {
       atomicOr(&g_device_status, kDevStatusTimeout);
       return false;
     }
@@ -98,6 +98,20 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
 // wait for the previous kernel's memory before touching data it may have produced.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Every CTA checks the tile header before it requests a single byte of the matrix: true when magic, row
+// count and K are what the call claims (a call whose N or K is larger than the buffer would otherwise read
+// past its end).  Called by ALL threads of the CTA (it synchronizes them); on a mismatch the bad-header bit
+// of the status word is raised and the CTA must return without touching the matrix.
+__device__ __forceinline__ bool tiled_header_ok_cta(const uint8_t* tiled, int n, int k) {
+  int bad = 0;
+  if (threadIdx.x == 0) {
+    const uint4 h = *reinterpret_cast<const uint4*>(tiled);  // magic, version, n, k
+    bad = !(h.x == kTiledMagic && h.z == (uint32_t)n && h.w == (uint32_t)k);
+    if (bad) atomicOr(&g_device_status, kDevStatusBadHeader);
+  }
+  return __syncthreads_or(bad) == 0;
+}
 
 // ------------------------------------------------------------------ scale decode
 __device__ __forceinline__ float decode_scale(uint32_t raw16, uint32_t scale_mode) {

@@ -15,8 +15,9 @@ constexpr int kSimtMTile = kSimtRowsPerWarp * kSimtWarps;
 
 __global__ void __launch_bounds__(kSimtWarps * 32) w4a32_gemm_simt_kernel(
     const uint8_t* __restrict__ a_rec, const float2* __restrict__ a_hdr, const uint8_t* __restrict__ tiled,
-    float* __restrict__ y, int m, int n, int ldy, int num_groups, size_t zsum_off, size_t bias_off) {
+    float* __restrict__ y, int m, int n, int k, int ldy, int num_groups, size_t zsum_off, size_t bias_off) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!tiled_header_ok_cta(tiled, n, k)) return;  // before the first byte of the matrix is read
   const int panel = blockIdx.x;
   const int m0 = blockIdx.y * kSimtMTile + warp * kSimtRowsPerWarp;
   if (m0 >= m) return;
@@ -79,7 +80,7 @@ cudaError_t launch_w4a32_gemm_simt(const uint8_t* a_rec, const float2* a_hdr, co
   if (my > 65535) return cudaErrorInvalidValue;
   dim3 grid((unsigned)num_panels, (unsigned)my, 1);
   w4a32_gemm_simt_kernel<<<grid, kSimtWarps * 32, 0, stream>>>(a_rec, a_hdr, static_cast<const uint8_t*>(tiled), y, m, n,
-                                                               ldy, num_groups, th.zsum_off, th.bias_off);
+                                                               k, ldy, num_groups, th.zsum_off, th.bias_off);
   return cudaGetLastError();
 }
 

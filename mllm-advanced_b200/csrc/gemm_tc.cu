@@ -68,6 +68,7 @@ template <int NT>
 __global__ void __launch_bounds__(kTcThreads, 1) w4a32_gemm_tc_kernel(const TcParams p) {
   using S = TcSmem<NT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
+  if (!tiled_header_ok_cta(p.tiled, p.n, p.k)) return;  // before any copy, barrier or tensor-memory allocation
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [kTcStages]
   uint64_t* mma_done = raw_full + kTcStages;               // [kTcStages] the MMAs of a stage completed

@@ -5,16 +5,19 @@
 // conversion and one FMA per (row, column, K-group) on the CUDA cores, which bounds it far below
 // the tensor cores.  Here the group scale moves INTO the weight operand:
 //   A[n, k] = fp16( (u[n,k] - 8) * s[n, group(k)] * 2^E )      B[m, k] = fp16( a_q[m, k] + a_off[m] )
-// Both are exact: (u - 8) has at most 4 significant bits (and 8 is a power of two), a bf16/fp16
-// scale at most 11 together with it, |a_q + a_off| <= 255 fits fp16 (so the zero point needs no
-// correction term and nothing cancels); 2^E (one exponent per matrix, from the
-// largest |scale| recorded in the tile header by the repack) keeps the products in fp16's normal
-// range.  Every product a_q * A is then exact in fp32, and the only difference to the reference
-// (tests/Arm/KaiLinearTest.hpp:338-377 of the reference project) is the order and rounding of the
-// fp32 additions, which the GEMV and SIMT paths change as well.  Stated bound: max|diff| <=
-// 1e-3 * rms(y), the bar of every other path; measured ~1e-6 * rms.  Scales more than 2^25 below
-// the matrix maximum fall into fp16 subnormals and lose low bits (contribution < 2^-25 of the
-// largest group's).
+// B is exact: |a_q + a_off| <= 255 fits fp16 (so the zero point needs no correction term and nothing
+// cancels).  A is exact for bf16-encoded scales (the reference's encoding and the default,
+// MLLMB200_SCALE_BF16_TRUNC / _RNE): (u - 8) has at most 3 significant bits, a bf16 scale 8, the
+// product at most 11 = what fp16 holds; 2^E (one exponent per matrix, from the largest |scale| recorded
+// in the tile header by the repack) keeps the products in fp16's normal range.  Every product a_q * A is
+// then exact in fp32, and the only difference to the reference (tests/Arm/KaiLinearTest.hpp:338-377 of
+// the reference project) is the order and rounding of the fp32 additions, which the GEMV and SIMT paths
+// change as well.  Stated bound: max|diff| <= 1e-3 * rms(y), the bar of every other path; measured
+// ~1e-6 * rms.  With fp16-ENCODED scales (MLLMB200_SCALE_FP16: 11 significant bits) the product needs up
+// to 14 bits and the HMUL2 below rounds it to 11: a relative error of at most 2^-12 per weight, which
+// shows up as about 1.5e-4 * rms(y) per output; stated bound for that mode 2e-3 * rms(y) (the exact
+// kernels 1-3 remain available for it).  Scales more than 2^25 below the matrix maximum fall into fp16
+// subnormals and lose low bits (contribution < 2^-25 of the largest group's).
 //
 //   y[m,n] = lhs_scale[m] * 2^-E * sum_k A[n,k] B[m,k] + bias[n]
 //
@@ -117,6 +120,9 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   for (int i = 1; i < kTfMaxProblems; ++i)
     if (i < p.num_problems && (int)blockIdx.x >= p.prob[i].tile_begin) pi = i;
   const TfProblem& pr = p.prob[pi];
+  if constexpr (!A16) {  // (the W4A16 launcher's kernels check their own header format)
+    if (!tiled_header_ok_cta(pr.tiled, pr.n, p.k)) return;  // before any copy, barrier or tensor-memory allocation
+  }
   const int tile_n = (int)blockIdx.x - pr.tile_begin, tile_m = blockIdx.y;
   const int panel0 = tile_n * kPanels, m0 = tile_m * NT;
   const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
@@ -263,7 +269,8 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
           w = *reinterpret_cast<const uint4*>(raw + g * kCellBytes + r * 16);
           sc = decode_scale(*reinterpret_cast<const uint16_t*>(raw + g * kCellBytes + kCellNibbleBytes + r * 2), scale_mode);
         }
-        const __half2 s2 = __float2half2_rn(sc * up);           // exact: a power-of-two multiple of a bf16/fp16 value
+        const __half2 s2 = __float2half2_rn(sc * up);           // exact: a power-of-two multiple of a bf16 / fp16 value
+        // (u - 8) * s2 below is exact for a bf16-encoded scale (3 + 8 bits); for an fp16-encoded one HMUL2 rounds it once
         const __half2 off = __floats2half2_rn(1032.0f, 1032.0f);  // 0x6400 | nibble = 1024 + nibble; weight = nibble - 8
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -330,11 +337,14 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
 template <int NT, int ROWS, bool A16 = false>
 static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_t stream) {
   using S = TfSmem<NT, ROWS, A16>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS, A16>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+  static bool configured[64] = {};  // function attributes are per device
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (!(dev >= 0 && dev < 64 && configured[dev])) {
+    e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS, A16>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const dim3 grid((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
   w4a32_gemm_tcf16_kernel<NT, ROWS, A16><<<grid, kTfThreads, S::kTotal, stream>>>(prm);

@@ -119,13 +119,18 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) w4a32_gemv_kerne
   // Arrive now, wait just before the remote stores: the barrier latency hides behind the work.
   if (p.split > 1) cluster_arrive_relaxed();
 
-  // ---- 1. every weight byte of this CTA in flight: lane c of warp 0 owns chunk c
+  // ---- 1. every weight byte of this CTA in flight: lane c of warp 0 owns chunk c.
+  // The tile header is checked first: a call whose N or K exceeds the buffer must not read past its end.
+  const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(pr.tiled);
+  const uint4 hdr4 = *reinterpret_cast<const uint4*>(pr.tiled);  // magic, version, n, k
+  const uint32_t hdr_magic = hdr4.x, hdr_n = hdr4.z, hdr_k = hdr4.w, scale_mode = hdr->scale_mode;
+  const bool hdr_ok = hdr_magic == kTiledMagic && hdr_n == (uint32_t)pr.n && hdr_k == (uint32_t)p.k;
   if (warp == 0) {
     if (lane < nchunks) mbar_init(&bars[lane], 1);
     if (lane == 31) mbar_init(&bars[kGemvMaxChunks], 1);
     mbar_fence_init();
     __syncwarp();
-    if (lane < nchunks) {
+    if (lane < nchunks && hdr_ok) {
       const uint8_t* src = pr.tiled + sizeof(TiledHeader) + ((size_t)panel0 * p.num_groups + g0) * kCellBytes;
       const int c0 = lane << p.chunk_shift;
       const uint32_t bytes = (uint32_t)(min(cells_per_chunk, total_cells - c0) * kCellBytes);
@@ -135,9 +140,6 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) w4a32_gemv_kerne
   }
   // the next kernel in the stream may start fetching its own (constant) weights now
   if (p.use_pdl) pdl_launch_dependents();
-  // header words: requested now, consumed in the main loop / epilogue
-  const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(pr.tiled);
-  const uint32_t hdr_magic = hdr->magic, hdr_n = hdr->n, hdr_k = hdr->k, scale_mode = hdr->scale_mode;
   // the weights are constant; the activations may come from the kernel before us
   if (p.use_pdl) pdl_wait_prior();
 
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) w4a32_gemv_kerne
     a_off = (float)__float_as_int(h.y);
   }
   __syncthreads();  // barrier initialisation visible to the waiters
-  bool ok = mbar_wait_bounded(&bars[kGemvMaxChunks], 0);  // on a timeout: keep going (barriers below), store nothing
+  bool ok = mbar_wait_bounded(&bars[kGemvMaxChunks], 0) && hdr_ok;  // on a timeout or a bad header: keep going (barriers below), store nothing
 
   // ---- 3. main loop.  The kGemvWarps / pp warps of a panel take its cells round robin; lane = weight row.
   const int wpp = kGemvWarps / p.pp;  // warps per panel
@@ -222,7 +224,6 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) w4a32_gemv_kerne
 #pragma unroll
   for (int m = 0; m < M_MAX; ++m) red[(warp * M_MAX + m) * 32 + lane] = acc[m];
   __syncthreads();
-  const bool hdr_ok = hdr_magic == kTiledMagic && hdr_n == (uint32_t)pr.n && hdr_k == (uint32_t)p.k;
   if (!hdr_ok && tid == 0) atomicOr(&g_device_status, kDevStatusBadHeader);
 
   // ---- 5. reduction + epilogue.  Warp rm (< M_MAX) finishes activation row rm for every panel of the CTA.

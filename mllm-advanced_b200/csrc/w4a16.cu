@@ -501,12 +501,16 @@ static cudaError_t a16_launch_fused(const A16Group& grp, int panels, const void*
   cfg.stream = st;
   const size_t rec_bytes = (size_t)MT * gps * kActRecordBytesA16;
   if (rec_bytes > 160 * 1024) return cudaErrorInvalidConfiguration;  // not reachable under the size rule of this kernel
-  static size_t configured = 48 * 1024 - sizeof(float) * (8 * MT * 32 + MT * 32);
-  if (rec_bytes > configured) {
-    const cudaError_t e = cudaFuncSetAttribute(a16_gemv_fused_kernel<MT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)(160 * 1024));
+  static bool configured[64] = {};  // function attributes are per device
+  if (rec_bytes > 48 * 1024 - sizeof(float) * (8 * MT * 32 + MT * 32)) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    configured = 160 * 1024;
+    if (!(dev >= 0 && dev < 64 && configured[dev])) {
+      e = cudaFuncSetAttribute(a16_gemv_fused_kernel<MT, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(160 * 1024));
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
   }
   cfg.dynamicSmemBytes = rec_bytes;
   cudaLaunchAttribute attr[2];

@@ -13,11 +13,15 @@ BIN = os.path.join(ROOT, "oracle", "_ref", "backend_boundary_test")
 
 @pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/backend_boundary_test not built (needs the reference tree)")
 def test_quantization_pass_through_reference_pass_manager_host_only():
-    """CudaQuantizationPass run by the reference's ir::PassManager on a flat IR module: the blob's
-    nibble and scale sections equal the oracle's quantizer bit for bit.  No GPU involved."""
-    r = subprocess.run([BIN, "--host-only"], capture_output=True, text=True, timeout=120)
+    """CudaQuantizationPass run by the reference's ir::PassManager on flat IR modules (Linear, the W4A16 sibling,
+    Conv3D): the blob's nibble and scale sections equal the oracle's quantizer bit for bit; and the quantizer
+    tool's whole flow (tools::createFlatModule + the pass + the reference's CommonParamQuantizePass + mllm::write)
+    over a generated 28-layer parameter file, read back with mllm::load.  No GPU involved."""
+    r = subprocess.run([BIN, "--host-only"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    assert "BOUNDARY TEST PASSED" in r.stdout and r.stdout.count("[ ok ]") >= 10
+    assert "BOUNDARY TEST PASSED" in r.stdout and r.stdout.count("[ ok ]") >= 60
+    assert "createFlatModule found 196 linears, the pass quantized 196" in r.stdout
+    assert "196 linear blobs bit-identical to the oracle's quantizer" in r.stdout
 
 
 @pytest.mark.gpu
@@ -29,3 +33,4 @@ def test_linear_op_through_reference_plugin_api():
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "BOUNDARY TEST PASSED" in r.stdout
     assert "FAIL" not in r.stdout.replace("0 failures", "")
+    assert r.stdout.count("nn::Conv3D forward") == 3  # the Conv3D op ran through nn::Conv3D on the CUDA backend

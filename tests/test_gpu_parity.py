@@ -322,6 +322,29 @@ def test_tcgen05_fp16_gemm_vs_oracle(orc, m, k, n):
     print(f"tcgen05 fp16 m={m} k={k} n={n}: max|diff| / rms = {float(np.max(np.abs(y - ref))) / rms:.2e}")
 
 
+@pytest.mark.parametrize("mode", [mb.SCALE_BF16_RNE, mb.SCALE_FP16])
+@pytest.mark.parametrize("m,k,n", [(128, 1536, 256), (512, 1536, 8960), (256, 8960, 1536), (200, 1176, 1280)])
+def test_tcgen05_fp16_gemm_other_scale_encodings(orc, m, k, n, mode):
+    """The fp16 tensor-core path (kernel 4, and policy 5 which picks it for M >= 128) under the other two scale
+    encodings.  bf16 scales (either rounding): the weight operand (u-8) * s is exact in fp16, bar 1e-3 * rms as
+    everywhere.  fp16-encoded scales (the encoding BASELINE config 0 states): the product needs up to 14 bits and
+    is rounded to fp16's 11 - relative error <= 2^-12 per weight; stated bar for that mode 2e-3 * rms(y)."""
+    rng = np.random.default_rng(m + k + n + mode)
+    x, w, b = make_case(rng, m, n, k, x_scale=rng.uniform(0.5, 2.0))
+    blob = mb.quant_prepack(w, b, scale_mode=mode)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b, mode)
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    bar = (2e-3 if mode == mb.SCALE_FP16 else TOL) * rms
+    for kern in (mb.KERNEL_TC_F16, mb.KERNEL_FASTEST):
+        y = gpu_forward(x, blob, kern)
+        err = float(np.max(np.abs(y.astype(np.float64) - ref)))
+        print(f"fp16 tensor-core path, scale mode {mode}, kernel {kern}, m={m} k={k} n={n}: max|diff| / rms = {err / rms:.2e}")
+        assert np.all(np.isfinite(y)) and err <= bar, (mode, kern, err / rms)
+    # the exact int8 path under the same encoding meets the common bar
+    assert_close(gpu_forward(x, blob, mb.KERNEL_TC), ref, f"int8 tensor-core path, scale mode {mode}")
+
+
 @pytest.mark.parametrize("policy", [0, 5])
 def test_grouped_prefill_shares_quantization(orc, policy):
     """q/k/v and gate/up at prefill size through the grouped call equal single calls bit for bit:
@@ -355,6 +378,56 @@ def test_tcgen05_prefill_layer_shapes_full_size():
         y = gpu_forward(x, blob, mb.KERNEL_TC)
         y2 = gpu_forward(x, blob, mb.KERNEL_SIMT)
         assert_close(y, y2, f"prefill k={k} n={n}")
+
+
+def test_config1_prefill_full_size_vs_oracle(orc):
+    """BASELINE config 1 at prefill, full size (M = 512, the four shapes of the 1.5B layer), every kernel policy
+    against the ORACLE: an output row depends on its own activation row only, so the oracle computes 64 of the
+    512 rows (spread over all four 128-row tiles) and those rows of every GPU result are compared."""
+    rng = np.random.default_rng(512)
+    sel = np.sort(rng.choice(512, 64, replace=False))
+    sel[0], sel[-1] = 0, 511
+    for k, n in QWEN_SHAPES:
+        x, w, b = make_case(rng, 512, n, k, bias=(n != 8960))
+        blob = mb.quant_prepack(w, b)
+        q, s, _ = mb.blob_sections(blob)
+        ref = orc.linear(np.ascontiguousarray(x[sel]), np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+        for kern in (mb.KERNEL_AUTO, mb.KERNEL_TC, mb.KERNEL_TC_F16, mb.KERNEL_FASTEST, mb.KERNEL_SIMT):
+            y = gpu_forward(x, blob, kern)
+            assert_close(y[sel], ref, f"config 1 prefill k={k} n={n} kernel {kern}")
+
+
+def test_config4_full_size_vs_oracle(orc):
+    """BASELINE config 4's matrix (W [28672, 8192], int4 + bf16 scales drawn directly): the GEMV at M = 2 against the
+    oracle on every output; the GEMM at M = 2048 (int8 and fp16 tensor-core kernels) against the oracle on 96
+    activation rows x 512 weight rows (rows of y depend on their own x row, columns on their own weight row)."""
+    n, k = 28672, 8192
+    g = torch.Generator().manual_seed(4)
+    nib = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, generator=g).numpy()
+    sc = (torch.randn((n, k // 32), generator=g).abs() * (0.02 / 7)).numpy()
+    s16 = (sc.view(np.uint32) >> 16).astype(np.uint16)
+    blob = mb.prepack_from_quantized(nib, s16, n, k, None, mb.SCALE_BF16_TRUNC)
+    wt = mb.W4A32Weights.from_blob(blob)
+    x2 = torch.randn((2, k), generator=g).numpy()
+    ref2 = orc.linear(x2, nib, s16, None)
+    y2 = mb.linear_forward(torch.from_numpy(x2).cuda(), wt, kernel=mb.KERNEL_GEMV).cpu().numpy()
+    mb.check_device_status()
+    assert_close(y2, ref2, "config 4 GEMV M=2")
+    m = 2048
+    xm = torch.randn((m, k), generator=g).numpy()
+    rng = np.random.default_rng(44)
+    xsel = np.sort(rng.choice(m, 96, replace=False))
+    wsel = np.sort(rng.choice(n, 512, replace=False))
+    xsel[0], xsel[-1], wsel[0], wsel[-1] = 0, m - 1, 0, n - 1
+    ref = orc.linear(np.ascontiguousarray(xm[xsel]), np.ascontiguousarray(nib[wsel]), np.ascontiguousarray(s16[wsel]), None)
+    xd = torch.from_numpy(xm).cuda()
+    for kern in (mb.KERNEL_TC, mb.KERNEL_TC_F16):
+        y = mb.linear_forward(xd, wt, kernel=kern)
+        torch.cuda.synchronize()
+        mb.check_device_status()
+        got = y[torch.from_numpy(xsel).cuda()][:, torch.from_numpy(wsel).cuda()].cpu().numpy()
+        assert_close(got, ref, f"config 4 GEMM M=2048 kernel {kern}")
+        del y
 
 
 def test_strided_input_and_output(orc):
@@ -462,3 +535,23 @@ def test_bad_header_reports_status():
         mb.check_device_status()
     assert e.value.status == 5
     mb.check_device_status()  # cleared
+
+
+def test_bounded_wait_gives_up_and_reports_timeout():
+    """Every device-side wait of the library is bounded.  A test kernel waits, with a short tick limit, for bytes
+    that nobody sends: it must come back (no hang), the status word must say MLLMB200_TIMEOUT exactly once, and
+    the GPU must be usable right after."""
+    import ctypes as C
+    mb.check_device_status()  # clean before
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = mb.lib().mllmb200_selftest_wait_timeout(1 << 20, C.c_void_p(flag.data_ptr()), None)  # ~0.5 ms of ticks
+    assert st == 0, mb.status_str(st)
+    with pytest.raises(mb.MllmB200Error) as e:
+        mb.check_device_status()
+    assert e.value.status == 4  # MLLMB200_TIMEOUT
+    assert int(flag.item()) == 1
+    mb.check_device_status()  # the word was cleared by the read
+    rng = np.random.default_rng(1)
+    x, w, b = make_case(rng, 1, 64, 64)
+    y = gpu_forward(x, mb.quant_prepack(w, b))  # the context is intact
+    assert np.all(np.isfinite(y))
