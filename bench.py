@@ -1004,44 +1004,82 @@ def run_config4(args, torch, mb, gen, hbm_peak, tensor_peak, peak_kind):
 
 
 def run_tp(args, torch, mb, dist, rank, world, gen):
-    """BASELINE config 4: W [28672, 8192] column-sharded over the ranks, x replicated, NCCL all-gather of y.
-    M=1 (GEMV) and a reduced M for the GEMM; device time, max over ranks."""
+    """BASELINE config 4 through the C ABI's tensor-parallel entry points (mllmb200_w4a32_tp_*): W [28672, 8192]
+    column-sharded over the ranks, x replicated, every rank ends with the full fp32 y.  The GEMV at M = 1 and the GEMM
+    at M = 2048 rows of x per call (four such calls are the config's 8192 rows), each with the fused gather (the
+    kernels' epilogues store into every rank's y over NVLink), with the NCCL baseline (ncclAllGather + re-assembly)
+    and against ONE GPU running the unsharded matrix in the same process.  Device time, max over ranks.  The gathered
+    result is compared on every rank with the unsharded one."""
     from mllm_b200 import tp
-    n_total, k = 28672, 8192
-    if n_total % (world * 32) != 0:
+    n, k = 28672, 8192
+    if n % (world * 32) != 0:
         return None
-    n_loc = n_total // world
-    g = torch.Generator(device="cuda").manual_seed(99)  # same on every rank: only the shard differs
-    w = make_random_weights(mb, torch, n_loc, k, False, gen)
-    out = {}
-    for m in (1, 256):
+    g = torch.Generator(device="cuda").manual_seed(99)  # the same matrix and activations on every rank
+    nib = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    sc = torch.randn((n, k // 32), device="cuda", generator=g).abs() * (0.02 / 7.0)
+    s16 = (sc.view(torch.int32) >> 16).to(torch.int16).cpu().numpy().view(np.uint16)
+    blob_host = mb.prepack_from_quantized(nib.cpu().numpy(), s16, n, k)  # int4 + bf16 scales drawn directly (config 0's distributions)
+    del nib, sc, s16
+    m_gemm = 2048
+    full = mb.W4A32Weights.from_blob(blob_host)  # the unsharded matrix, for the one-GPU time and the check
+    tpl = tp.TensorParallelLinear(blob_host, m_gemm)
+    del blob_host
+    ws_full = torch.empty(mb.workspace_size(m_gemm, k), dtype=torch.uint8, device="cuda")
+    out = {"workload": "config4: W[28672,8192] int4 g32 column-sharded over the ranks; fused gather (peer stores from the "
+                       "kernels' epilogues) vs NCCL all-gather vs one GPU, same process, device time, max over ranks",
+           "world": world}
+    checked = True
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = float(np.median([event_time_ms(torch, fn, iters) for _ in range(3)]))
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for key, m, kern, iters in (("gemv", 1, mb.KERNEL_AUTO, 50), ("gemm", m_gemm, mb.KERNEL_FASTEST, 10)):
         x = torch.randn((m, k), device="cuda", generator=g)
-        y_loc = torch.empty((m, n_loc), device="cuda")
-        ws = torch.empty(mb.workspace_size(m, k), dtype=torch.uint8, device="cuda")
-
-        kern = mb.KERNEL_AUTO if m == 1 else mb.KERNEL_FASTEST
-
-        def fwd():
-            mb.linear_forward(x, w, out=y_loc, workspace=ws, kernel=kern)
-
-        def fwd_gather():
-            mb.linear_forward(x, w, out=y_loc, workspace=ws, kernel=kern)
-            tp.gather_columns(y_loc, n_total, n_loc)  # all-gather + [world, M, N/world] -> [M, N]
-        res = {}
-        for name, fn in (("compute_ms", fwd), ("compute_allgather_ms", fwd_gather)):
-            for _ in range(3):
-                fn()
+        y1 = torch.empty((m, n), device="cuda")
+        res = {"M": m}
+        res["one_gpu_ms"] = timed(lambda: mb.linear_forward(x, full, out=y1, workspace=ws_full, kernel=kern), iters)
+        res["tp_fused_ms"] = timed(lambda: tpl.forward(x, gather=tp.GATHER_PEER_STORES, kernel=kern), iters)
+        res["tp_nccl_ms"] = timed(lambda: tpl.forward(x, gather=tp.GATHER_NCCL, kernel=kern), iters)
+        res["tp_compute_only_ms"] = timed(lambda: tpl.forward(x, gather=tp.GATHER_NONE, kernel=kern), iters)
+        res["speedup_vs_1gpu"] = res["one_gpu_ms"] / res["tp_fused_ms"]
+        res["speedup_vs_1gpu_nccl"] = res["one_gpu_ms"] / res["tp_nccl_ms"]
+        recv_bytes = (world - 1) / world * m * n * 4
+        res["nvlink_bound_ms"] = recv_bytes / 770e9 * 1e3  # every rank receives the other ranks' blocks; 770 GB/s measured peer copy
+        res["tflops" if m > 1 else "GBs_weights_alg"] = (2.0 * m * k * n / (res["tp_fused_ms"] * 1e-3) / 1e12 if m > 1 else
+                                                         algorithmic_bytes(m, k, n, False) / (res["tp_fused_ms"] * 1e-3) / 1e9)
+        # the gathered result against the unsharded one computed here: the GEMM bit for bit (a tile's sum does not depend
+        # on how the rows are sharded), the GEMV within 1e-5 * rms (the shard splits K over its CTAs differently)
+        mb.linear_forward(x, full, out=y1, workspace=ws_full, kernel=kern)
+        ok = True
+        for mode in (tp.GATHER_PEER_STORES, tp.GATHER_NCCL):
+            tpl.output(m).zero_()
             torch.cuda.synchronize()
             dist.barrier()
-            ms = event_time_ms(torch, fn, 10)
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            res[name] = float(t.item())
-        by = algorithmic_bytes(m, k, n_total, False)
-        res["GBs_weights_alg"] = by / (res["compute_allgather_ms"] * 1e-3) / 1e9
-        res["tflops"] = 2.0 * m * k * n_total / (res["compute_allgather_ms"] * 1e-3) / 1e12
-        out[f"M{m}"] = res
-    out["workload"] = "config4: W[28672,8192] int4 g32, column-sharded, NCCL all-gather of y [world, M, N/world]"
+            y = tpl.forward(x, gather=mode, kernel=kern)
+            torch.cuda.synchronize()
+            mb.check_device_status()
+            if m > 1:
+                ok = ok and bool(torch.equal(y, y1))
+            else:
+                rms = float(y1.pow(2).mean().sqrt())
+                ok = ok and float((y - y1).abs().max()) <= 1e-5 * rms
+            dist.barrier()
+        flag = torch.tensor([1.0 if ok else 0.0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        res["checked"] = bool(flag.item() > 0.5)
+        checked = checked and res["checked"]
+        out[key] = res
+        del y1
+    out["checked"] = checked
+    dist.barrier()
+    tpl.close()
     return out
 
 

@@ -341,6 +341,41 @@ MLLMB200_API int mllmb200_qwen2_phase_cycles(void* handle, long long* out, int c
 /* The decoder's CUDA stream (cudaStream_t), for event timing. */
 MLLMB200_API void* mllmb200_qwen2_stream(void* handle);
 
+/* ------------------------------------------------------------------------------------------
+ * Tensor parallelism over the GPUs of one node, one process per GPU (no counterpart in the reference, whose
+ * engine is single-device: mllm/Engine/Context.cpp:56-59).  Output channels are sharded: rank r holds rows
+ * [r N/g, (r+1) N/g) of W in the tile layout (mllmb200_w4a32_repack_device with that row range), x is
+ * replicated, and every rank ends up with the full fp32 y [M, N] in an output buffer that the library
+ * allocates and maps into the other ranks' processes (CUDA IPC).
+ *   tp_init          nranks in [1,8]; nccl_comm = an ncclComm_t (as void*) over exactly these ranks, or NULL.
+ *                    The library calls NCCL through the copy the process has already loaded (dlopen).
+ *   tp_alloc_output  collective: allocates this rank's y buffer (bytes must cover the largest M * N * 4 to be
+ *                    used) and a flag array, exchanges their IPC handles over the communicator and maps the peers'.
+ *                    Needs the communicator.  Synchronizes `stream`.
+ *   tp_ipc_export /  the same in two steps for hosts that move the 128-byte blobs themselves: export allocates and
+ *   tp_ipc_import    writes this rank's blob; import takes all ranks' blobs (nranks * 128 bytes, in rank order).
+ *   linear_forward_tp  y[:, r N/g : (r+1) N/g] = x W_r^T + b_r on this rank, delivered to all ranks:
+ *                    gather_mode 2 = the kernels' epilogues store every finished element into every rank's buffer
+ *                    (plain stores over NVLink while other tiles are still computed: the single-launch GEMV for
+ *                    M <= 4, the fp16 tensor-core GEMM for kernel policies 4 / 5 at M >= 128; other kernels
+ *                    compute the block and push it with strided device copies), then each rank flags every peer
+ *                    and waits - bounded, MLLMB200_TIMEOUT through mllmb200_check_device_status - for theirs;
+ *                    1 = NCCL baseline (ncclAllGather of the blocks + a re-assembly kernel; needs the
+ *                    communicator); 0 = no gather (own columns only).  `kernel` as in linear_forward_ex.
+ *                    N must be a multiple of 32 * nranks.  All ranks must make the same sequence of calls.
+ *                    Not capturable in a CUDA graph (a call counter is baked into the launches).
+ *   tp_output        the buffer again (device pointer, bytes).
+ * ------------------------------------------------------------------------------------------ */
+MLLMB200_API int mllmb200_w4a32_tp_init(int nranks, int rank, void* nccl_comm, void** handle);
+MLLMB200_API int mllmb200_w4a32_tp_alloc_output(void* handle, size_t y_bytes, float** y_dev, void* stream);
+MLLMB200_API int mllmb200_w4a32_tp_ipc_export(void* handle, size_t y_bytes, float** y_dev, void* blob_out);
+MLLMB200_API int mllmb200_w4a32_tp_ipc_import(void* handle, const void* all_blobs);
+MLLMB200_API int mllmb200_w4a32_linear_forward_tp(void* handle, const float* x_dev, const void* tiled_shard_dev,
+                                                  void* ws_dev, int M, int K, int N_total, int ldx, int kernel,
+                                                  int gather_mode, void* stream);
+MLLMB200_API int mllmb200_w4a32_tp_output(void* handle, float** y_dev, size_t* bytes);
+MLLMB200_API void mllmb200_w4a32_tp_destroy(void* handle);
+
 /* Self-test of the bounded device-side waits (no counterpart in the reference).  Every wait on an
  * mbarrier in this library has a tick limit; when it runs out the kernel raises the timeout bit of the
  * status word and returns instead of hanging the GPU.  This launches one warp that waits, with the

@@ -22,7 +22,8 @@ bool w4a32_gemv_supported(int m, int k, int n);
 bool w4a32_gemv_stream_supported(int m, int count, const int* k, const int* n);
 cudaError_t launch_w4a32_gemv_stream(int count, const float* const* x, const int* ldx, const uint8_t* const* a_rec,
                                      const float2* const* a_hdr, int m, const int* k, const void* const* tiled,
-                                     float* const* y, const int* n, const int* ldy, int use_pdl, cudaStream_t stream);
+                                     float* const* y, const int* n, const int* ldy, int use_pdl, cudaStream_t stream,
+                                     int num_peers = 0, float* const* y_peers = nullptr);
 int w4a32_gemv_stream_plan_check(int, int, const int*, const int*, int*, int*, int*, int*, size_t*);
 cudaError_t w4a32_gemv_stream_set_trace(unsigned long long*, int);
 cudaError_t launch_w4a32_gemv_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
@@ -39,7 +40,8 @@ cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, 
 cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t);
 int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n);
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
-                                            const int*, const int*, cudaStream_t);
+                                            const int*, const int*, cudaStream_t, int num_peers = 0,
+                                            float* const* y_peers = nullptr);
 
 static thread_local int t_last_cuda_error = 0;
 static int cuda_fail(cudaError_t e) {
@@ -59,6 +61,7 @@ static inline size_t ws_rec_bytes(int m, int k) {
   const size_t big = rec > blk ? rec : blk;
   return align_up(big > blk16 ? big : blk16, 256);
 }
+size_t w4a32_ws_rec_bytes(int m, int k) { return ws_rec_bytes(m, k); }  // for tp.cu
 }  // namespace mllmb200
 
 using namespace mllmb200;

@@ -49,12 +49,17 @@ constexpr int kTfThreads = (kTfDequantWarps + 2) * 32;
 constexpr int kTfTileRows = 128;   // weight rows per MMA (tensor-memory lanes); a CTA tile is ROWS = 128 or 256 of them
 
 constexpr int kTfMaxProblems = 4;
+constexpr int kTfMaxPeers = 7;
 struct TfProblem {          // one weight matrix of a launch; all problems share x (M, K, the activation blocks)
   const uint8_t* tiled;     // TiledHeader at offset 0
   void* y;                  // fp32 [M, ldy] (W4A32) or fp16 [M, ldy] (W4A16)
   int n, ldy, num_panels;
   int tile_begin;           // first blockIdx.x of this problem
   size_t bias_off;
+  // tensor parallelism (W4A32 only): every element is also stored at y_peer[i][m * ldy + n], i < num_peers - the
+  // output buffers of the other GPUs mapped into this process; plain stores that cross NVLink tile by tile
+  int num_peers;
+  float* y_peer[kTfMaxPeers];
 };
 struct TfParams {
   const uint8_t* a_blocks;  // activations, [num_groups][m8_pad][512 bytes] fp16 canonical blocks
@@ -318,7 +323,10 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
               } else {
                 const float2 h = s_hdr[c0 + i];
                 const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
-                static_cast<float*>(pr.y)[(size_t)m * pr.ldy + n] = clamp_flt_max(val);  // lanes = consecutive n: coalesced per m
+                const float out = clamp_flt_max(val);
+                const size_t at = (size_t)m * pr.ldy + n;
+                static_cast<float*>(pr.y)[at] = out;  // lanes = consecutive n: coalesced per m
+                for (int pe = 0; pe < pr.num_peers; ++pe) pr.y_peer[pe][at] = out;
               }
             }
           }
@@ -396,8 +404,9 @@ bool w4a32_gemm_tcf16_preferred(int m, int k, int n) { return w4a32_gemm_tcf16_s
 // w4a32_gemm_tcf16_tile_grouped for the same arguments.
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float2* a_hdr, int m, int k, int count,
                                             const void* const* tiled, float* const* y, const int* n, const int* ldy,
-                                            cudaStream_t stream) {
+                                            cudaStream_t stream, int num_peers, float* const* y_peers) {
   if (count < 1 || count > kTfMaxProblems) return cudaErrorInvalidValue;
+  if (num_peers > 0 && (count != 1 || num_peers > kTfMaxPeers || y_peers == nullptr)) return cudaErrorInvalidValue;
   const TfTile tile = tf_tile_for(m, count, n);
   const int nt = tile.nt;
   TfParams prm = {};
@@ -417,6 +426,8 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
     prm.prob[i].num_panels = (n[i] + kPanelRows - 1) / kPanelRows;
     prm.prob[i].tile_begin = tiles;
     prm.prob[i].bias_off = th.bias_off;
+    prm.prob[i].num_peers = num_peers > 0 ? num_peers : 0;
+    for (int j = 0; j < prm.prob[i].num_peers; ++j) prm.prob[i].y_peer[j] = y_peers[j];
     tiles += (n[i] + tile.rows - 1) / tile.rows;
   }
   if (tile.rows == 256) return launch_tf_t<256, 256>(prm, tiles, stream);
@@ -470,7 +481,7 @@ cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, 
 
 cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
                                     int n, int ldy, cudaStream_t stream) {
-  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream);
+  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream, 0, nullptr);
 }
 
 }  // namespace mllmb200

@@ -14,9 +14,10 @@
 // contiguous runs, one per CTA (S > 1 only where a matrix has too few panels, or too uneven a
 // number of them, to fill the SMs with whole panels; the size is chosen from what the device can
 // co-schedule).  A CTA walks its run in bands of two panels (one where the run begins or ends
-// inside a panel), each band in blocks of 16 K-groups; one block is one stage of a shared-memory
-// ring: one bulk copy of 9 KB per panel (cp.async.bulk, a full/empty mbarrier pair per stage).
-// Compute warp w takes K-groups w and w + 8 of the block: it reads the group's activation record
+// inside a panel), each band in blocks of 48 K-groups; one block is one stage of a shared-memory
+// ring: one bulk copy of up to 27 KB per panel (cp.async.bulk, a full/empty mbarrier pair per stage,
+// the weights marked evict-first in L2 so that they do not displace activations and outputs).
+// Compute warp w takes K-groups w, w + 8, ... of the block: it reads the group's activation record
 // once and uses it for the cell of either panel (lane = weight row, one 16-byte shared load = the
 // row's 32 nibbles, two masks, eight dp4a, one FMA with the group scale).  A small matrix fits
 // entirely in the ring, so all of its bytes are requested by the first instructions of the kernel
@@ -25,9 +26,11 @@
 // kernel.
 //
 // Under programmatic dependent launch the first copies are issued before griddepcontrol.wait, i.e.
-// while the previous kernels of the stream still run; with 288 threads, <= 72 registers and about a
-// third of the shared memory per CTA, three consecutive launches are resident on an SM together,
-// so a call's weights are requested two calls ahead.  Only what depends on x comes after the wait:
+// while the previous kernel of the stream still runs; with 288 threads, <= 96 registers and, for runs of
+// a few hundred KB, a ring of at most 90 KB, two consecutive launches are resident on an SM together,
+// so a call's first stages are in shared memory before its activations exist (long runs get a 180 KB
+// ring instead: the head start is worth less there than depth for the stream).  Only what depends on
+// x comes after the wait:
 //   * the dynamic per-row int8 quantization of x (reference: tests/Arm/KaiLinearTest.hpp:163-230;
 //     production call kai_linear.cpp:358-362), done by every CTA for itself into shared memory in
 //     the byte order the nibble masks produce (48-byte records, layout.h) - only the K-groups the
@@ -40,8 +43,11 @@
 //     rank order - deterministic.
 //
 // Measured on B200 (CUDA events, graph replay): the seven linears of a Qwen2-1.5B layer in one launch
-// ~10-11 us per layer (26.5 MB); the 28672 x 8192 matrix ~30 us (132 MB).  The main loop runs at
-// ~22 SM cycles per cell (shared-memory wavefronts + integer pipe, 8 warps), i.e. about HBM speed.
+// ~8.5 us per layer (26.5 MB), of which ~4 us are the chain's serial part (release of the dependent
+// launch ~1.3 us, quantization of x 1.3-2.4 us, epilogue 0.5 us); the 28672 x 8192 matrix ~27 us
+// (132 MB).  With its cells resident in shared memory the main loop takes ~16 SM cycles per cell for
+// single panels and ~12 for panel pairs (8 warps; shared-memory wavefronts + integer pipe); HBM
+// delivers a cell per ~25 cycles per SM.
 #include <algorithm>
 #include <vector>
 
@@ -53,17 +59,40 @@ constexpr int kGsCWarps = 8;                  // compute warps
 constexpr int kGsCThreads = kGsCWarps * 32;   // 256
 constexpr int kGsThreads = kGsCThreads + 32;  // + the producer warp
 constexpr int kGsMaxProblems = 8;
+constexpr int kGsMaxPeers = 7;
 constexpr int kGsMaxM = 4;
 constexpr int kGsMaxSlots = 16;       // (panels of a CTA's run) x (activation rows, padded) kept per warp
 constexpr int kGsMaxStages = 16;      // ring stages
 constexpr int kGsMaxCluster = 8;
-constexpr int kGsItemsPerThread = 3;  // 8-value items of x a thread keeps in registers between the two passes
+#ifndef MLLMB200_GS_ITEMS
+#define MLLMB200_GS_ITEMS 5
+#endif
+constexpr int kGsItemsPerThread = MLLMB200_GS_ITEMS;  // 8-value items of x a thread keeps in registers between the two passes
 constexpr size_t kGsSmemBudget = 200 * 1024;
-constexpr int kGsBlockGroups = 16;                            // K-groups of a panel per ring stage
-constexpr int kGsBandBytes = kGsBlockGroups * kCellBytes;     // 9216: one panel's share of a stage
+#ifndef MLLMB200_GS_BLOCK_GROUPS
+#define MLLMB200_GS_BLOCK_GROUPS 48
+#endif
+constexpr int kGsBlockGroups = MLLMB200_GS_BLOCK_GROUPS;      // K-groups of a panel per ring stage (a multiple of 16)
+#ifndef MLLMB200_GS_MIN_CTAS
+#define MLLMB200_GS_MIN_CTAS 2
+#endif
+#ifndef MLLMB200_GS_RING_KB
+#define MLLMB200_GS_RING_KB 90
+#endif
+#ifndef MLLMB200_GS_RING_LONG_KB
+#define MLLMB200_GS_RING_LONG_KB 180
+#endif
+// Ring of a run too long to be in flight all at once.  Runs of a few hundred KB get the small ring: two CTAs
+// then fit on an SM, so the next launch of a chain moves in beside the running one and has its first stages
+// in shared memory by the time its activations are ready.  For long runs that head start is worth less than
+// a deep ring for the stream itself.
+constexpr long long kGsRingBytes = MLLMB200_GS_RING_KB * 1024LL;
+constexpr long long kGsRingBytesLong = MLLMB200_GS_RING_LONG_KB * 1024LL;
+constexpr long long kGsLongRunBytes = 400 * 1024LL;
+constexpr int kGsBandBytes = kGsBlockGroups * kCellBytes;     // 27648: one panel's share of a stage
 
 // How a CTA walks its run of cells [cb, ce) (cells of the cluster, [panel][K-group] order): in bands of one
-// or two whole-or-partial panels, each band in blocks of 16 K-groups.  One block of a band is one ring stage
+// or two whole-or-partial panels, each band in blocks of kGsBlockGroups K-groups.  One block of a band is one ring stage
 // (one bulk copy per panel of the band); two panels in a band let a warp use the activation record of a
 // K-group for two cells.  The producer, the compute warps and the host-side plan check all run this code.
 struct GsWalk {
@@ -72,7 +101,7 @@ struct GsWalk {
   int panel;  // first panel of the current band (relative to the cluster's first panel)
   int R;      // panels of the current band (0 before the first)
   int g_end, g_next;
-  int g0, cnt;  // current stage: first K-group and number of K-groups (<= 16)
+  int g0, cnt;  // current stage: first K-group and number of K-groups (<= kGsBlockGroups)
   bool band_end;
   __host__ __device__ void init(int cb, int ce_, int G_, int rmax_) {
     G = G_;
@@ -125,11 +154,15 @@ struct GsProblem {
   int num_groups, num_panels;
   int cl_begin, clusters;     // clusters [cl_begin, cl_begin + clusters) of the grid work on this matrix
   size_t zsum_off, bias_off;  // byte offsets of the per-row arrays inside the tiled buffer
+  // tensor parallelism: the same element is also stored at y_peer[i][m * ldy + n] for i < num_peers - the output
+  // buffers of the other GPUs, mapped into this process (plain stores over NVLink)
+  int num_peers;
+  float* y_peer[kGsMaxPeers];
 };
 
 struct GsParams {
   int m, cluster_size;
-  int rmax, stages;  // panels per band (1 or 2: a ring stage is rmax * 9216 bytes), ring stages
+  int rmax, stages;  // panels per band (1 or 2: a ring stage is rmax * kGsBandBytes bytes), ring stages
   int np_max;       // panels a CTA's run may touch (np_max * M_MAX <= kGsMaxSlots)
   int g_max;        // largest num_groups of the call (sizes the record buffer)
   int use_pdl, num_problems, trace;
@@ -216,7 +249,7 @@ __device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kGsCThreads) : "memory"); }
 
 template <int M_MAX>
-__global__ void __launch_bounds__(kGsThreads, 3) w4a32_gemv_stream_kernel(const __grid_constant__ GsParams p) {
+__global__ void __launch_bounds__(kGsThreads, MLLMB200_GS_MIN_CTAS) w4a32_gemv_stream_kernel(const __grid_constant__ GsParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   // the next kernels of the stream may become resident and start fetching their own (constant) weights
@@ -293,14 +326,20 @@ __global__ void __launch_bounds__(kGsThreads, 3) w4a32_gemv_stream_kernel(const 
 
   if (warp == kGsCWarps) {
     // =============================== producer warp ===============================
-    // a stage = one block of <= 16 K-groups of a band: one contiguous copy per panel of the band
+    // a stage = one block of <= kGsBlockGroups K-groups of a band: one contiguous copy per panel of the band
     const uint8_t* cells_src = pr.tiled + sizeof(TiledHeader) + (size_t)p0 * G * kCellBytes;  // first cell of the cluster
+    const uint64_t stream_once = l2_policy_evict_first();
     auto issue_stage = [&](const GsWalk& w, int st) {  // one thread
       const uint32_t bytes = (uint32_t)(w.cnt * kCellBytes);
       mbar_arrive_expect_tx(&full[st], bytes * (uint32_t)w.R);
       for (int r = 0; r < w.R; ++r)
+#ifdef MLLMB200_GS_NO_HINT
         bulk_g2s(ring + (size_t)st * stage_bytes + (size_t)r * kGsBandBytes,
-                 cells_src + ((size_t)(w.panel + r) * G + w.g0) * kCellBytes, bytes, &full[st]);
+                      cells_src + ((size_t)(w.panel + r) * G + w.g0) * kCellBytes, bytes, &full[st]);
+#else
+        bulk_g2s_hint(ring + (size_t)st * stage_bytes + (size_t)r * kGsBandBytes,
+                      cells_src + ((size_t)(w.panel + r) * G + w.g0) * kCellBytes, bytes, &full[st], stream_once);
+#endif
     };
     if (lane < NS) {
       mbar_init(&full[lane], 1);
@@ -370,43 +409,57 @@ __global__ void __launch_bounds__(kGsThreads, 3) w4a32_gemv_stream_kernel(const 
         const float* row = pr.x + (size_t)m * pr.ldx;
         const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
         float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
-        // loads item j (counted from first_item) into v8 and folds it into the running min/max
-        auto load_item = [&](int j, float (&v8)[8]) {
+        // Item j (counted from first_item) -> v8 and the running min/max.  The common case (a whole item of
+        // an aligned row) is split in two steps so that a thread has all its loads in flight before it uses
+        // the first of them: one round trip to memory per row instead of one per item.
+        auto item_k0 = [&](int j) {
           int item = first_item + j;
           if (item >= num_items) item -= num_items;
-          const int k0 = item * 8;
-          if (j < num_items && k0 < k) {
-            if (vec && k0 + 8 <= k) {
-              const float4 a = *reinterpret_cast<const float4*>(row + k0);
-              const float4 b = *reinterpret_cast<const float4*>(row + k0 + 4);
-              v8[0] = a.x; v8[1] = a.y; v8[2] = a.z; v8[3] = a.w;
-              v8[4] = b.x; v8[5] = b.y; v8[6] = b.z; v8[7] = b.w;
+          return item * 8;
+        };
+        auto fold = [&](const float (&v8)[8]) {
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                mn = fminf(mn, v8[e]);
-                mx = fmaxf(mx, v8[e]);
-              }
-            } else {
+          for (int e = 0; e < 8; ++e) {
+            mn = fminf(mn, v8[e]);
+            mx = fmaxf(mx, v8[e]);
+          }
+        };
+        auto load_ragged = [&](int k0, float (&v8)[8]) {  // an item cut by the end of the row, or an unaligned row
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const bool in = k0 + e < k;
-                v8[e] = in ? row[k0 + e] : 0.0f;
-                if (in) {
-                  mn = fminf(mn, v8[e]);
-                  mx = fmaxf(mx, v8[e]);
-                }
-              }
+          for (int e = 0; e < 8; ++e) {
+            const bool in = k0 + e < k;
+            v8[e] = in ? row[k0 + e] : 0.0f;
+            if (in) {
+              mn = fminf(mn, v8[e]);
+              mx = fmaxf(mx, v8[e]);
             }
           }
         };
+        auto load_whole = [&](int j, bool& is_whole, float (&v8)[8]) {
+          const int k0 = item_k0(j);
+          is_whole = vec && j < num_items && k0 + 8 <= k;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+          if (is_whole) {
+            a = *reinterpret_cast<const float4*>(row + k0);
+            b = *reinterpret_cast<const float4*>(row + k0 + 4);
+          }
+          v8[0] = a.x; v8[1] = a.y; v8[2] = a.z; v8[3] = a.w;
+          v8[4] = b.x; v8[5] = b.y; v8[6] = b.z; v8[7] = b.w;
+        };
         float v[kGsItemsPerThread][8];
+        bool whole[kGsItemsPerThread];
 #pragma unroll
-        for (int it = 0; it < kGsItemsPerThread; ++it) load_item(tid + it * kGsCThreads, v[it]);
-        // the rest of the row only feeds the min/max
-        for (int j = kGsItemsPerThread * kGsCThreads + tid; j < num_items; j += 2 * kGsCThreads) {
-          float t0[8], t1[8];
-          load_item(j, t0);
-          load_item(j + kGsCThreads, t1);
+        for (int it = 0; it < kGsItemsPerThread; ++it) load_whole(tid + it * kGsCThreads, whole[it], v[it]);
+#pragma unroll
+        for (int it = 0; it < kGsItemsPerThread; ++it) {
+          const int j = tid + it * kGsCThreads;
+          if (whole[it]) fold(v[it]);
+          else if (j < num_items && item_k0(j) < k) load_ragged(item_k0(j), v[it]);
+        }
+        // the rest of a very long row only feeds the min/max here, and is read again when it is packed
+        for (int j = kGsItemsPerThread * kGsCThreads + tid; j < num_items; j += kGsCThreads) {
+          float t0[8];
+          if (item_k0(j) < k) load_ragged(item_k0(j), t0);
         }
         mn = warp_min_f32(mn);
         mx = warp_max_f32(mx);
@@ -470,7 +523,7 @@ __global__ void __launch_bounds__(kGsThreads, 3) w4a32_gemv_stream_kernel(const 
     __syncthreads();  // (A) records and row constants visible to every warp; mbarriers initialised
     stamp(3);
 
-    // ---- main loop.  Of the <= 16 K-groups of a stage warp w takes groups w and w + 8, each for every panel
+    // ---- main loop.  Of the K-groups of a stage warp w takes groups w, w + 8, w + 16, ..., each for every panel
     // of the band.  The weights of the next stage are requested before the arithmetic of the current one.
     constexpr int RM = 2;  // panels per band the registers are laid out for
     float acc[RM][M_MAX];
@@ -558,40 +611,43 @@ __global__ void __launch_bounds__(kGsThreads, 3) w4a32_gemv_stream_kernel(const 
         break;
       }
       if (trace != nullptr) wait_cycles += clock64() - tw0;
-      const uint32_t base = ring_s + (uint32_t)st * stage_bytes + lane_off;
-      const uint32_t rec = abuf_s + (uint32_t)(cur.g0 + warp) * kActRecordBytes;
-      const bool has_a = warp < cur.cnt, has_b = warp + kGsCWarps < cur.cnt;
-      if (cur.R == 2) {
-        // requests for all four cells first, then the arithmetic
-        uint4 wa0 = make_uint4(0, 0, 0, 0), wa1 = wa0, wb0 = wa0, wb1 = wa0;
-        uint32_t sa0 = 0, sa1 = 0, sb0 = 0, sb1 = 0;
-        if (has_a) {
-          wa0 = lds128(base);
-          sa0 = lds16(base + scale_off);
-          wa1 = lds128(base + kGsBandBytes);
-          sa1 = lds16(base + kGsBandBytes + scale_off);
+      for (int h = 0; h < kGsBlockGroups; h += 2 * kGsCWarps) {  // 16 K-groups at a time: two per warp
+        if (h >= cur.cnt) break;
+        const uint32_t base = ring_s + (uint32_t)st * stage_bytes + lane_off + (uint32_t)h * kCellBytes;
+        const uint32_t rec = abuf_s + (uint32_t)(cur.g0 + h + warp) * kActRecordBytes;
+        const bool has_a = h + warp < cur.cnt, has_b = h + warp + kGsCWarps < cur.cnt;
+        if (cur.R == 2) {
+          // requests for all four cells first, then the arithmetic
+          uint4 wa0 = make_uint4(0, 0, 0, 0), wa1 = wa0, wb0 = wa0, wb1 = wa0;
+          uint32_t sa0 = 0, sa1 = 0, sb0 = 0, sb1 = 0;
+          if (has_a) {
+            wa0 = lds128(base);
+            sa0 = lds16(base + scale_off);
+            wa1 = lds128(base + kGsBandBytes);
+            sa1 = lds16(base + kGsBandBytes + scale_off);
+          }
+          if (has_b) {
+            wb0 = lds128(base + kGsCWarps * kCellBytes);
+            sb0 = lds16(base + kGsCWarps * kCellBytes + scale_off);
+            wb1 = lds128(base + kGsCWarps * kCellBytes + kGsBandBytes);
+            sb1 = lds16(base + kGsCWarps * kCellBytes + kGsBandBytes + scale_off);
+          }
+          if (has_a) compute2(wa0, sa0, wa1, sa1, rec);
+          if (has_b) compute2(wb0, sb0, wb1, sb1, rec + kGsCWarps * kActRecordBytes);
+        } else {
+          uint4 wa0 = make_uint4(0, 0, 0, 0), wb0 = wa0;
+          uint32_t sa0 = 0, sb0 = 0;
+          if (has_a) {
+            wa0 = lds128(base);
+            sa0 = lds16(base + scale_off);
+          }
+          if (has_b) {
+            wb0 = lds128(base + kGsCWarps * kCellBytes);
+            sb0 = lds16(base + kGsCWarps * kCellBytes + scale_off);
+          }
+          if (has_a) compute(wa0, sa0, rec, acc[0]);
+          if (has_b) compute(wb0, sb0, rec + kGsCWarps * kActRecordBytes, acc[0]);
         }
-        if (has_b) {
-          wb0 = lds128(base + kGsCWarps * kCellBytes);
-          sb0 = lds16(base + kGsCWarps * kCellBytes + scale_off);
-          wb1 = lds128(base + kGsCWarps * kCellBytes + kGsBandBytes);
-          sb1 = lds16(base + kGsCWarps * kCellBytes + kGsBandBytes + scale_off);
-        }
-        if (has_a) compute2(wa0, sa0, wa1, sa1, rec);
-        if (has_b) compute2(wb0, sb0, wb1, sb1, rec + kGsCWarps * kActRecordBytes);
-      } else {
-        uint4 wa0 = make_uint4(0, 0, 0, 0), wb0 = wa0;
-        uint32_t sa0 = 0, sb0 = 0;
-        if (has_a) {
-          wa0 = lds128(base);
-          sa0 = lds16(base + scale_off);
-        }
-        if (has_b) {
-          wb0 = lds128(base + kGsCWarps * kCellBytes);
-          sb0 = lds16(base + kGsCWarps * kCellBytes + scale_off);
-        }
-        if (has_a) compute(wa0, sa0, rec, acc[0]);
-        if (has_b) compute(wb0, sb0, rec + kGsCWarps * kActRecordBytes, acc[0]);
       }
       __syncwarp();  // every lane is done reading the stage
       if (lane == 0) mbar_arrive(&empty[st]);
@@ -634,7 +690,10 @@ __global__ void __launch_bounds__(kGsThreads, 3) w4a32_gemv_stream_kernel(const 
         const float2 rc = rowc[m];
         float v = fmaf(rc.y, zs, part);
         v = fmaf(v, rc.x, bs);
-        pr.y[(size_t)m * pr.ldy + n_pad] = clamp_flt_max(v);
+        v = clamp_flt_max(v);
+        const size_t at = (size_t)m * pr.ldy + n_pad;
+        pr.y[at] = v;
+        for (int i = 0; i < pr.num_peers; ++i) pr.y_peer[i][at] = v;
       }
     };
     for (int t = warp; t < npairs; t += kGsCWarps) {
@@ -750,13 +809,20 @@ static bool gs_make_plan(int m_max, int count, const int* groups, const int* pan
     g_max = std::max(g_max, groups[i]);
   }
   (void)total_cells;
-  const int sms = 148;  // one CTA per SM keeps three consecutive launches resident together
+  const int sms = 148;  // one CTA per SM and launch: the second slot of an SM belongs to the next launch of a chain
   // Clusters of matrix i for a given cluster size and budget: every matrix gets one, then the matrix whose
   // busiest CTA has the most cells gets the next, until the budget is spent or nobody can use more.
   auto allocate = [&](int s, int budget, int* c) {
     for (int i = 0; i < count; ++i) c[i] = 1;
     int used = count;
-    auto busiest = [&](int i) { return (double)((panels[i] + c[i] - 1) / c[i]) * groups[i] / s; };
+#ifndef MLLMB200_GS_QUANT_CELLS
+#define MLLMB200_GS_QUANT_CELLS 0.3
+#endif
+    // cells of the busiest CTA, plus what quantizing a row of that many K-groups costs it before its first cell
+    // (in cells' worth of time: every CTA of a matrix quantizes the row for itself)
+    auto busiest = [&](int i) {
+      return (double)((panels[i] + c[i] - 1) / c[i]) * groups[i] / s + MLLMB200_GS_QUANT_CELLS * groups[i];
+    };
     while (used < budget) {
       int pick = -1;
       double worst = -1.0;
@@ -807,7 +873,7 @@ static bool gs_make_plan(int m_max, int count, const int* groups, const int* pan
           stages_bound = std::max(stages_bound, ((per_cluster + 1) / 2) * blocks);
         } else {
           if (Lc >= 2LL * G) rmax = 2;
-          // every panel the run touches is walked in blocks of 16 groups: at most one short block per panel
+          // every panel the run touches is walked in blocks of kGsBlockGroups groups: at most one short block per panel
           stages_bound = std::max(stages_bound, (Lc + kGsBlockGroups - 1) / kGsBlockGroups + (np - 1));
         }
         break;
@@ -818,17 +884,25 @@ static bool gs_make_plan(int m_max, int count, const int* groups, const int* pan
     if ((long long)((P + c[i] - 1) / c[i]) * G * S >= (1LL << 31)) return false;
     if ((long long)P * (c[i] + 1) >= (1LL << 31)) return false;
   }
-  // ring: the whole run in flight when it fits in about 130 KB, else 8 stages (6 of the 18 KB kind) that wrap
-  const long long stage_bytes = (long long)rmax * kGsBandBytes;
+  // ring: the whole run in flight when it fits in kGsRingBytes, else as many stages as fit in that (at least 2),
+  // wrapping - of single panels when two stages of panel pairs would not fit
+  long long stage_bytes = (long long)rmax * kGsBandBytes;
   int stages = (int)std::min<long long>(stages_bound, kGsMaxStages);
-  if (stages_bound * stage_bytes > 132 * 1024) stages = rmax == 2 ? 6 : 8;
+  const long long ring_cap = stages_bound * stage_bytes > kGsLongRunBytes ? kGsRingBytesLong : kGsRingBytes;
+  if (stages_bound * stage_bytes > ring_cap) {
+    if (rmax == 2 && 2 * stage_bytes > ring_cap) {
+      rmax = 1;
+      stage_bytes = kGsBandBytes;
+    }
+    stages = (int)std::min<long long>(kGsMaxStages, std::max<long long>(2, ring_cap / stage_bytes));
+  }
   for (;;) {
     const GsSmem L = gs_smem_layout(m_max, g_max, S, rmax, stages, np_max);
     if (L.total <= kGsSmemBudget) {
       plan->smem = L.total;
       break;
     }
-    if (stages > 3) --stages;
+    if (stages > 2) --stages;
     else return false;
   }
   int begin = 0;
@@ -896,7 +970,8 @@ static cudaError_t gs_launch_t(const GsParams& prm, int grid, size_t smem, cudaS
 // Returns cudaErrorInvalidValue when the call has no plan (the caller uses the GEMM path).
 cudaError_t launch_w4a32_gemv_stream(int count, const float* const* x, const int* ldx, const uint8_t* const* a_rec,
                                      const float2* const* a_hdr, int m, const int* k, const void* const* tiled,
-                                     float* const* y, const int* n, const int* ldy, int use_pdl, cudaStream_t stream) {
+                                     float* const* y, const int* n, const int* ldy, int use_pdl, cudaStream_t stream,
+                                     int num_peers, float* const* y_peers) {
   if (count < 1 || count > kGsMaxProblems || m < 1 || m > kGsMaxM) return cudaErrorInvalidValue;
   const int m_max = m <= 1 ? 1 : (m <= 2 ? 2 : 4);
   int groups[kGsMaxProblems], panels[kGsMaxProblems];
@@ -939,6 +1014,12 @@ cudaError_t launch_w4a32_gemv_stream(int count, const float* const* x, const int
     q.clusters = plan.clusters[i];
     q.zsum_off = th.zsum_off;
     q.bias_off = th.bias_off;
+    q.num_peers = 0;
+    if (num_peers > 0 && y_peers != nullptr) {  // (single-matrix calls only: the same offsets in every peer's buffer)
+      if (count != 1 || num_peers > kGsMaxPeers) return cudaErrorInvalidValue;
+      q.num_peers = num_peers;
+      for (int j = 0; j < num_peers; ++j) q.y_peer[j] = y_peers[j];
+    }
   }
   const int grid = plan.total_clusters * plan.cluster_size;
   switch (m_max) {
@@ -1027,7 +1108,7 @@ int w4a32_gemv_stream_plan_check(int m, int count, const int* k, const int* n, i
               const size_t gc = (size_t)p0 * G + (size_t)cell;
               if (requested[gc]++) return 5;
               // consumed by warp j % 8 as its item j / 8
-              if (j >= 2 * kGsCWarps) return 7;
+              if (j >= kGsBlockGroups) return 7;
               if (consumed[gc]++) return 7;
             }
             if (w.band_end) {

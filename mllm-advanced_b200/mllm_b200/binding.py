@@ -60,6 +60,13 @@ def lib():
         "mllmb200_w4a32_quant_activations": ([vp, C.c_int, C.c_int, C.c_int, vp, vp], C.c_int),
         "mllmb200_check_device_status": ([vp], C.c_int),
         "mllmb200_selftest_wait_timeout": ([C.c_longlong, vp, vp], C.c_int),
+        "mllmb200_w4a32_tp_init": ([C.c_int, C.c_int, vp, C.POINTER(vp)], C.c_int),
+        "mllmb200_w4a32_tp_alloc_output": ([vp, C.c_size_t, C.POINTER(vp), vp], C.c_int),
+        "mllmb200_w4a32_tp_ipc_export": ([vp, C.c_size_t, C.POINTER(vp), vp], C.c_int),
+        "mllmb200_w4a32_tp_ipc_import": ([vp, vp], C.c_int),
+        "mllmb200_w4a32_linear_forward_tp": ([vp, vp, vp, vp] + [C.c_int] * 6 + [vp], C.c_int),
+        "mllmb200_w4a32_tp_output": ([vp, C.POINTER(vp), sz_p], C.c_int),
+        "mllmb200_w4a32_tp_destroy": ([vp], None),
         "mllmb200_conv3d_w4a32_plan": ([int_p, int_p, int_p, C.c_int, int_p, int_p, sz_p], C.c_int),
         "mllmb200_conv3d_w4a32_forward": ([vp, vp, vp, vp, int_p, int_p, int_p, C.c_int, vp], C.c_int),
         "mllmb200_w4a16_prepack_size": ([C.c_int, C.c_int, C.c_int, sz_p], C.c_int),

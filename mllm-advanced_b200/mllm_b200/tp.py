@@ -62,3 +62,68 @@ class ShardedW4A32Linear:
 
     def forward(self, x, group=None, **kw):
         return gather_columns(self.forward_local(x, **kw), self.n, self.shard_size, group)
+
+
+GATHER_NONE, GATHER_NCCL, GATHER_PEER_STORES = 0, 1, 2
+
+
+def nccl_comm_ptr(group=None):
+    """The ncclComm_t of a torch process group (as an int), once the group has run a collective."""
+    import torch
+    import torch.distributed as dist
+    pg = group if group is not None else dist.distributed_c10d._get_default_group()
+    return pg._get_backend(torch.device("cuda"))._comm_ptr()
+
+
+class _DevArray:
+    """Wraps a raw device pointer for torch.as_tensor (the CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr="<f4"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3}
+
+
+class TensorParallelLinear:
+    """One rank of a column-sharded W4A32 linear driven through the C ABI (mllmb200_w4a32_tp_*): the output buffer
+    [max_m, n] lives in memory the library maps into every rank's process, and `forward` returns the full y on
+    every rank.  blob: the full pre-pack blob (every rank repacks its own rows)."""
+
+    def __init__(self, blob, max_m, group=None, stream=None):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from . import binding as mb
+        self.mb = mb
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        n, k, _, _ = mb.blob_info(blob)
+        assert n % (32 * self.world) == 0, "equal shards of whole 32-row panels"
+        self.n, self.k, self.nl, self.max_m = n, k, n // self.world, max_m
+        self.weights = mb.W4A32Weights.from_blob(blob, row_begin=self.rank * self.nl, row_count=self.nl)
+        # the communicator exists after the first collective of the group
+        dist.all_reduce(torch.zeros(1, device="cuda"), group=group)
+        torch.cuda.synchronize()
+        h = C.c_void_p()
+        mb._check(mb.lib().mllmb200_w4a32_tp_init(self.world, self.rank, C.c_void_p(nccl_comm_ptr(group)), C.byref(h)), "tp_init")
+        self.handle = h
+        y = C.c_void_p()
+        mb._check(mb.lib().mllmb200_w4a32_tp_alloc_output(h, max_m * n * 4, C.byref(y), mb._stream_ptr(stream)), "tp_alloc_output")
+        self._y_ptr = y.value
+        self.ws = torch.empty(mb.workspace_size(max_m, k), dtype=torch.uint8, device="cuda")
+
+    def output(self, m):
+        """The library's output buffer viewed as a [m, n] tensor (no copy)."""
+        import torch
+        return torch.as_tensor(_DevArray(self._y_ptr, (m, self.n)), device="cuda")
+
+    def forward(self, x, gather=GATHER_PEER_STORES, kernel=0, stream=None, pdl=False):
+        import ctypes as C
+        m = x.shape[0]
+        assert m <= self.max_m and x.shape[1] == self.k and x.stride(1) == 1
+        self.mb._check(self.mb.lib().mllmb200_w4a32_linear_forward_tp(
+            self.handle, x.data_ptr(), self.weights.tiled.data_ptr(), self.ws.data_ptr(), m, self.k, self.n, x.stride(0),
+            kernel | (0x100 if pdl else 0), gather, self.mb._stream_ptr(stream)), "linear_forward_tp")
+        return self.output(m)
+
+    def close(self):
+        if self.handle:
+            self.mb.lib().mllmb200_w4a32_tp_destroy(self.handle)
+            self.handle = None
