@@ -736,7 +736,12 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
         dec.set_norm(1, l, np.ones(cfg["hidden"], np.float32))
     dec.set_norm(2, 0, np.ones(cfg["hidden"], np.float32))
     emb = torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen)
-    head = (torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen) * 0.02).to(torch.float16)
+    # lm_head = a row permutation of the embedding table (x 0.02): the largest logit then belongs to the row that
+    # matches the current token's embedding in the residual stream, so greedy decoding walks the permutation instead
+    # of collapsing onto one token as a fully random head does (`distinct_tokens` below)
+    perm = torch.randperm(cfg["vocab"], device="cuda", generator=gen)
+    head = (emb[perm] * 0.02).to(torch.float16)
+    del perm
     dec.set_tables(emb, head)
     host_prompt = np.random.default_rng(7).integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     ds = dec.stream()
@@ -824,8 +829,79 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
         out["cpu_reference_linears_only_tokens_per_s"] = 1e3 / (cpu_ms_per_layer * LAYERS)
         out["cpu_note"] = ("upper bound for the host-CPU reference: only the 28x7 linears of a step, timed with the "
                            "reference X86 Q4_K x Q8_K kernels; attention, norms and lm_head not included")
+    if not args.no_batched_decode:
+        try:
+            out["batched"] = run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind)
+        except Exception as ex:  # e.g. out of memory on a shared device: the batch-1 numbers stand
+            out["batched"] = {"error": str(ex)[:200]}
     dec.close()
     del emb, head
+    return out
+
+
+def run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind):
+    """BASELINE config 3: 64 concurrent sequences on the same weights, every quantized linear at M = 64.  Each
+    sequence is prefilled with 512 positions - 256 synthetic vision-patch embeddings (~N(0,1), width 1536) followed by
+    256 looked-up text tokens - then all decode together up to a 1024-token context.  Timed: device time of the
+    greedy steps at the start (context 512) and at the end (context ~1000) of that range."""
+    B, ctx_end, steps_t = args.batch_sequences, cfg["max_ctx"], args.batch_timed_steps
+    n_vis, n_txt = 256, 256
+    bd = mb.Qwen2BatchDecoder(dec, B)
+    ds = dec.stream()
+    rng = np.random.default_rng(11)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record(ds)
+    for b in range(B):
+        vis = torch.randn((n_vis, cfg["hidden"]), device="cuda", generator=gen)
+        txt = emb[torch.from_numpy(rng.integers(0, cfg["vocab"], n_txt)).cuda()]
+        bd.prefill(b, embeds=torch.cat([vis, txt]).contiguous())
+    ev[1].record(ds)
+    ds.synchronize()
+    prefill_ms = ev[0].elapsed_time(ev[1])
+    n0 = n_vis + n_txt
+    bd.decode(2)  # builds the step graph
+    ds.synchronize()
+    mb.check_device_status(ds)
+
+    def timed(steps):
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(ds)
+        bd.decode(steps)
+        b_.record(ds)
+        ds.synchronize()
+        return a.elapsed_time(b_) / steps
+
+    ms_start = timed(steps_t)
+    done = 2 + steps_t
+    room = ctx_end - 1 - n0 - done - steps_t
+    if room > 0:
+        bd.decode(room)  # untimed: walk to the end of the context
+        done += room
+    ctx_late = n0 + done
+    ms_end = timed(steps_t)
+    done += steps_t
+    mb.check_device_status(ds)
+    toks = np.stack([bd.generated(b, done) for b in range(B)])
+    lin = LAYERS * sum(algorithmic_bytes(B, k, n, hb) for _, k, n, hb in LINEARS)
+    head_b = cfg["vocab"] * cfg["hidden"] * 2
+
+    def step_bytes(ctx):
+        return lin + head_b + LAYERS * B * 2 * cfg["kv_heads"] * cfg["head_dim"] * 4 * ctx
+
+    def entry(ms, ctx):
+        by = step_bytes(ctx)
+        return {"context": int(ctx), "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "bytes_per_step": by,
+                "GBs": by / (ms * 1e-3) / 1e9, "frac_hbm": by / (ms * 1e-3) / 1e9 / hbm_peak}
+
+    out = {"config": f"BASELINE config 3: {B} sequences x {ctx_end}-token context on the Qwen2-1.5B language tower, prefill of "
+                     f"{n_vis} vision-patch embeddings + {n_txt} text tokens per sequence, fp32 KV cache, every linear at M = {B}",
+           "prefill_ms_all_sequences": prefill_ms, "prefill_tokens_per_s": B * n0 / (prefill_ms * 1e-3),
+           "at_start": entry(ms_start, n0 + 2 + steps_t / 2), "at_end": entry(ms_end, ctx_late + steps_t / 2),
+           "timed_steps": steps_t, "peak_kind": f"of {peak_kind}",
+           "distinct_tokens_per_sequence_min": int(min(len(set(r.tolist())) for r in toks)),
+           "sequences_differ": bool(len({tuple(r.tolist()) for r in toks}) > 1),
+           "bytes_note": "per step: the 196 linears at M = 64 (weights once), fp16 lm_head once, every sequence's K and V rows once"}
+    bd.close()
     return out
 
 
@@ -1105,6 +1181,9 @@ def main():
     ap.add_argument("--decoder-mode", default="both", choices=["both", "persistent", "graph"])
     ap.add_argument("--decoder-reps", type=int, default=3, help="timed repetitions of prefill + 128 steps")
     ap.add_argument("--no-decoder", action="store_true", help="skip the whole-model prefill + decode section")
+    ap.add_argument("--no-batched-decode", action="store_true", help="skip the 64-sequence batched decode of the decoder section")
+    ap.add_argument("--batch-sequences", type=int, default=64, help="sequences of the batched decode section (BASELINE config 3: 64)")
+    ap.add_argument("--batch-timed-steps", type=int, default=16, help="timed greedy steps at either end of the batched decode")
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run one decoder layer's seven linears at M=512 once and exit (small target for ncu)")

@@ -292,8 +292,8 @@ MLLMB200_API int mllmb200_w4a16_linear_forward_grouped(const void* x_dev, int x_
 /* ------------------------------------------------------------------------------------------
  * Decoder: the Qwen2-architecture language model whose linears are the W4A32 op above
  * (reference project: mllm/Models/ds_qwen2/modeling_ds_qwen2.hpp:47-54,106-155,175-215, greedy loop
- * mllm/Models/AutoLLM.hpp:39-105).  Batch 1, fp32 activations and KV cache, fp16 lm_head, greedy
- * sampling on the device.  A decode step is one CUDA graph replay; the position and the current
+ * mllm/Models/AutoLLM.hpp:39-105).  Batch 1 (the batched form follows below), fp32 activations and KV cache,
+ * fp16 lm_head, greedy sampling on the device.  A decode step is one CUDA graph replay; the position and the current
  * token live in device memory.  All calls are asynchronous on the decoder's own stream except
  * set_* (which synchronize it) and read.
  * ------------------------------------------------------------------------------------------ */
@@ -340,6 +340,29 @@ MLLMB200_API int mllmb200_qwen2_set_profiling(void* handle, int on);
 MLLMB200_API int mllmb200_qwen2_phase_cycles(void* handle, long long* out, int capacity, int* nctas, int* stamps);
 /* The decoder's CUDA stream (cudaStream_t), for event timing. */
 MLLMB200_API void* mllmb200_qwen2_stream(void* handle);
+
+/* Batched greedy decode: `batch` sequences, each with its own fp32 KV cache and position, advance one token per
+ * step together, so every quantized linear of a step runs at M = batch.  No counterpart in the reference, whose
+ * KV cache asserts a batch of one (mllm/Backends/Arm/Ops/KVCacheOp.cpp:107,156): the contract is that sequence b
+ * yields the tokens the batch-1 decoder yields on sequence b alone (its forward: modeling_ds_qwen2.hpp:106-155,
+ * cache append KVCacheOp.cpp:15-72, greedy loop AutoLLM.hpp:39-105).  The batch object borrows weights, norms,
+ * tables, context length and stream of `decoder` (a handle of mllmb200_qwen2_create with everything set; keep it
+ * alive, and do not run it while batch calls are in flight: prefill shares its activation buffers).
+ * Device memory: 2 * layers * batch * kv_heads * max_ctx * head_dim * 4 bytes of cache plus activations. */
+MLLMB200_API int mllmb200_qwen2_batch_create(void* decoder, int batch, void** handle);
+MLLMB200_API void mllmb200_qwen2_batch_destroy(void* handle);
+/* Kernel policy of the M = batch linears: 0 (default) exact int32 group sums, 4 / 5 as in linear_forward_ex. */
+MLLMB200_API int mllmb200_qwen2_batch_set_policy(void* handle, int policy);
+/* Prefills sequence `seq` from an empty cache and samples its first token.  Exactly one of tokens_dev (int32 [n])
+ * and embeds_dev (fp32 [n, hidden]: rows that already are embeddings, e.g. vision-patch embeddings mixed with
+ * looked-up text tokens) is non-NULL.  Prompts of different sequences may differ in length. */
+MLLMB200_API int mllmb200_qwen2_batch_prefill(void* handle, int seq, const int* tokens_dev, const float* embeds_dev, int n);
+/* `steps` greedy steps for all sequences together: one CUDA graph replay per step.  Every sequence needs a
+ * prefill first and position + steps <= max_ctx. */
+MLLMB200_API int mllmb200_qwen2_batch_decode(void* handle, int steps);
+/* As mllmb200_qwen2_read, for sequence `seq`. */
+MLLMB200_API int mllmb200_qwen2_batch_read(void* handle, int seq, int first, int count, int* tokens_out, int* pos_out,
+                                           float* logits_out);
 
 /* ------------------------------------------------------------------------------------------
  * Tensor parallelism over the GPUs of one node, one process per GPU (no counterpart in the reference, whose

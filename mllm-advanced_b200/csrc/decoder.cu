@@ -162,6 +162,74 @@ int enqueue_decode_step(Decoder* d) {
 }
 
 }  // namespace
+
+int check_ready(Decoder* d) {
+  if (!d->embedding || !d->lm_head) return MLLMB200_INVALID_ARG;
+  for (auto& L : d->layers)
+    for (int i = 0; i < kNumLinears; ++i)
+      if (!L.w[i]) return MLLMB200_INVALID_ARG;
+  return MLLMB200_OK;
+}
+
+// The prompt pass of the batch-1 decoder, writing keys / values into the given per-layer caches
+// ([kv_heads][max_ctx][D] each) and the sampled token and position into the given words: the decoder's own for
+// mllmb200_qwen2_prefill, a sequence's for the batched decoder (decoder_batch.cu).  Exactly one of tokens_dev
+// (int32 [n]) and embeds_dev (fp32 [n, hidden], rows that are already embeddings) is given.
+int prefill_into(Decoder* d, const int* tokens_dev, const float* embeds_dev, int n, float* const* cache_k,
+                 float* const* cache_v, int* pos, int* token, int* next, int* history) {
+  if (!d || (tokens_dev == nullptr) == (embeds_dev == nullptr) || n <= 0 || n >= d->cfg.max_ctx) return MLLMB200_INVALID_ARG;
+  DEC_ST(check_ready(d));
+  const auto& c = d->cfg;
+  cudaStream_t s = d->stream;
+  const int H = c.hidden, QD = c.q_heads * c.head_dim, KD = c.kv_heads * c.head_dim, I = c.inter;
+  if (tokens_dev)
+    embedding_kernel<<<n, 256, 0, s>>>(tokens_dev, d->embedding, H, d->h);
+  else
+    DEC_CHECK(cudaMemcpyAsync(d->h, embeds_dev, (size_t)n * H * sizeof(float), cudaMemcpyDeviceToDevice, s));
+  for (int l = 0; l < c.layers; ++l) {
+    const Layer& L = d->layers[l];
+    add_rmsnorm_quant_kernel<<<n, 256, 0, s>>>(d->h, l == 0 ? nullptr : d->down, L.ln1, c.eps, H, d->h, d->xn, nullptr,
+                                               nullptr, 0);
+    {  // q, k, v share one quantization of the normalized rows
+      const void* tw[3] = {L.w[kQ], L.w[kK], L.w[kV]};
+      float* ty[3] = {d->q, d->k, d->v};
+      const int tn[3] = {QD, KD, KD};
+      DEC_ST(mllmb200_w4a32_linear_forward_grouped(d->xn, n, H, H, 3, tw, ty, tn, tn, d->ws, 5, s));
+    }
+    rope_kv_append_kernel<<<dim3(c.kv_heads, n), c.head_dim, 0, s>>>(d->k, d->v, KD, d->sin_t, d->cos_t, d->zero, c.max_ctx,
+                                                                    cache_k[l], cache_v[l]);
+    {
+      const dim3 grid((n + 7) / 8, c.kv_heads);
+      const size_t smem = attention_prefill_smem_bytes(c.head_dim);
+      if (c.head_dim == 128)
+        attention_prefill_kernel<128><<<grid, 256, smem, s>>>(d->q, QD, n, d->sin_t, d->cos_t, d->zero, c.max_ctx,
+                                                               c.q_heads / c.kv_heads, cache_k[l], cache_v[l], d->attn, QD);
+      else
+        attention_prefill_kernel<64><<<grid, 256, smem, s>>>(d->q, QD, n, d->sin_t, d->cos_t, d->zero, c.max_ctx,
+                                                              c.q_heads / c.kv_heads, cache_k[l], cache_v[l], d->attn, QD);
+    }
+    DEC_ST(mllmb200_w4a32_linear_forward_ex(d->attn, L.w[kO], d->o, d->ws, n, QD, H, QD, H, 5, s));
+    add_rmsnorm_quant_kernel<<<n, 256, 0, s>>>(d->h, d->o, L.ln2, c.eps, H, d->h, d->xn, nullptr, nullptr, 0);
+    {  // gate and up likewise
+      const void* tw[2] = {L.w[kGate], L.w[kUp]};
+      float* ty[2] = {d->gate, d->up};
+      const int tn[2] = {I, I};
+      DEC_ST(mllmb200_w4a32_linear_forward_grouped(d->xn, n, H, H, 2, tw, ty, tn, tn, d->ws, 5, s));
+    }
+    silu_mul_quant_kernel<<<n, 512, (size_t)I * sizeof(float), s>>>(d->gate, d->up, I, d->act, nullptr, nullptr, 0);
+    DEC_ST(mllmb200_w4a32_linear_forward_ex(d->act, L.w[kDown], d->down, d->ws, n, I, H, I, H, 5, s));
+  }
+  // only the last position feeds the sampler (the reference computes all rows and reads the last)
+  const size_t last = (size_t)(n - 1) * H;
+  add_rmsnorm_quant_kernel<<<1, 256, 0, s>>>(d->h + last, d->down + last, d->final_norm, c.eps, H, nullptr, d->xn, nullptr,
+                                             nullptr, 0);
+  lm_head_f16_kernel<<<kHeadCtas, 256, H * sizeof(float), s>>>(d->xn, d->lm_head, H, c.vocab, d->logits, d->best);
+  set_int_kernel<<<1, 1, 0, s>>>(pos, n - 1);
+  sample_advance_kernel<<<1, 32, 0, s>>>(d->best, kHeadCtas, pos, token, next, history, c.max_ctx);
+  DEC_CHECK(cudaGetLastError());
+  return MLLMB200_OK;
+}
+
 }  // namespace mllmb200
 
 #include "decoder_api.inc"

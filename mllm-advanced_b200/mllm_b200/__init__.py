@@ -10,4 +10,4 @@ from .binding import (  # noqa: F401
     MllmB200Error, lib, lib_path, status_str, prepack_size, quant_prepack, prepack_from_quantized, blob_info,
     blob_sections, tiled_size, workspace_size, W4A32Weights, linear_forward, linear_forward_grouped, quant_activations, check_device_status, conv3d_forward,
 )
-from .decoder import Qwen2Decoder, Qwen2Config, QWEN2_1P5B, LINEAR_NAMES, plan_check, DECODE_AUTO, DECODE_GRAPH, DECODE_PERSISTENT  # noqa: F401,E402
+from .decoder import Qwen2Decoder, Qwen2BatchDecoder, Qwen2Config, QWEN2_1P5B, LINEAR_NAMES, plan_check, DECODE_AUTO, DECODE_GRAPH, DECODE_PERSISTENT  # noqa: F401,E402

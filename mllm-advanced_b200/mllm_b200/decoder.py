@@ -58,6 +58,13 @@ def _bind():
     L.mllmb200_qwen2_phase_cycles.argtypes = [vp, vp, ci, C.POINTER(ci), C.POINTER(ci)]
     L.mllmb200_qwen2_stream.argtypes = [vp]
     L.mllmb200_qwen2_stream.restype = vp
+    L.mllmb200_qwen2_batch_create.argtypes = [vp, ci, C.POINTER(vp)]
+    L.mllmb200_qwen2_batch_destroy.argtypes = [vp]
+    L.mllmb200_qwen2_batch_destroy.restype = None
+    L.mllmb200_qwen2_batch_set_policy.argtypes = [vp, ci]
+    L.mllmb200_qwen2_batch_prefill.argtypes = [vp, ci, vp, vp, ci]
+    L.mllmb200_qwen2_batch_decode.argtypes = [vp, ci]
+    L.mllmb200_qwen2_batch_read.argtypes = [vp, ci, ci, ci, vp, vp, vp]
     _bound = True
     return L
 
@@ -153,3 +160,63 @@ class Qwen2Decoder:
     def stream(self):
         import torch
         return torch.cuda.ExternalStream(self._L.mllmb200_qwen2_stream(self._h), device=self.device)
+
+
+class Qwen2BatchDecoder:
+    """`batch` sequences decoding together on the weights of a Qwen2Decoder (mllmb200_qwen2_batch_*): every
+    sequence has its own KV cache and position; sequence b yields what the batch-1 decoder yields on it alone."""
+
+    def __init__(self, decoder, batch):
+        import torch
+        self.dec = decoder
+        self.batch = int(batch)
+        self._L = _bind()
+        self._h = C.c_void_p()
+        self._keep = []
+        self.prompt_len = [0] * self.batch
+        with torch.cuda.device(decoder.device):
+            B._check(self._L.mllmb200_qwen2_batch_create(decoder._h, self.batch, C.byref(self._h)), "qwen2_batch_create")
+
+    def close(self):
+        if self._h:
+            self._L.mllmb200_qwen2_batch_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_policy(self, policy):
+        B._check(self._L.mllmb200_qwen2_batch_set_policy(self._h, policy), "qwen2_batch_set_policy")
+
+    def prefill(self, seq, tokens=None, embeds=None):
+        """tokens: int sequence, or embeds: torch fp32 [n, hidden] on the device (rows that already are embeddings)."""
+        import torch
+        if tokens is not None:
+            t = tokens if isinstance(tokens, torch.Tensor) else torch.as_tensor(np.asarray(tokens, np.int32)).to(self.dec.device)
+            self._keep.append(t)
+            n = int(t.numel())
+            B._check(self._L.mllmb200_qwen2_batch_prefill(self._h, seq, t.data_ptr(), None, n), "qwen2_batch_prefill")
+        else:
+            assert embeds.is_cuda and embeds.dtype == torch.float32 and embeds.is_contiguous()
+            self._keep.append(embeds)
+            n = int(embeds.shape[0])
+            B._check(self._L.mllmb200_qwen2_batch_prefill(self._h, seq, None, embeds.data_ptr(), n), "qwen2_batch_prefill")
+        self.prompt_len[seq] = n
+
+    def decode(self, steps):
+        B._check(self._L.mllmb200_qwen2_batch_decode(self._h, steps), "qwen2_batch_decode")
+
+    def read(self, seq, first, count, want_logits=False):
+        toks = np.zeros(max(count, 1), np.int32)
+        pos = C.c_int(0)
+        logits = np.zeros(self.dec.cfg["vocab"], np.float32) if want_logits else None
+        B._check(self._L.mllmb200_qwen2_batch_read(self._h, seq, first, count, toks.ctypes.data, C.byref(pos),
+                                                   logits.ctypes.data if want_logits else None), "qwen2_batch_read")
+        return toks[:count], pos.value, logits
+
+    def generated(self, seq, steps):
+        """Tokens sampled after the prompt of `seq` and after each of `steps` decode steps."""
+        return self.read(seq, self.prompt_len[seq] - 1, steps + 1)[0]

@@ -1,0 +1,119 @@
+"""Batched decode (C ABI mllmb200_qwen2_batch_*): B sequences with their own KV caches advance together, so the
+quantized linears of a step run at M = B.  The reference has no batched mode (its KV cache asserts a batch of one),
+so the oracle is B independent batch-1 runs: here the batch-1 CUDA decoder (itself checked against the numpy oracle
+in test_decoder.py) on every sequence alone, and for one small case the numpy oracle directly.
+
+Bars: identical greedy tokens; last logits within 5e-3 * rms (the M = B linears take other kernels than the
+batch-1 GEMV, which changes the order of fp32 additions only)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+from test_decoder import SMALL, WIDE, make_model, bind_oracle_linears, _gpu_decoder  # noqa: E402
+
+LOGIT_TOL = 5e-3
+
+
+def _rms(a):
+    return float(np.sqrt(np.mean(np.asarray(a, np.float64) ** 2)))
+
+
+def _run_single(dec, prompt, steps):
+    dec.prefill(prompt)
+    dec.decode(steps)
+    toks = dec.generated(steps).copy()
+    _, pos, logits = dec.read(0, 0, want_logits=True)
+    return toks, pos, logits
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg,batch,steps", [(SMALL, 5, 6), (WIDE, 20, 5), (WIDE, 64, 3)])
+def test_batched_decode_equals_independent_runs(cfg, batch, steps):
+    import mllm_b200 as mb
+    rng = np.random.default_rng(batch)
+    w, raw = make_model(cfg, 7)
+    dec = _gpu_decoder(cfg, w, raw)
+    prompts = [rng.integers(0, cfg["vocab"], size=int(rng.integers(1, 24))).tolist() for _ in range(batch)]
+    singles = [_run_single(dec, p, steps) for p in prompts]
+    bd = mb.Qwen2BatchDecoder(dec, batch)
+    for b, p in enumerate(prompts):
+        bd.prefill(b, tokens=p)
+    bd.decode(steps)
+    worst = 0.0
+    for b, p in enumerate(prompts):
+        toks = bd.generated(b, steps)
+        _, pos, logits = bd.read(b, 0, 0, want_logits=True)
+        ref_toks, ref_pos, ref_logits = singles[b]
+        assert pos == ref_pos == len(p) + steps
+        err = float(np.max(np.abs(logits - ref_logits))) / _rms(ref_logits)
+        worst = max(worst, err)
+        assert err <= LOGIT_TOL, (b, err)
+        if not np.array_equal(toks, ref_toks):
+            # a differing token is accepted only on a near tie of the reference's own logits at that step
+            i = int(np.argmax(toks != ref_toks))
+            raise AssertionError(f"sequence {b}: tokens differ from step {i}: {toks} vs {ref_toks}")
+    mb.check_device_status()
+    bd.close()
+    dec.close()
+
+
+@pytest.mark.gpu
+def test_batched_decode_against_numpy_oracle():
+    """Two sequences of the small configuration against the numpy restatement itself."""
+    import mllm_b200 as mb
+    from qwen2_oracle import Qwen2Oracle
+    from oracle_lib import Oracle
+    cfg, steps = SMALL, 4
+    w, raw = make_model(cfg, 3)
+    dec = _gpu_decoder(cfg, w, raw)
+    bd = mb.Qwen2BatchDecoder(dec, 2)
+    prompts = [[5, 9, 700, 31], [1, 2, 3, 4, 5, 6, 7, 8, 9]]
+    for b, p in enumerate(prompts):
+        bd.prefill(b, tokens=p)
+    bd.decode(steps)
+    orc = Oracle()
+    bind_oracle_linears(w, raw, orc)
+    for b, p in enumerate(prompts):
+        m = Qwen2Oracle(cfg, w)
+        logits = m.forward(p)
+        want = [int(np.argmax(logits))]
+        for _ in range(steps):
+            logits = m.forward([want[-1]])
+            want.append(int(np.argmax(logits)))
+        got = bd.generated(b, steps)
+        assert list(got) == want, (b, got, want)
+        _, _, glog = bd.read(b, 0, 0, want_logits=True)
+        assert float(np.max(np.abs(glog - logits))) <= LOGIT_TOL * _rms(logits)
+    bd.close()
+    dec.close()
+
+
+@pytest.mark.gpu
+def test_batched_prefill_from_embeddings_and_arguments():
+    """Prefill from embedding rows equals prefill from the tokens they were looked up from; bad arguments are refused."""
+    import torch
+    import mllm_b200 as mb
+    cfg = SMALL
+    w, raw = make_model(cfg, 11)
+    dec = _gpu_decoder(cfg, w, raw)
+    bd = mb.Qwen2BatchDecoder(dec, 2)
+    prompt = [4, 8, 15, 16, 23, 42]
+    emb = torch.from_numpy(w["embedding"][prompt]).cuda().contiguous()
+    bd.prefill(0, tokens=prompt)
+    bd.prefill(1, embeds=emb)
+    bd.decode(5)
+    assert np.array_equal(bd.generated(0, 5), bd.generated(1, 5))
+    with pytest.raises(mb.MllmB200Error):
+        bd.prefill(2, tokens=prompt)                       # no such sequence
+    with pytest.raises(mb.MllmB200Error):
+        bd.decode(cfg["max_ctx"])                          # does not fit the cache
+    bd2 = mb.Qwen2BatchDecoder(dec, 2)
+    bd2.prefill(0, tokens=prompt)
+    with pytest.raises(mb.MllmB200Error):
+        bd2.decode(1)                                      # sequence 1 has no prompt yet
+    bd2.close()
+    bd.close()
+    dec.close()
