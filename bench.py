@@ -567,30 +567,31 @@ def run_gpu(args):
         # and the call structure a decoder uses: (q,k,v) and (gate,up) through the grouped call, sharing one
         # quantization of their common input, with the fastest policy
         try:
-            def pf_grouped():
+            def pf_grouped(pdl=True):
                 for lw in layers[:n_pf_layers]:
                     mb.linear_forward_grouped(xp[1536], lw[0:3], outs=[yp[1536], yp[256], yp256b], workspace=ws, stream=stream,
-                                              policy=mb.KERNEL_FASTEST)
-                    mb.linear_forward(xp[1536], lw[3], out=yp[1536], workspace=ws, stream=stream, kernel=mb.KERNEL_FASTEST)
+                                              policy=mb.KERNEL_FASTEST, pdl=pdl)
+                    mb.linear_forward(xp[1536], lw[3], out=yp[1536], workspace=ws, stream=stream, kernel=mb.KERNEL_FASTEST, pdl=pdl)
                     mb.linear_forward_grouped(xp[1536], lw[4:6], outs=[yp[8960], yp8960b], workspace=ws, stream=stream,
-                                              policy=mb.KERNEL_FASTEST)
-                    mb.linear_forward(xp[8960], lw[6], out=yp[1536], workspace=ws, stream=stream, kernel=mb.KERNEL_FASTEST)
+                                              policy=mb.KERNEL_FASTEST, pdl=pdl)
+                    mb.linear_forward(xp[8960], lw[6], out=yp[1536], workspace=ws, stream=stream, kernel=mb.KERNEL_FASTEST, pdl=pdl)
             yp256b = torch.empty((PREFILL_M, 256), device="cuda")
             yp8960b = torch.empty((PREFILL_M, 8960), device="cuda")
             with torch.cuda.stream(stream):
                 pf_grouped()
             stream.synchronize()
-            with torch.cuda.stream(stream):
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for _ in range(3):
-                    pf_grouped()
-                e1.record(stream)
-            stream.synchronize()
-            ms_v = e0.elapsed_time(e1) / 3
+            mb.check_device_status(stream)
+            # one CUDA graph of the whole pass (8 launches per layer, programmatic dependent launch between them)
+            gpf = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gpf, stream=stream):
+                pf_grouped()
+            for _ in range(2):
+                gpf.replay()
+            ms_v = event_time_ms(torch, gpf.replay, 5)
+            del gpf
             line["prefill_fastest_grouped"] = {"M": PREFILL_M, "layers": n_pf_layers, "ms": ms_v,
                                                "tflops": flops / (ms_v * 1e-3) / 1e12, "unit": "TOP/s (2*M*N*K)",
-                                               "kernel": "fastest policy, (q,k,v) and (gate,up) as grouped calls (shared quantization)",
+                                               "kernel": "fastest policy, (q,k,v) and (gate,up) as grouped calls (shared quantization); CUDA graph, programmatic dependent launch",
                                                "frac_of_bf16_peak": flops / (ms_v * 1e-3) / 1e12 / tensor_peak,
                                                "peak_kind": f"of {peak_kind}"}
             mb.check_device_status()

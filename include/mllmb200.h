@@ -132,8 +132,11 @@ MLLMB200_API int mllmb200_w4a32_linear_forward(const float* x_dev, const void* t
  * scales folded into an fp16 weight operand - exact for bf16-encoded scales, rounded to fp16's 11 bits
  * (relative error <= 2^-11 per weight) for MLLMB200_SCALE_FP16 - fp32 accumulation over all of K in
  * tensor memory; same 1e-3*rms bound; auto never picks it), 5 fastest: kernel 4 for M >= 128, else auto,
- * 6 the two-launch GEMV (activation-quantization kernel + one-shot GEMV), kept for comparison.
- * OR 0x100 into `kernel` to allow programmatic dependent launch for the GEMV kernels: the kernel then
+ * 6 the two-launch GEMV (activation-quantization kernel + one-shot GEMV), kept for comparison,
+ * 7 streaming tensor-core GEMM for small batches (M <= 64; what auto picks for 5 <= M <= 64): the weight cells are
+ * spread over all SMs as in the GEMV, the per-group integer products run as mma.sync u8 x s8 (exact int32 group
+ * sums, as the reference), clusters split K where the quantized activations of a whole row do not fit one CTA.
+ * OR 0x100 into `kernel` to allow programmatic dependent launch (kernels 1, 4, 5, 6, 7): the kernel then
  * requests its (constant) weights while the previous kernel of the stream still runs and reads x only
  * after that kernel has completed. */
 MLLMB200_API int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, float* y_dev,

@@ -6,7 +6,7 @@ NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 OUT="$HERE/lib"
 mkdir -p "$OUT"
 SRC=("$HERE"/csrc/host_pack.cpp "$HERE"/csrc/c_api.cu "$HERE"/csrc/repack.cu "$HERE"/csrc/act_quant.cu
-     "$HERE"/csrc/gemv.cu "$HERE"/csrc/gemv_stream.cu "$HERE"/csrc/gemm_simt.cu "$HERE"/csrc/gemm_tc.cu "$HERE"/csrc/gemm_tcf16.cu
+     "$HERE"/csrc/gemv.cu "$HERE"/csrc/gemv_stream.cu "$HERE"/csrc/gemm_stream.cu "$HERE"/csrc/gemm_simt.cu "$HERE"/csrc/gemm_tc.cu "$HERE"/csrc/gemm_tcf16.cu
      "$HERE"/csrc/decoder_kernels.cu "$HERE"/csrc/decoder_attn.cu "$HERE"/csrc/decoder.cu "$HERE"/csrc/decoder_batch.cu "$HERE"/csrc/decoder_persistent.cu "$HERE"/csrc/conv3d.cu
      "$HERE"/csrc/host_pack_a16.cpp "$HERE"/csrc/w4a16.cu "$HERE"/csrc/c_api_a16.cu "$HERE"/csrc/tp.cu)
 EXTRA=()

@@ -254,8 +254,14 @@ constexpr int kF16RowsPerCta = 4;   // rows 4i .. 4i+3 sit side by side in a blo
 constexpr int kF16WarpsPerRow = 8;
 __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_quant_blocks_f16_kernel(
     const float* __restrict__ x, int m_total, int k, int ldx, int num_groups, int m8_pad, uint8_t* __restrict__ blocks,
-    float2* __restrict__ hdr) {
+    float2* __restrict__ hdr, int use_pdl) {
   __shared__ float s_mm[kF16RowsPerCta][kF16WarpsPerRow][2];
+  if (use_pdl) {
+    // x may be the previous kernel's output, and that kernel may still be reading the blocks this one overwrites:
+    // nothing happens before it has finished; the kernel behind this one may set itself up meanwhile
+    pdl_launch_dependents();
+    pdl_wait_prior();
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = warp & (kF16RowsPerCta - 1), part = warp / kF16RowsPerCta;
   const int m = blockIdx.x * kF16RowsPerCta + r;
@@ -329,11 +335,20 @@ __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_qua
 }
 
 cudaError_t launch_act_quant_blocks_f16(const float* x, int m, int m_pad, int k, int ldx, uint8_t* blocks, float2* hdr,
-                                        cudaStream_t stream) {
+                                        cudaStream_t stream, int use_pdl) {
   const int num_groups = (k + kGroup - 1) / kGroup;
-  act_quant_blocks_f16_kernel<<<m_pad / kF16RowsPerCta, kF16RowsPerCta * kF16WarpsPerRow * 32, 0, stream>>>(
-      x, m, k, ldx, num_groups, m_pad / 8, blocks, hdr);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(m_pad / kF16RowsPerCta), 1, 1);
+  cfg.blockDim = dim3(kF16RowsPerCta * kF16WarpsPerRow * 32, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  if (use_pdl) {
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, act_quant_blocks_f16_kernel, x, m, k, ldx, num_groups, m_pad / 8, blocks, hdr, use_pdl);
 }
 
 // m8_pad == 0: 48-byte records; m8_pad > 0: canonical 256-byte blocks with m8_pad blocks per K-group.

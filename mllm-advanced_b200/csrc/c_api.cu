@@ -36,12 +36,19 @@ bool w4a32_gemm_tcf16_supported(int m, int k, int n);
 bool w4a32_gemm_tcf16_preferred(int m, int k, int n);
 int w4a32_gemm_tcf16_m_pad(int m, int n);
 int w4a32_gemm_tcf16_m_pad_max(int m);
-cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t);
-cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t);
+cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t, int use_pdl);
+cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t, int use_pdl = 0);
 int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n);
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
                                             const int*, const int*, cudaStream_t, int num_peers = 0,
-                                            float* const* y_peers = nullptr);
+                                            float* const* y_peers = nullptr, int use_pdl = 0);
+
+bool w4a32_gemm_stream_supported(int m, int k, int count, const int* n);
+size_t w4a32_gemm_stream_act_bytes(int m, int k);
+cudaError_t launch_act_quant_mma(const float*, int, int, int, uint8_t*, float2*, int, cudaStream_t);
+cudaError_t launch_w4a32_gemm_stream(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
+                                     const int*, const int*, int, cudaStream_t);
+constexpr int kStreamGemmMinM = 5, kStreamGemmMaxM = 64;  // batch sizes the streaming tensor-core GEMM takes by default
 
 static thread_local int t_last_cuda_error = 0;
 static int cuda_fail(cudaError_t e) {
@@ -58,7 +65,10 @@ static inline size_t ws_rec_bytes(int m, int k) {
   const size_t blk = w4a32_gemm_tc_supported(m, k, 1) ? (size_t)w4a32_gemm_tc_m_pad(m) * blob_num_blocks(k) * 32 : 0;
   // fp16 operand blocks of the fp16 tensor-core path (64 bytes per row and K-group, rows padded to its widest tile)
   const size_t blk16 = w4a32_gemm_tcf16_supported(m, k, 1) ? (size_t)w4a32_gemm_tcf16_m_pad_max(m) * blob_num_blocks(k) * 64 : 0;
-  const size_t big = rec > blk ? rec : blk;
+  // activation blocks of the streaming small-batch GEMM (36 bytes per row and K-group, rows padded to 8)
+  const size_t mma = m <= kStreamGemmMaxM ? w4a32_gemm_stream_act_bytes(m, k) : 0;
+  size_t big = rec > blk ? rec : blk;
+  big = big > mma ? big : mma;
   return align_up(big > blk16 ? big : blk16, 256);
 }
 size_t w4a32_ws_rec_bytes(int m, int k) { return ws_rec_bytes(m, k); }  // for tp.cu
@@ -167,6 +177,7 @@ int mllmb200_w4a32_quant_activations(const float* x_dev, int M, int K, int ldx, 
 
 int mllmb200_w4a32_select_kernel(int M, int K, int N) {
   if (M > 0 && K > 0 && N > 0 && w4a32_gemv_stream_supported(M, 1, &K, &N)) return 1;
+  if (M >= kStreamGemmMinM && M <= kStreamGemmMaxM && K > 0 && N > 0 && w4a32_gemm_stream_supported(M, K, 1, &N)) return 7;
   if (w4a32_gemm_tc_supported(M, K, N)) return 3;
   return 2;
 }
@@ -191,7 +202,7 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int use_pdl = (kernel >> 8) & 1;
   kernel &= 0xFF;
-  if (kernel < 0 || kernel > 6) return MLLMB200_INVALID_ARG;
+  if (kernel < 0 || kernel > 7) return MLLMB200_INVALID_ARG;
   if (kernel == 5) kernel = w4a32_gemm_tcf16_preferred(M, K, N) ? 4 : 0;  // "fastest": fp16 path where it wins
   if (kernel == 0) kernel = mllmb200_w4a32_select_kernel(M, K, N);
   if (kernel == 1) {  // single launch: x is quantized inside the GEMV, no workspace
@@ -200,6 +211,15 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
         launch_w4a32_gemv_stream(1, &x_dev, &ldx, nullptr, nullptr, M, &K, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
     return e1 == cudaSuccess ? MLLMB200_OK : cuda_fail(e1);
   }
+  if (kernel == 7) {  // streaming tensor-core GEMM for small batches: its own activation layout
+    if (!w4a32_gemm_stream_supported(M, K, 1, &N)) return MLLMB200_UNSUPPORTED;
+    if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+    uint8_t* acts = static_cast<uint8_t*>(ws_dev);
+    float2* hdr7 = reinterpret_cast<float2*>(acts + ws_rec_bytes(M, K));
+    cudaError_t e7 = launch_act_quant_mma(x_dev, M, K, ldx, acts, hdr7, use_pdl, st);
+    if (e7 == cudaSuccess) e7 = launch_w4a32_gemm_stream(acts, hdr7, M, K, 1, &tiled_dev, &y_dev, &N, &ldy, use_pdl, st);
+    return e7 == cudaSuccess ? MLLMB200_OK : cuda_fail(e7);
+  }
   if (kernel == 6 && !w4a32_gemv_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   if (kernel == 3 && !w4a32_gemm_tc_supported(M, K, N)) return MLLMB200_UNSUPPORTED;
   if (kernel == 4) {  // fp16 tensor-core path: its own activation layout
@@ -207,8 +227,8 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
     if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
     uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
     float2* hdr16 = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
-    cudaError_t e16 = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N), K, ldx, blocks, hdr16, st);
-    if (e16 == cudaSuccess) e16 = launch_w4a32_gemm_tcf16(blocks, hdr16, tiled_dev, y_dev, M, K, N, ldy, st);
+    cudaError_t e16 = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N), K, ldx, blocks, hdr16, st, use_pdl);
+    if (e16 == cudaSuccess) e16 = launch_w4a32_gemm_tcf16(blocks, hdr16, tiled_dev, y_dev, M, K, N, ldy, st, use_pdl);
     return e16 == cudaSuccess ? MLLMB200_OK : cuda_fail(e16);
   }
   uint8_t* a_rec;
@@ -246,6 +266,17 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
                                                    (flags >> 8) & 1, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
   }
+  if (((flags & 0xFF) == 0 || (flags & 0xFF) == 5) && M >= kStreamGemmMinM && M <= kStreamGemmMaxM &&
+      w4a32_gemm_stream_supported(M, K, count, N)) {  // small batch: one quantization, ONE streaming tensor-core launch
+    if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
+    cudaStream_t st7 = static_cast<cudaStream_t>(stream);
+    uint8_t* acts = static_cast<uint8_t*>(ws_dev);
+    float2* hdr7 = reinterpret_cast<float2*>(acts + ws_rec_bytes(M, K));
+    const int pdl7 = (flags >> 8) & 1;
+    cudaError_t e7 = launch_act_quant_mma(x_dev, M, K, ldx, acts, hdr7, pdl7, st7);
+    if (e7 == cudaSuccess) e7 = launch_w4a32_gemm_stream(acts, hdr7, M, K, count, tiled_dev, y_dev, N, ldy, pdl7, st7);
+    return e7 == cudaSuccess ? MLLMB200_OK : cuda_fail(e7);
+  }
   bool gemv = (flags & 0xFF) == 6;  // the two-launch path (quantization kernel + one-shot GEMV), kept for comparison
   for (int i = 0; i < count && gemv; ++i) gemv = w4a32_gemv_supported(M, K, N[i]);
   if ((flags & 0xFF) == 6 && !gemv) return MLLMB200_UNSUPPORTED;
@@ -272,8 +303,10 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
       uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
       float2* hdr = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
       const int nt = w4a32_gemm_tcf16_tile_grouped(M, count, N);
-      cudaError_t e = launch_act_quant_blocks_f16(x_dev, M, (M + nt - 1) / nt * nt, K, ldx, blocks, hdr, st_grp);
-      if (e == cudaSuccess) e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, count, tiled_dev, y_dev, N, ldy, st_grp);
+      const int pdl = (flags >> 8) & 1;
+      cudaError_t e = launch_act_quant_blocks_f16(x_dev, M, (M + nt - 1) / nt * nt, K, ldx, blocks, hdr, st_grp, pdl);
+      if (e == cudaSuccess)
+        e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, count, tiled_dev, y_dev, N, ldy, st_grp, 0, nullptr, pdl);
       return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
     }
   }

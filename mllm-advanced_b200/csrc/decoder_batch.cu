@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "../../include/mllmb200.h"
@@ -105,93 +106,125 @@ __global__ void __launch_bounds__(kBatchCombineThreads) attn_combine_batched_ker
   }
 }
 
-// logits[b][v] = sum_k x[b][k] * W[v][k] for a tile of kLmRows activation rows (blockIdx.y) and the vocabulary rows
-// v = 4 * (blockIdx.x * 8 + warp) + {0..3}, stepping by 4 * 8 * gridDim.x: W fp16 [V, hidden], x fp32, fp32
-// accumulation.  A warp holds the 16-byte chunks of FOUR vocabulary rows in registers and runs every activation
-// row of the tile (fp32 in shared memory) past them, so a weight row is fetched once per tile of 16 activation
-// rows.  Per (b, v) the lane-to-chunk assignment, the order of the FMAs and the shuffle tree are those of
-// lm_head_f16_kernel: the logits are bit-identical to the batch-1 kernel's.  Each CTA also leaves, per activation
-// row, its largest logit and the index (lowest index on ties) in best[b][blockIdx.x].
-constexpr int kLmRows = 16;   // activation rows per CTA tile
-constexpr int kLmVocab = 4;   // vocabulary rows a warp keeps in registers
-__global__ void __launch_bounds__(256) lm_head_f16_batched_kernel(const float* __restrict__ x, int batch,
-                                                                  const __half* __restrict__ w, int hidden, int vocab,
-                                                                  float* __restrict__ logits, float2* __restrict__ best) {
-  extern __shared__ float s_x[];  // [kLmRows][hidden]
-  __shared__ float s_bv[kLmRows][8];
-  __shared__ int s_bi[kLmRows][8];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+// logits[b][v] = sum_k x[b][k] * W[v][k] for a tile of kLmRows activation rows (blockIdx.y), W fp16 [V, hidden], on
+// the tensor cores without giving up the fp32 activations: x = hi + lo with hi = fp16(x), lo = fp16(x - hi) (error
+// 2^-22 |x|), both halves in shared memory, every product w * hi and w * lo exact in the fp32 accumulator of
+// mma.sync.m16n8k16.  A warp owns tiles of 16 vocabulary rows; per 32 values of k a lane loads 16 bytes of W rows
+// g and g + 8 straight from global memory (k = 8 c .. 8 c + 7 of the step; the contraction index may be permuted
+// freely as long as both operands agree, so two instructions use the words {0, 1} and {2, 3} of what was loaded)
+// and, per 8 activation rows, 16 bytes of hi and of lo from shared memory for the same k.  Rows of the activation
+// tile are padded to 64 bytes past a multiple of 128, which makes those 16-byte loads conflict-free.
+// Each CTA also leaves, per activation row, its largest logit and the index (lowest index on ties) in
+// best[b][blockIdx.x].  hidden must be a multiple of 32.
+constexpr int kLmRows = 32;     // activation rows per CTA tile (4 column tiles of the instruction)
+constexpr int kLmWarps = 16;
+constexpr int kLmThreads = kLmWarps * 32;
+__host__ __device__ inline size_t lm_row_bytes(int hidden) { return (size_t)hidden * 2 + 64; }
+__host__ __device__ inline size_t lm_smem_bytes(int hidden) { return 2 * (size_t)kLmRows * lm_row_bytes(hidden); }
+
+__device__ __forceinline__ void lm_mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kLmThreads, 1) lm_head_f16_batched_kernel(const float* __restrict__ x, int batch,
+                                                                            const __half* __restrict__ w, int hidden,
+                                                                            int vocab, float* __restrict__ logits,
+                                                                            float2* __restrict__ best) {
+  extern __shared__ __align__(128) uint8_t lm_smem[];
+  __shared__ float s_bv[kLmRows][kLmWarps];
+  __shared__ int s_bi[kLmRows][kLmWarps];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int b0 = blockIdx.y * kLmRows;
   const int nb = min(kLmRows, batch - b0);
-  for (int i = threadIdx.x; i < kLmRows * hidden; i += blockDim.x) {
-    const int r = i / hidden;
-    s_x[i] = r < nb ? x[(size_t)(b0 + r) * hidden + (i - r * hidden)] : 0.0f;
+  const size_t row_bytes = lm_row_bytes(hidden);
+  uint8_t* s_hi = lm_smem;
+  uint8_t* s_lo = lm_smem + (size_t)kLmRows * row_bytes;
+  for (int i = tid; i < kLmRows * (hidden >> 1); i += kLmThreads) {  // two values per thread and trip
+    const int r = i / (hidden >> 1), k = (i - r * (hidden >> 1)) * 2;
+    float2 v = make_float2(0.0f, 0.0f);
+    if (r < nb) v = *reinterpret_cast<const float2*>(x + (size_t)(b0 + r) * hidden + k);
+    const __half2 hi = __floats2half2_rn(v.x, v.y);
+    const float2 hf = __half22float2(hi);
+    const __half2 lo = __floats2half2_rn(v.x - hf.x, v.y - hf.y);
+    *reinterpret_cast<__half2*>(s_hi + (size_t)r * row_bytes + (size_t)k * 2) = hi;
+    *reinterpret_cast<__half2*>(s_lo + (size_t)r * row_bytes + (size_t)k * 2) = lo;
   }
   __syncthreads();
-  float bv[kLmRows];
-  int bi[kLmRows];
+  float bv[8];
+  int bi[8];
 #pragma unroll
-  for (int r = 0; r < kLmRows; ++r) bv[r] = -3.402823466e+38f, bi[r] = 0x7fffffff;
-  const int chunks = hidden >> 3;
-  for (int v0 = kLmVocab * (blockIdx.x * 8 + warp); v0 < vocab; v0 += kLmVocab * 8 * gridDim.x) {
-    float acc[kLmVocab][kLmRows];
+  for (int i = 0; i < 8; ++i) bv[i] = -3.402823466e+38f, bi[i] = 0x7fffffff;
+  const int steps = hidden >> 5;  // 32 values of k per step
+  const uint32_t hi_s = (uint32_t)__cvta_generic_to_shared(s_hi) + (uint32_t)g * (uint32_t)row_bytes + (uint32_t)c * 16;
+  const uint32_t lo_s = hi_s + (uint32_t)((size_t)kLmRows * row_bytes);
+  for (int v0 = 16 * (blockIdx.x * kLmWarps + warp); v0 < vocab; v0 += 16 * kLmWarps * gridDim.x) {
+    float acc[4][4];
 #pragma unroll
-    for (int j = 0; j < kLmVocab; ++j)
+    for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+    // rows past the end of the vocabulary repeat its last row (their results are dropped)
+    const uint4* wa = reinterpret_cast<const uint4*>(w + (size_t)min(v0 + g, vocab - 1) * hidden) + c;
+    const uint4* wb = reinterpret_cast<const uint4*>(w + (size_t)min(v0 + g + 8, vocab - 1) * hidden) + c;
+#pragma unroll 4
+    for (int ss = 0; ss < steps; ++ss) {
+      const uint4 ra = wa[ss * 4], rb = wb[ss * 4];  // 16 bytes of either row: k = 32 ss + 8 c ..
 #pragma unroll
-      for (int r = 0; r < kLmRows; ++r) acc[j][r] = 0.0f;
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 pk[kLmVocab];
-#pragma unroll
-      for (int j = 0; j < kLmVocab; ++j)
-        pk[j] = v0 + j < vocab ? reinterpret_cast<const uint4*>(w + (size_t)(v0 + j) * hidden)[c] : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-      for (int r = 0; r < kLmRows; ++r) {
-        const float4 xa = *reinterpret_cast<const float4*>(s_x + (size_t)r * hidden + c * 8);
-        const float4 xb = *reinterpret_cast<const float4*>(s_x + (size_t)r * hidden + c * 8 + 4);
-        const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-        for (int j = 0; j < kLmVocab; ++j) {
-          const __half2* h2 = reinterpret_cast<const __half2*>(&pk[j]);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(h2[e]);
-            acc[j][r] = fmaf(f.x, xs[2 * e], acc[j][r]);
-            acc[j][r] = fmaf(f.y, xs[2 * e + 1], acc[j][r]);
-          }
-        }
+      for (int t = 0; t < 4; ++t) {
+        uint4 xh, xl;
+        const uint32_t off = (uint32_t)t * 8 * (uint32_t)row_bytes + (uint32_t)ss * 64;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(xh.x), "=r"(xh.y), "=r"(xh.z), "=r"(xh.w) : "r"(hi_s + off));
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(xl.x), "=r"(xl.y), "=r"(xl.z), "=r"(xl.w) : "r"(lo_s + off));
+        lm_mma_f16(acc[t], ra.x, rb.x, ra.y, rb.y, xh.x, xh.y);
+        lm_mma_f16(acc[t], ra.x, rb.x, ra.y, rb.y, xl.x, xl.y);
+        lm_mma_f16(acc[t], ra.z, rb.z, ra.w, rb.w, xh.z, xh.w);
+        lm_mma_f16(acc[t], ra.z, rb.z, ra.w, rb.w, xl.z, xl.w);
       }
     }
+    // lane (g, c): rows v0 + g and v0 + g + 8, activation rows 8 t + 2 c and 8 t + 2 c + 1
 #pragma unroll
-    for (int j = 0; j < kLmVocab; ++j) {
+    for (int t = 0; t < 4; ++t)
 #pragma unroll
-      for (int r = 0; r < kLmRows; ++r) {
-        float a = acc[j][r];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        const int v = v0 + j;
+      for (int i = 0; i < 4; ++i) {
+        const int v = v0 + g + (i >> 1) * 8, r = 8 * t + 2 * c + (i & 1);
         if (v < vocab && r < nb) {
-          if (lane == 0 && logits) logits[(size_t)(b0 + r) * vocab + v] = a;
-          if (a > bv[r]) {  // rows come in increasing order within a warp: a strict test keeps the lowest index
-            bv[r] = a;
-            bi[r] = v;
+          const float a = acc[t][i];
+          if (logits) logits[(size_t)(b0 + r) * vocab + v] = a;
+          const int slot = 2 * t + (i & 1);
+          if (a > bv[slot]) {  // this lane meets the rows of a column in increasing order: a strict test keeps the lowest index
+            bv[slot] = a;
+            bi[slot] = v;
           }
         }
       }
-    }
   }
-  if (lane == 0) {
+  // the eight lanes with the same c hold different vocabulary rows of the same activation rows
 #pragma unroll
-    for (int r = 0; r < kLmRows; ++r) {
-      s_bv[r][warp] = bv[r];
-      s_bi[r][warp] = bi[r];
+  for (int slot = 0; slot < 8; ++slot) {
+    float v = bv[slot];
+    int i = bi[slot];
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+      if (ov > v || (ov == v && oi < i)) {
+        v = ov;
+        i = oi;
+      }
+    }
+    if (g == 0) {
+      const int r = 8 * (slot >> 1) + 2 * c + (slot & 1);
+      s_bv[r][warp] = v;
+      s_bi[r][warp] = i;
     }
   }
   __syncthreads();
-  if (threadIdx.x < nb) {
-    const int r = threadIdx.x;
+  if (tid < nb) {
+    const int r = tid;
     float v = s_bv[r][0];
     int i = s_bi[r][0];
-    for (int k = 1; k < 8; ++k)
+    for (int k = 1; k < kLmWarps; ++k)
       if (s_bv[r][k] > v || (s_bv[r][k] == v && s_bi[r][k] < i)) {
         v = s_bv[r][k];
         i = s_bi[r][k];
@@ -234,7 +267,7 @@ __global__ void sample_advance_batched_kernel(const float2* __restrict__ best, i
 
 namespace {
 
-constexpr int kLmCtas = 148;  // vocabulary CTAs of the batched lm_head (x ceil(B / 16) activation tiles)
+constexpr int kLmCtas = 148;  // vocabulary CTAs of the batched lm_head (x ceil(B / 32) activation tiles)
 
 struct BatchDecoder {
   Decoder* base = nullptr;
@@ -244,6 +277,10 @@ struct BatchDecoder {
   float *h = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *o = nullptr;
   float *gate = nullptr, *up = nullptr, *act = nullptr, *down = nullptr, *logits = nullptr;
   float *part_o = nullptr, *part_ml = nullptr;
+  // context split of the decode attention: with many sequences the grid is full without fine splits, and a CTA's fixed
+  // cost (rotating the queries, the first cache round trip) is paid once per chunk - so chunks of about 128 positions
+  // for large batches, the batch-1 decoder's fine split for small ones
+  int attn_chunk = 32, attn_splits = 1;
   float2* best = nullptr;
   int *pos = nullptr, *token = nullptr, *history = nullptr, *scratch_next = nullptr;
   void* ws = nullptr;
@@ -292,36 +329,36 @@ int enqueue_batched_step(BatchDecoder* b) {
       const void* tw[3] = {L.w[kQ], L.w[kK], L.w[kV]};
       float* ty[3] = {b->q, b->k, b->v};
       const int tn[3] = {QD, KD, KD};
-      BD_ST(mllmb200_w4a32_linear_forward_grouped(b->xn, B, H, H, 3, tw, ty, tn, tn, b->ws, b->policy, s));
+      BD_ST(mllmb200_w4a32_linear_forward_grouped(b->xn, B, H, H, 3, tw, ty, tn, tn, b->ws, b->policy | 0x100, s));
     }
     {
-      const dim3 grid(d->attn_splits, c.kv_heads, B);
+      const dim3 grid(b->attn_splits, c.kv_heads, B);
       if (c.head_dim == 128)
         attn_decode_partial_batched_kernel<128><<<grid, kAttnThreads, 0, s>>>(
-            b->q, QD, b->k, b->v, KD, d->sin_t, d->cos_t, b->pos, c.max_ctx, d->attn_chunk, group, c.q_heads, b->cache_k[l],
-            b->cache_v[l], b->cache_seq_stride, b->part_o, b->part_ml, d->attn_splits);
+            b->q, QD, b->k, b->v, KD, d->sin_t, d->cos_t, b->pos, c.max_ctx, b->attn_chunk, group, c.q_heads, b->cache_k[l],
+            b->cache_v[l], b->cache_seq_stride, b->part_o, b->part_ml, b->attn_splits);
       else
         attn_decode_partial_batched_kernel<64><<<grid, kAttnThreads, 0, s>>>(
-            b->q, QD, b->k, b->v, KD, d->sin_t, d->cos_t, b->pos, c.max_ctx, d->attn_chunk, group, c.q_heads, b->cache_k[l],
-            b->cache_v[l], b->cache_seq_stride, b->part_o, b->part_ml, d->attn_splits);
-      attn_combine_batched_kernel<<<B, kBatchCombineThreads, (size_t)c.q_heads * d->attn_splits * sizeof(float), s>>>(
-          b->part_o, b->part_ml, b->pos, c.max_ctx, d->attn_chunk, d->attn_splits, c.q_heads, c.head_dim, b->attn);
+            b->q, QD, b->k, b->v, KD, d->sin_t, d->cos_t, b->pos, c.max_ctx, b->attn_chunk, group, c.q_heads, b->cache_k[l],
+            b->cache_v[l], b->cache_seq_stride, b->part_o, b->part_ml, b->attn_splits);
+      attn_combine_batched_kernel<<<B, kBatchCombineThreads, (size_t)c.q_heads * b->attn_splits * sizeof(float), s>>>(
+          b->part_o, b->part_ml, b->pos, c.max_ctx, b->attn_chunk, b->attn_splits, c.q_heads, c.head_dim, b->attn);
     }
-    BD_ST(mllmb200_w4a32_linear_forward_ex(b->attn, L.w[kO], b->o, b->ws, B, QD, H, QD, H, b->policy, s));
+    BD_ST(mllmb200_w4a32_linear_forward_ex(b->attn, L.w[kO], b->o, b->ws, B, QD, H, QD, H, b->policy | 0x100, s));
     add_rmsnorm_quant_kernel<<<B, 256, 0, s>>>(b->h, b->o, L.ln2, c.eps, H, b->h, b->xn, nullptr, nullptr, 0);
     {
       const void* tw[2] = {L.w[kGate], L.w[kUp]};
       float* ty[2] = {b->gate, b->up};
       const int tn[2] = {I, I};
-      BD_ST(mllmb200_w4a32_linear_forward_grouped(b->xn, B, H, H, 2, tw, ty, tn, tn, b->ws, b->policy, s));
+      BD_ST(mllmb200_w4a32_linear_forward_grouped(b->xn, B, H, H, 2, tw, ty, tn, tn, b->ws, b->policy | 0x100, s));
     }
     silu_mul_quant_kernel<<<B, 512, (size_t)I * sizeof(float), s>>>(b->gate, b->up, I, b->act, nullptr, nullptr, 0);
-    BD_ST(mllmb200_w4a32_linear_forward_ex(b->act, L.w[kDown], b->down, b->ws, B, I, H, I, H, b->policy, s));
+    BD_ST(mllmb200_w4a32_linear_forward_ex(b->act, L.w[kDown], b->down, b->ws, B, I, H, I, H, b->policy | 0x100, s));
   }
   add_rmsnorm_quant_kernel<<<B, 256, 0, s>>>(b->h, b->down, d->final_norm, c.eps, H, nullptr, b->xn, nullptr, nullptr, 0);
   {
     const dim3 grid(kLmCtas, (B + kLmRows - 1) / kLmRows);
-    lm_head_f16_batched_kernel<<<grid, 256, (size_t)kLmRows * H * sizeof(float), s>>>(b->xn, B, d->lm_head, H, c.vocab,
+    lm_head_f16_batched_kernel<<<grid, kLmThreads, lm_smem_bytes(H), s>>>(b->xn, B, d->lm_head, H, c.vocab,
                                                                                       b->logits, b->best);
   }
   sample_advance_batched_kernel<<<B, 32, 0, s>>>(b->best, kLmCtas, b->pos, b->token, b->history, c.max_ctx);
@@ -345,6 +382,7 @@ int mllmb200_qwen2_batch_create(void* decoder, int batch, void** handle) {
   auto* d = static_cast<Decoder*>(decoder);
   if (!d || !handle || batch < 1 || batch > 1024) return MLLMB200_INVALID_ARG;
   const auto& c = d->cfg;
+  if (c.hidden % 32 != 0) return MLLMB200_UNSUPPORTED;  // the batched lm_head walks k in steps of 32
   auto* b = new BatchDecoder();
   b->base = d;
   b->batch = batch;
@@ -352,12 +390,20 @@ int mllmb200_qwen2_batch_create(void* decoder, int batch, void** handle) {
   const size_t B = (size_t)batch;
   const int QD = c.q_heads * c.head_dim, KD = c.kv_heads * c.head_dim;
   b->cache_seq_stride = (size_t)c.kv_heads * c.max_ctx * c.head_dim;
+  {
+    // aim at about 8 CTAs per SM over the (split, kv head, sequence) grid, chunks a multiple of 32 and at least the batch-1 chunk
+    const long long want_splits = std::max<long long>(1, (8LL * 148) / ((long long)batch * c.kv_heads));
+    int chunk = (int)((c.max_ctx + want_splits - 1) / want_splits);
+    chunk = std::max(d->attn_chunk, (chunk + 31) / 32 * 32);
+    b->attn_chunk = chunk;
+    b->attn_splits = (c.max_ctx + chunk - 1) / chunk;
+  }
   bool ok = balloc(b, &b->h, B * c.hidden) && balloc(b, &b->xn, B * c.hidden) && balloc(b, &b->q, B * QD) &&
             balloc(b, &b->k, B * KD) && balloc(b, &b->v, B * KD) && balloc(b, &b->attn, B * QD) && balloc(b, &b->o, B * c.hidden) &&
             balloc(b, &b->gate, B * c.inter) && balloc(b, &b->up, B * c.inter) && balloc(b, &b->act, B * c.inter) &&
             balloc(b, &b->down, B * c.hidden) && balloc(b, &b->logits, B * c.vocab) &&
-            balloc(b, &b->part_o, B * c.q_heads * d->attn_splits * c.head_dim) &&
-            balloc(b, &b->part_ml, B * c.q_heads * d->attn_splits * 2) && balloc(b, &b->best, B * kLmCtas) &&
+            balloc(b, &b->part_o, B * c.q_heads * b->attn_splits * c.head_dim) &&
+            balloc(b, &b->part_ml, B * c.q_heads * b->attn_splits * 2) && balloc(b, &b->best, B * kLmCtas) &&
             balloc(b, &b->pos, B) && balloc(b, &b->token, B) && balloc(b, &b->scratch_next, 1) &&
             balloc(b, &b->history, B * c.max_ctx);
   size_t wsb = 0;
@@ -374,7 +420,7 @@ int mllmb200_qwen2_batch_create(void* decoder, int batch, void** handle) {
     ok = balloc(b, &b->cache_k[l], B * b->cache_seq_stride) && balloc(b, &b->cache_v[l], B * b->cache_seq_stride);
   if (ok)
     ok = cudaFuncSetAttribute(lm_head_f16_batched_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)((size_t)kLmRows * c.hidden * sizeof(float))) == cudaSuccess &&
+                              (int)lm_smem_bytes(c.hidden)) == cudaSuccess &&
          cudaMemsetAsync(b->pos, 0, B * sizeof(int), d->stream) == cudaSuccess &&
          cudaMemsetAsync(b->token, 0, B * sizeof(int), d->stream) == cudaSuccess &&
          cudaStreamSynchronize(d->stream) == cudaSuccess;

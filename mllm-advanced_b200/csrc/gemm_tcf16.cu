@@ -65,6 +65,7 @@ struct TfParams {
   const uint8_t* a_blocks;  // activations, [num_groups][m8_pad][512 bytes] fp16 canonical blocks
   const float2* a_hdr;      // [m] {lhs_scale, a_off bits}; unused (may be null) on the W4A16 path
   int m, k, num_groups, m8_pad, num_problems;
+  int use_pdl;  // programmatic dependent launch: everything up to the first read of the activations overlaps the previous kernel
   TfProblem prob[kTfMaxProblems];
 };
 
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   uint8_t* a_stages = smem + S::kAOffset;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (p.use_pdl) pdl_launch_dependents();  // the next kernel waits for this whole grid before it touches anything we use
   int pi = 0;
 #pragma unroll
   for (int i = 1; i < kTfMaxProblems; ++i)
@@ -142,8 +144,6 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
-  if constexpr (!A16)
-    for (int i = tid; i < NT; i += kTfThreads) s_hdr[i] = (m0 + i < p.m) ? p.a_hdr[m0 + i] : make_float2(0.0f, 0.0f);
   if (warp == kTfDequantWarps + 1) {
     tmem_alloc(tmem_base_slot, kTmemCols);
     tmem_relinquish();
@@ -157,6 +157,8 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   if (warp == kTfDequantWarps) {
     // ------------------------------------------------------------ producer
     const int np = min(kPanels, pr.num_panels - panel0);
+    // the weights are constant, the activation blocks come from the kernel before this one
+    if (p.use_pdl) pdl_wait_prior();
     for (int it = 0; it < k_tiles; ++it) {
       const int s = it % kStages;
       const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -228,6 +230,13 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     const int emax = (int)(((A16 ? reinterpret_cast<const TiledHeaderA16*>(pr.tiled)->max_weight_bits : hdr->max_scale_bits) >> 23) & 0xFFu);
     const int E = emax == 0 ? 0 : (A16 ? 14 : 11) - (emax - 127);
     const float up = exp2f((float)E), down = exp2f((float)-E);
+    if constexpr (!A16) {
+      // the rows' {scale, offset} pairs, written by the quantization kernel in front of this one; read by these
+      // same warps in the epilogue, after the barrier below
+      if (p.use_pdl) pdl_wait_prior();
+      for (int i = tid; i < NT; i += kTfDequantWarps * 32) s_hdr[i] = (m0 + i < p.m) ? p.a_hdr[m0 + i] : make_float2(0.0f, 0.0f);
+      asm volatile("bar.sync 1, %0;" ::"n"(kTfDequantWarps * 32) : "memory");
+    }
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
       const int s = it % kStages, sa = it % kTfAStages;
@@ -354,9 +363,19 @@ static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const dim3 grid((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
-  w4a32_gemm_tcf16_kernel<NT, ROWS, A16><<<grid, kTfThreads, S::kTotal, stream>>>(prm);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
+  cfg.blockDim = dim3(kTfThreads, 1, 1);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  if (prm.use_pdl) {
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, w4a32_gemm_tcf16_kernel<NT, ROWS, A16>, prm);
 }
 
 // Tile shape for a launch: weight rows per CTA (128, or 256 = two accumulators sharing every loaded
@@ -404,7 +423,7 @@ bool w4a32_gemm_tcf16_preferred(int m, int k, int n) { return w4a32_gemm_tcf16_s
 // w4a32_gemm_tcf16_tile_grouped for the same arguments.
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float2* a_hdr, int m, int k, int count,
                                             const void* const* tiled, float* const* y, const int* n, const int* ldy,
-                                            cudaStream_t stream, int num_peers, float* const* y_peers) {
+                                            cudaStream_t stream, int num_peers, float* const* y_peers, int use_pdl) {
   if (count < 1 || count > kTfMaxProblems) return cudaErrorInvalidValue;
   if (num_peers > 0 && (count != 1 || num_peers > kTfMaxPeers || y_peers == nullptr)) return cudaErrorInvalidValue;
   const TfTile tile = tf_tile_for(m, count, n);
@@ -416,6 +435,7 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
   prm.num_groups = (k + kGroup - 1) / kGroup;
   prm.m8_pad = (m + nt - 1) / nt * nt / 8;
   prm.num_problems = count;
+  prm.use_pdl = use_pdl;
   int tiles = 0;
   for (int i = 0; i < count; ++i) {
     const TiledHeader th = make_tiled_header(n[i], k, 0, 0);
@@ -480,8 +500,8 @@ cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, 
 }
 
 cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
-                                    int n, int ldy, cudaStream_t stream) {
-  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream, 0, nullptr);
+                                    int n, int ldy, cudaStream_t stream, int use_pdl) {
+  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream, 0, nullptr, use_pdl);
 }
 
 }  // namespace mllmb200

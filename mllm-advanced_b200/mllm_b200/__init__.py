@@ -6,7 +6,7 @@ used for device memory and streams, nothing else: every computation goes through
 and importing this module fails loudly when that library has not been built.
 """
 from .binding import (  # noqa: F401
-    SCALE_BF16_TRUNC, SCALE_BF16_RNE, SCALE_FP16, KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_F16, KERNEL_FASTEST, KERNEL_GEMV_2LAUNCH, gemv_plan_check, linear_forward_multi,
+    SCALE_BF16_TRUNC, SCALE_BF16_RNE, SCALE_FP16, KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_F16, KERNEL_FASTEST, KERNEL_GEMV_2LAUNCH, KERNEL_STREAM_TC, gemv_plan_check, linear_forward_multi,
     MllmB200Error, lib, lib_path, status_str, prepack_size, quant_prepack, prepack_from_quantized, blob_info,
     blob_sections, tiled_size, workspace_size, W4A32Weights, linear_forward, linear_forward_grouped, quant_activations, check_device_status, conv3d_forward,
 )

@@ -4,7 +4,7 @@ import os
 import numpy as np
 
 SCALE_BF16_TRUNC, SCALE_BF16_RNE, SCALE_FP16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_F16, KERNEL_FASTEST, KERNEL_GEMV_2LAUNCH = 0, 1, 2, 3, 4, 5, 6
+KERNEL_AUTO, KERNEL_GEMV, KERNEL_SIMT, KERNEL_TC, KERNEL_TC_F16, KERNEL_FASTEST, KERNEL_GEMV_2LAUNCH, KERNEL_STREAM_TC = 0, 1, 2, 3, 4, 5, 6, 7
 KERNEL_FLAG_PDL = 0x100
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

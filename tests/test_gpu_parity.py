@@ -283,6 +283,51 @@ def test_simt_gemm_vs_oracle(orc, m, k, n):
     assert_close(y, ref, f"simt m={m} k={k} n={n}")
 
 
+@pytest.mark.parametrize("m,k,n", [(5, 1536, 256), (8, 1536, 1536), (9, 64, 40), (16, 1176, 1280), (17, 1536, 256),
+                                   (24, 8960, 1536), (32, 4096, 96), (33, 1536, 1536), (40, 32, 33), (64, 1536, 8960),
+                                   (64, 8960, 1536), (64, 70, 45), (63, 8192, 512), (64, 12288, 64)])
+def test_streaming_small_batch_gemm_vs_oracle(orc, m, k, n):
+    """The streaming tensor-core GEMM for 5 <= M <= 64 (mma.sync u8 x s8 per K-group, clusters split K where the
+    activations of a whole row do not fit one CTA): exact int32 group sums, fp32 scale-accumulate; against the
+    oracle, and the default policy must pick it for these batch sizes."""
+    rng = np.random.default_rng(m * 5 + k + n)
+    x, w, b = make_case(rng, m, n, k, bias=(n % 2 == 0), x_scale=rng.uniform(0.2, 3.0))
+    if m > 8:
+        x[7] = np.abs(x[7]) + 1.0   # zero point -128
+        x[8] = 0.0
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    y = gpu_forward(x, blob, mb.KERNEL_STREAM_TC)
+    assert_close(y, ref, f"streaming tensor-core m={m} k={k} n={n}")
+    assert mb.lib().mllmb200_w4a32_select_kernel(m, k, n) == mb.KERNEL_STREAM_TC
+    y2 = gpu_forward(x, blob, mb.KERNEL_AUTO, pdl=True)
+    assert np.array_equal(y, y2), "default policy / dependent launch must give the same bits"
+    assert_close(y, gpu_forward(x, blob, mb.KERNEL_SIMT), "streaming tensor-core vs simt")
+    mb.check_device_status()
+
+
+def test_streaming_small_batch_gemm_grouped_and_scale_modes(orc):
+    """q, k, v sharing one quantization and ONE launch at M = 64, and the other two scale encodings."""
+    rng = np.random.default_rng(64)
+    k, ns, m = 1536, (1536, 256, 256), 64
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    ws = [make_case(rng, 1, n, k)[1:] for n in ns]
+    wts = [mb.W4A32Weights.from_blob(mb.quant_prepack(w, b)) for w, b in ws]
+    outs = mb.linear_forward_grouped(torch.from_numpy(x).cuda(), wts)
+    for (w, b), wt, o in zip(ws, wts, outs):
+        single = mb.linear_forward(torch.from_numpy(x).cuda(), wt, kernel=mb.KERNEL_STREAM_TC)
+        assert torch.equal(o, single)
+        q, s, _ = mb.blob_sections(mb.quant_prepack(w, b))
+        assert_close(o.cpu().numpy(), orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b), "grouped small batch")
+    for mode in (mb.SCALE_BF16_RNE, mb.SCALE_FP16):
+        w, b = ws[1]
+        blob = mb.quant_prepack(w, b, scale_mode=mode)
+        y = gpu_forward(x[:20], blob, mb.KERNEL_STREAM_TC)
+        assert_close(y, gpu_forward(x[:20], blob, mb.KERNEL_SIMT), f"scale mode {mode}")
+    mb.check_device_status()
+
+
 @pytest.mark.parametrize("m,k,n", [(128, 128, 128), (17, 1536, 256), (33, 1536, 1536), (64, 8960, 1536),
                                    (128, 1536, 8960), (100, 70, 45), (200, 1176, 1280), (512, 1536, 256),
                                    (300, 4096, 96), (129, 32, 33)])
