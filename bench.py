@@ -257,15 +257,21 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------------------------ GPU side
 def make_random_weights(mb, torch, n, k, has_bias, gen, scale_mode=0):
-    """Random int4 + scales (BASELINE config 0 distributions), assembled as a blob on the device and
-    repacked there: no host quantization of 1.3 G weights."""
+    """Random int4 (uniform in -7..7) + scales |N(0, 0.02)| / 7 (BASELINE config 0 distributions), assembled as a blob
+    on the device and repacked there: no host quantization of 1.3 G weights."""
     dev = "cuda"
     total = mb.prepack_size(n, k, has_bias)
     blob = torch.zeros(total, dtype=torch.uint8, device=dev)
     # section offsets of a blob of this shape (the repack takes the shape as arguments, not from the header)
     a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
     mb.lib().mllmb200_w4a32_blob_offsets(n, k, int(has_bias), C.byref(a), C.byref(b), C.byref(c))
-    nib = torch.randint(0, 256, (n * (k // 2),), dtype=torch.uint8, device=dev, generator=gen)
+    # int4 values uniform in -7..7 (stored +8): zero-mean rows, as a symmetric quantizer leaves them.  With the full
+    # 0..15 range every row has mean -0.5 scale units, and the common-mode term that gives a 28-layer random stack
+    # (the same all-negative vector added by every layer) drowns the token embedding in the residual stream.
+    lo = torch.randint(1, 16, (n * (k // 2),), dtype=torch.uint8, device=dev, generator=gen)
+    hi = torch.randint(1, 16, (n * (k // 2),), dtype=torch.uint8, device=dev, generator=gen)
+    nib = lo | (hi << 4)
+    del lo, hi
     sc = (torch.randn((n * (k // 32),), device=dev, generator=gen).abs() * (0.02 / 7.0))
     sc16 = (sc.view(torch.int32) >> 16).to(torch.int16)
     blob[a.value:a.value + nib.numel()] = nib
@@ -736,10 +742,11 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
         dec.set_norm(0, l, np.ones(cfg["hidden"], np.float32))
         dec.set_norm(1, l, np.ones(cfg["hidden"], np.float32))
     dec.set_norm(2, 0, np.ones(cfg["hidden"], np.float32))
-    emb = torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen)
-    # lm_head = a row permutation of the embedding table (x 0.02): the largest logit then belongs to the row that
-    # matches the current token's embedding in the residual stream, so greedy decoding walks the permutation instead
-    # of collapsing onto one token as a fully random head does (`distinct_tokens` below)
+    # embedding rows ~ N(0, 16^2): the current token stays the largest component of the residual stream through all 28
+    # random-init layers (each adds a vector of rms < 1).  lm_head = a row permutation of the embedding table (x 0.02):
+    # the largest logit then belongs to the row that matches the current token's embedding, so greedy decoding walks
+    # the permutation instead of collapsing onto one token as a fully random head does (`distinct_tokens` below)
+    emb = torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen) * 16.0
     perm = torch.randperm(cfg["vocab"], device="cuda", generator=gen)
     head = (emb[perm] * 0.02).to(torch.float16)
     del perm
