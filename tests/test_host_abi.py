@@ -101,6 +101,24 @@ def test_sizes():
     assert mb.workspace_size(512, 1536) >= 512 * 1536 + 512 * 8
 
 
+def test_default_kernel_by_batch_size():
+    """Which kernel family the default policy takes (host logic only): the single-launch GEMV up to 4 rows, the
+    streaming tensor-core GEMM up to 64 rows where its plan applies (a cluster of at most 8 CTAs must hold the
+    activations of a row: K up to 12288 at 64 rows), the tcgen05 tile GEMM above, the dp4a kernel for what is left;
+    and the workspace covers the activation blocks of whichever is taken."""
+    L = mb.lib()
+    for k, n in ((1536, 1536), (1536, 256), (1536, 8960), (8960, 1536), (8192, 28672)):
+        for m in (1, 4):
+            assert L.mllmb200_w4a32_select_kernel(m, k, n) == mb.KERNEL_GEMV
+        for m in (5, 8, 33, 64):
+            assert L.mllmb200_w4a32_select_kernel(m, k, n) == mb.KERNEL_STREAM_TC
+            assert mb.workspace_size(m, k) >= (k // 32) * ((m + 7) // 8 * 8) * 36 + m * 8
+        for m in (65, 512):
+            assert L.mllmb200_w4a32_select_kernel(m, k, n) == mb.KERNEL_TC
+    assert L.mllmb200_w4a32_select_kernel(64, 32768, 64) in (mb.KERNEL_TC, mb.KERNEL_SIMT)  # a row's activations do not fit 8 CTAs
+    assert L.mllmb200_w4a32_select_kernel(8, 32768, 64) == mb.KERNEL_STREAM_TC               # ... but those of 8 rows do
+
+
 def test_gemv_plan_replay_covers_every_cell_once():
     """The streaming GEMV's work decomposition, replayed on the host with the kernel's own walk: every weight
     cell requested and consumed once, every activation group a CTA reads quantized by it, every panel finished
