@@ -335,6 +335,11 @@ def run_gpu(args):
         return
 
     # ---- weights: 28 layers x 7 linears, each its own tiled buffer
+    if args.batched_only:
+        # the batched decode section alone on a model of --decoder-layers layers (small captures under a profiler)
+        few = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(args.decoder_layers)]
+        print(json.dumps({"batched": run_decoder(args, torch, mb, few, gen, hbm_peak, peak_kind, batched_only=True)}), flush=True)
+        return
     layers = [[make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in LINEARS] for _ in range(LAYERS)]
     if args.decoder_only:
         print(json.dumps({"decoder": run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind)}), flush=True)
@@ -730,10 +735,10 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_layer=None):
+def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_layer=None, batched_only=False):
     """BASELINE config 2: the whole 28-layer decoder with random-init W4A32 weights, batch 1,
     512-token prompt of uniform random ids, 128 greedy decode steps, fp32 KV cache, fp16 lm_head."""
-    cfg = dict(mb.QWEN2_1P5B, max_ctx=1024)
+    cfg = dict(mb.QWEN2_1P5B, max_ctx=1024, layers=len(layers))
     prompt_len, steps = args.decoder_prompt, args.decoder_steps  # BASELINE config 2: 512 and 128
     dec = mb.Qwen2Decoder(cfg)
     for l, lw in enumerate(layers):
@@ -751,6 +756,10 @@ def run_decoder(args, torch, mb, layers, gen, hbm_peak, peak_kind, cpu_ms_per_la
     head = (emb[perm] * 0.02).to(torch.float16)
     del perm
     dec.set_tables(emb, head)
+    if batched_only:
+        out = run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind)
+        dec.close()
+        return out
     host_prompt = np.random.default_rng(7).integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     ds = dec.stream()
     modes = {"persistent": mb.DECODE_PERSISTENT, "graph": mb.DECODE_GRAPH}
@@ -881,7 +890,7 @@ def run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind)
 
     ms_start = timed(steps_t)
     done = 2 + steps_t
-    room = ctx_end - 1 - n0 - done - steps_t
+    room = (args.batch_context or ctx_end - 1) - n0 - done - steps_t
     if room > 0:
         bd.decode(room)  # untimed: walk to the end of the context
         done += room
@@ -890,11 +899,11 @@ def run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind)
     done += steps_t
     mb.check_device_status(ds)
     toks = np.stack([bd.generated(b, done) for b in range(B)])
-    lin = LAYERS * sum(algorithmic_bytes(B, k, n, hb) for _, k, n, hb in LINEARS)
+    lin = cfg["layers"] * sum(algorithmic_bytes(B, k, n, hb) for _, k, n, hb in LINEARS)
     head_b = cfg["vocab"] * cfg["hidden"] * 2
 
     def step_bytes(ctx):
-        return lin + head_b + LAYERS * B * 2 * cfg["kv_heads"] * cfg["head_dim"] * 4 * ctx
+        return lin + head_b + cfg["layers"] * B * 2 * cfg["kv_heads"] * cfg["head_dim"] * 4 * ctx
 
     def entry(ms, ctx):
         by = step_bytes(ctx)
@@ -1190,6 +1199,9 @@ def main():
     ap.add_argument("--decoder-reps", type=int, default=3, help="timed repetitions of prefill + 128 steps")
     ap.add_argument("--no-decoder", action="store_true", help="skip the whole-model prefill + decode section")
     ap.add_argument("--no-batched-decode", action="store_true", help="skip the 64-sequence batched decode of the decoder section")
+    ap.add_argument("--batched-only", action="store_true", help="only the batched decode section, on --decoder-layers layers")
+    ap.add_argument("--decoder-layers", type=int, default=LAYERS, help="layers of the model of --batched-only (small values for profiler captures)")
+    ap.add_argument("--batch-context", type=int, default=0, help="with --batched-only: stop the untimed walk at this context (0 = the full 1024)")
     ap.add_argument("--batch-sequences", type=int, default=64, help="sequences of the batched decode section (BASELINE config 3: 64)")
     ap.add_argument("--batch-timed-steps", type=int, default=16, help="timed greedy steps at either end of the batched decode")
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
