@@ -609,26 +609,41 @@ def run_gpu(args):
         except Exception as ex:
             line["prefill_fastest_grouped"] = {"error": str(ex)[:160]}
 
-        # e2e: the same step with HOST buffers (pinned) through the C ABI: per layer one cudaMemcpyAsync H2D of the
-        # seven inputs, the layer call, one cudaMemcpyAsync D2H of the seven outputs; one CUDA graph per step and a host
-        # synchronize after every step because the host reads y.  Host wall clock: launch and synchronize included.
-        hx_all = torch.randn(x_all.shape).pin_memory()
-        hy_all = torch.empty(y_all.shape).pin_memory()
+        # e2e: the same step with HOST buffers (pinned) through the C ABI: one cudaMemcpyAsync H2D of the step's inputs
+        # (every layer's seven x), the 28 layer calls on their slices, one cudaMemcpyAsync D2H of the step's outputs
+        # (every layer's seven y); one CUDA graph per step and a host synchronize after every step because the host
+        # reads y.  Host wall clock: launch and synchronize included.
+        nx, ny = x_all.numel(), y_all.numel()
+        hx_all = torch.randn((LAYERS, nx)).pin_memory()
+        hy_all = torch.empty((LAYERS, ny)).pin_memory()
+        dx_all = torch.empty((LAYERS, nx), device="cuda")
+        dy_all = torch.empty((LAYERS, ny), device="cuda")
+        xs_l, ys_l = [], []
+        for l in range(LAYERS):
+            xo = yo = 0
+            xs_l.append([])
+            ys_l.append([])
+            for _, k, n, _ in LINEARS:
+                xs_l[l].append(dx_all[l, xo:xo + k].view(1, k))
+                ys_l[l].append(dy_all[l, yo:yo + n].view(1, n))
+                xo += k
+                yo += n
 
         def e2e_pass():
-            for lw in layers:
-                x_all.copy_(hx_all, non_blocking=True)
+            dx_all.copy_(hx_all, non_blocking=True)
+            for l, lw in enumerate(layers):
+                xs, ys = xs_l[l], ys_l[l]
                 if args.calls == "layer":
-                    mb.linear_forward_multi(xs7, lw, outs=ys7, stream=stream, pdl=pdl)
+                    mb.linear_forward_multi(xs, lw, outs=ys, stream=stream, pdl=pdl)
                 elif args.calls == "grouped":
-                    mb.linear_forward_grouped(xs7[0], lw[0:3], outs=ys7[0:3], workspace=ws, stream=stream, pdl=pdl)
-                    mb.linear_forward(xs7[3], lw[3], out=ys7[3], workspace=ws, stream=stream, pdl=pdl)
-                    mb.linear_forward_grouped(xs7[4], lw[4:6], outs=ys7[4:6], workspace=ws, stream=stream, pdl=pdl)
-                    mb.linear_forward(xs7[6], lw[6], out=ys7[6], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward_grouped(xs[0], lw[0:3], outs=ys[0:3], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward(xs[3], lw[3], out=ys[3], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward_grouped(xs[4], lw[4:6], outs=ys[4:6], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward(xs[6], lw[6], out=ys[6], workspace=ws, stream=stream, pdl=pdl)
                 else:
                     for i, w in enumerate(lw):
-                        mb.linear_forward(xs7[i], w, out=ys7[i], workspace=ws, stream=stream, pdl=pdl)
-                hy_all.copy_(y_all, non_blocking=True)
+                        mb.linear_forward(xs[i], w, out=ys[i], workspace=ws, stream=stream, pdl=pdl)
+            hy_all.copy_(dy_all, non_blocking=True)
 
         h2d = LAYERS * x_all.numel() * 4
         d2h = LAYERS * y_all.numel() * 4
@@ -650,15 +665,16 @@ def run_gpu(args):
                 for _ in range(iters):
                     g2.replay()
                     torch.cuda.current_stream().synchronize()  # the host reads y after every step
-                    _ = float(hy_all[0])
+                    _ = float(hy_all[LAYERS - 1, 0])
                 samples.append((time.perf_counter() - t0) * 1e3 / iters)
             ms_e2e = float(np.median(samples))
             del g2
             line["e2e"] = {"value": step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "transfer": "cudaMemcpyAsync, pinned host memory",
-                           "how": "per layer: the seven x in pinned host memory -> one H2D copy -> C-ABI call(s) -> one D2H copy "
-                                  "of the seven y into pinned host memory; one CUDA graph per step; host synchronizes and "
-                                  "reads y every step; host wall clock, median of 5 x %d steps" % iters}
+                           "how": "per step: every layer's seven x in pinned host memory -> ONE H2D copy -> the 28 C-ABI layer "
+                                  "calls on their slices -> ONE D2H copy of every layer's seven y into pinned host memory; "
+                                  "one CUDA graph per step; host synchronizes and reads y every step; host wall clock, "
+                                  "median of 5 x %d steps" % iters}
         except Exception as ex:
             line["e2e"] = {"error": str(ex)[:200]}
 
