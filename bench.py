@@ -502,6 +502,94 @@ def run_gpu(args):
         for name, v in cs.items():
             roofline[f"frac_{name.replace('-', '_')}_calls"] = v["frac"]
 
+    # ---- end to end, on every rank at the same time (N replicas, as the headline)
+    e2e_line = None
+    if not args.quick:
+        if dist is not None:
+            dist.barrier()
+        # e2e: the same step with HOST buffers (pinned) through the C ABI: one cudaMemcpyAsync H2D of the step's inputs
+        # (every layer's seven x), the 28 layer calls on their slices, one cudaMemcpyAsync D2H of the step's outputs
+        # (every layer's seven y); one CUDA graph per step and a host synchronize after every step because the host
+        # reads y.  Host wall clock: launch and synchronize included.
+        nx, ny = x_all.numel(), y_all.numel()
+        hx_all = torch.randn((LAYERS, nx)).pin_memory()
+        hy_all = torch.empty((LAYERS, ny)).pin_memory()
+        dx_all = torch.empty((LAYERS, nx), device="cuda")
+        dy_all = torch.empty((LAYERS, ny), device="cuda")
+        xs_l, ys_l = [], []
+        for l in range(LAYERS):
+            xo = yo = 0
+            xs_l.append([])
+            ys_l.append([])
+            for _, k, n, _ in LINEARS:
+                xs_l[l].append(dx_all[l, xo:xo + k].view(1, k))
+                ys_l[l].append(dy_all[l, yo:yo + n].view(1, n))
+                xo += k
+                yo += n
+
+        def e2e_pass():
+            dx_all.copy_(hx_all, non_blocking=True)
+            for l, lw in enumerate(layers):
+                xs, ys = xs_l[l], ys_l[l]
+                if args.calls == "layer":
+                    mb.linear_forward_multi(xs, lw, outs=ys, stream=stream, pdl=pdl)
+                elif args.calls == "grouped":
+                    mb.linear_forward_grouped(xs[0], lw[0:3], outs=ys[0:3], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward(xs[3], lw[3], out=ys[3], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward_grouped(xs[4], lw[4:6], outs=ys[4:6], workspace=ws, stream=stream, pdl=pdl)
+                    mb.linear_forward(xs[6], lw[6], out=ys[6], workspace=ws, stream=stream, pdl=pdl)
+                else:
+                    for i, w in enumerate(lw):
+                        mb.linear_forward(xs[i], w, out=ys[i], workspace=ws, stream=stream, pdl=pdl)
+            hy_all.copy_(dy_all, non_blocking=True)
+
+        h2d = LAYERS * x_all.numel() * 4
+        d2h = LAYERS * y_all.numel() * 4
+        try:
+            with torch.cuda.stream(stream):
+                e2e_pass()
+            stream.synchronize()
+            mb.check_device_status(stream)
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=stream):
+                e2e_pass()
+            for _ in range(3):
+                g2.replay()
+            torch.cuda.synchronize()
+            iters = max(5, args.steps)
+            samples = []
+            for _ in range(5):
+                t0 = time.perf_counter()
+                for _ in range(iters):
+                    g2.replay()
+                    torch.cuda.current_stream().synchronize()  # the host reads y after every step
+                    _ = float(hy_all[LAYERS - 1, 0])
+                samples.append((time.perf_counter() - t0) * 1e3 / iters)
+            ms_e2e = float(np.median(samples))
+            del g2
+        except Exception as ex:
+            ms_e2e, e2e_err = -1.0, str(ex)[:200]
+        else:
+            e2e_err = None
+        if dist is not None:  # every rank ran its own copy of the step at the same time: the slowest one counts
+            t = torch.tensor([ms_e2e, 1.0 if e2e_err is None else 0.0], device="cuda")
+            tmax, tmin = t.clone(), t.clone()
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+            ms_e2e = float(tmax[0].item())
+            if float(tmin[1].item()) == 0.0 and e2e_err is None:
+                e2e_err = "another rank failed"
+        if e2e_err is None:
+            e2e_line = {"value": world * step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                        "h2d_bytes_per_step": world * h2d, "d2h_bytes_per_step": world * d2h,
+                        "transfer": "cudaMemcpyAsync, pinned host memory",
+                        "how": "per step and rank: every layer's seven x in pinned host memory -> ONE H2D copy -> the 28 C-ABI "
+                               "layer calls on their slices -> ONE D2H copy of every layer's seven y into pinned host memory; "
+                               "one CUDA graph per step; host synchronizes and reads y every step; host wall clock, median of "
+                               "5 x %d steps, max over ranks; value = all ranks' bytes / that time" % max(5, args.steps)}
+        else:
+            e2e_line = {"error": e2e_err}
+
     if rank == 0 and not args.quick:
         # per-shape GEMV numbers, each over its 28 distinct weight copies
         per_shape = {}
@@ -519,6 +607,7 @@ def run_gpu(args):
             per_shape[f"{name}_{k}x{n}"] = {"us": ms * 1e3 / LAYERS, "GBs": by * LAYERS / (ms * 1e-3) / 1e9}
             del g
         line["per_shape"] = per_shape
+        line["e2e"] = e2e_line
 
         # prefill: the same seven linears at M=512 (one layer after another, all 28 layers)
         xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
@@ -608,75 +697,6 @@ def run_gpu(args):
             mb.check_device_status()
         except Exception as ex:
             line["prefill_fastest_grouped"] = {"error": str(ex)[:160]}
-
-        # e2e: the same step with HOST buffers (pinned) through the C ABI: one cudaMemcpyAsync H2D of the step's inputs
-        # (every layer's seven x), the 28 layer calls on their slices, one cudaMemcpyAsync D2H of the step's outputs
-        # (every layer's seven y); one CUDA graph per step and a host synchronize after every step because the host
-        # reads y.  Host wall clock: launch and synchronize included.
-        nx, ny = x_all.numel(), y_all.numel()
-        hx_all = torch.randn((LAYERS, nx)).pin_memory()
-        hy_all = torch.empty((LAYERS, ny)).pin_memory()
-        dx_all = torch.empty((LAYERS, nx), device="cuda")
-        dy_all = torch.empty((LAYERS, ny), device="cuda")
-        xs_l, ys_l = [], []
-        for l in range(LAYERS):
-            xo = yo = 0
-            xs_l.append([])
-            ys_l.append([])
-            for _, k, n, _ in LINEARS:
-                xs_l[l].append(dx_all[l, xo:xo + k].view(1, k))
-                ys_l[l].append(dy_all[l, yo:yo + n].view(1, n))
-                xo += k
-                yo += n
-
-        def e2e_pass():
-            dx_all.copy_(hx_all, non_blocking=True)
-            for l, lw in enumerate(layers):
-                xs, ys = xs_l[l], ys_l[l]
-                if args.calls == "layer":
-                    mb.linear_forward_multi(xs, lw, outs=ys, stream=stream, pdl=pdl)
-                elif args.calls == "grouped":
-                    mb.linear_forward_grouped(xs[0], lw[0:3], outs=ys[0:3], workspace=ws, stream=stream, pdl=pdl)
-                    mb.linear_forward(xs[3], lw[3], out=ys[3], workspace=ws, stream=stream, pdl=pdl)
-                    mb.linear_forward_grouped(xs[4], lw[4:6], outs=ys[4:6], workspace=ws, stream=stream, pdl=pdl)
-                    mb.linear_forward(xs[6], lw[6], out=ys[6], workspace=ws, stream=stream, pdl=pdl)
-                else:
-                    for i, w in enumerate(lw):
-                        mb.linear_forward(xs[i], w, out=ys[i], workspace=ws, stream=stream, pdl=pdl)
-            hy_all.copy_(dy_all, non_blocking=True)
-
-        h2d = LAYERS * x_all.numel() * 4
-        d2h = LAYERS * y_all.numel() * 4
-        try:
-            with torch.cuda.stream(stream):
-                e2e_pass()
-            stream.synchronize()
-            mb.check_device_status(stream)
-            g2 = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g2, stream=stream):
-                e2e_pass()
-            for _ in range(3):
-                g2.replay()
-            torch.cuda.synchronize()
-            iters = max(5, args.steps)
-            samples = []
-            for _ in range(5):
-                t0 = time.perf_counter()
-                for _ in range(iters):
-                    g2.replay()
-                    torch.cuda.current_stream().synchronize()  # the host reads y after every step
-                    _ = float(hy_all[LAYERS - 1, 0])
-                samples.append((time.perf_counter() - t0) * 1e3 / iters)
-            ms_e2e = float(np.median(samples))
-            del g2
-            line["e2e"] = {"value": step_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
-                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "transfer": "cudaMemcpyAsync, pinned host memory",
-                           "how": "per step: every layer's seven x in pinned host memory -> ONE H2D copy -> the 28 C-ABI layer "
-                                  "calls on their slices -> ONE D2H copy of every layer's seven y into pinned host memory; "
-                                  "one CUDA graph per step; host synchronizes and reads y every step; host wall clock, "
-                                  "median of 5 x %d steps" % iters}
-        except Exception as ex:
-            line["e2e"] = {"error": str(ex)[:200]}
 
         # CPU baselines on this box's host cores (single-process runs only: under a multi-process launcher
         # every rank is pinned to one OpenMP thread, which would misstate the host)
