@@ -54,7 +54,7 @@ class CUDAW4A32Backend final : public BackendBase {
   void* deviceAlloc(size_t bytes);
   void deviceFree(void* ptr);
 
-  // Kernel policy of CUDAW4A32LinearOp::forward for M >= 17 (the `kernel` argument of
+  // Kernel policy of CUDAW4A32LinearOp::forward for M >= 65 (the `kernel` argument of
   // mllmb200_w4a32_linear_forward_ex): 0 = the exact int8 tensor-core path (default: the reference's
   // arithmetic), 5 = the fastest path (fp16 tensor-core kernel for M >= 128, same 1e-3 * rms bound).
   void setLinearKernelPolicy(int policy) { linear_policy_ = policy; }
