@@ -42,6 +42,13 @@
 #include "layout_a16.h"
 #include "tcgen05_common.cuh"
 
+#ifndef MLLMB200_TF_RASTER_M
+#define MLLMB200_TF_RASTER_M 1
+#endif
+#ifndef MLLMB200_TF_WEIGHT_HINT
+#define MLLMB200_TF_WEIGHT_HINT 1
+#endif
+
 namespace mllmb200 {
 
 constexpr int kTfDequantWarps = 8;  // warps w and w + 4 share the weight rows 32 (w % 4)..; each takes one K-group of a stage
@@ -122,15 +129,25 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (p.use_pdl) pdl_launch_dependents();  // the next kernel waits for this whole grid before it touches anything we use
+  // CTAs are dispatched in order of blockIdx.x, then y.  Renumbered so that the tiles that share a weight tile (same
+  // columns of W, different rows of x) are neighbours in that order: they run in the same wave, the weight tile comes
+  // from DRAM once and the rest of them find it in L2, while the activation blocks, which every wave reads in full,
+  // stay resident.
+#if MLLMB200_TF_RASTER_M
+  const int linear = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  const int bx = linear / (int)gridDim.y, tile_m = linear % (int)gridDim.y;
+#else
+  const int bx = blockIdx.x, tile_m = blockIdx.y;
+#endif
   int pi = 0;
 #pragma unroll
   for (int i = 1; i < kTfMaxProblems; ++i)
-    if (i < p.num_problems && (int)blockIdx.x >= p.prob[i].tile_begin) pi = i;
+    if (i < p.num_problems && bx >= p.prob[i].tile_begin) pi = i;
   const TfProblem& pr = p.prob[pi];
   if constexpr (!A16) {  // (the W4A16 launcher's kernels check their own header format)
     if (!tiled_header_ok_cta(pr.tiled, pr.n, p.k)) return;  // before any copy, barrier or tensor-memory allocation
   }
-  const int tile_n = (int)blockIdx.x - pr.tile_begin, tile_m = blockIdx.y;
+  const int tile_n = bx - pr.tile_begin;
   const int panel0 = tile_n * kPanels, m0 = tile_m * NT;
   const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
   constexpr uint32_t kTmemCols = (uint32_t)(kHalves * NT) < 32u ? 32u : (uint32_t)(kHalves * NT);
@@ -157,26 +174,51 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   if (warp == kTfDequantWarps) {
     // ------------------------------------------------------------ producer
     const int np = min(kPanels, pr.num_panels - panel0);
-    // the weights are constant, the activation blocks come from the kernel before this one
-    if (p.use_pdl) pdl_wait_prior();
-    for (int it = 0; it < k_tiles; ++it) {
+#if MLLMB200_TF_WEIGHT_HINT
+    const uint64_t stream_once = l2_policy_evict_first();
+#endif
+    // One K-tile into its stage: `parts` bit 0 = the weight cells, bit 1 = the activation blocks.  The barrier is armed
+    // for both together, with the first part that is requested.
+    auto request = [&](int it, int parts) {
       const int s = it % kStages;
-      const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&mma_done[s], ph ^ 1u))) break;
       const int g0 = it * kTfGroupsPerStage;
       const int ng = min(kTfGroupsPerStage, p.num_groups - g0);
       uint8_t* st = stages + (size_t)s * S::kStageBytes;
-      if (lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCell + ng * NT * 64));
+      if ((parts & 1) && lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCell + ng * NT * 64));
       __syncwarp();
-      if (lane < np) {
+      if ((parts & 1) && lane < np) {
+        // the weights pass through once per tile row; the activation blocks are what every tile row re-reads:
+        // first in line for eviction, so that a wave of weight tiles does not push the blocks out of L2
+#if MLLMB200_TF_WEIGHT_HINT
+        bulk_g2s_hint(st + lane * kTfGroupsPerStage * kCell,
+                      pr.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCell,
+                      (uint32_t)(ng * kCell), &raw_full[s], stream_once);
+#else
         bulk_g2s(st + lane * kTfGroupsPerStage * kCell,
                  pr.tiled + sizeof(TiledHeader) + ((size_t)(panel0 + lane) * p.num_groups + g0) * kCell,
                  (uint32_t)(ng * kCell), &raw_full[s]);
-      } else if (lane >= kPanels && lane < kPanels + ng) {
+#endif
+      } else if ((parts & 2) && lane >= kPanels && lane < kPanels + ng) {
         const int g = lane - kPanels;
         bulk_g2s(st + S::kRawBytes + g * NT * 64, p.a_blocks + ((size_t)(g0 + g) * p.m8_pad + (m0 >> 3)) * 512,
                  (uint32_t)(NT * 64), &raw_full[s]);
       }
+    };
+    // The weights are constant, the activation blocks come from the kernel before this one: under programmatic
+    // dependent launch the weight cells of the first lap are requested before the wait, the blocks after it.
+    const int first_lap = min(k_tiles, kStages);
+    if (p.use_pdl) {
+      for (int it = 0; it < first_lap; ++it) request(it, 1);
+      pdl_wait_prior();
+      for (int it = 0; it < first_lap; ++it) request(it, 2);
+    } else {
+      for (int it = 0; it < first_lap; ++it) request(it, 3);
+    }
+    for (int it = first_lap; it < k_tiles; ++it) {
+      const int s = it % kStages;
+      const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&mma_done[s], ph ^ 1u))) break;
+      request(it, 3);
     }
   } else if (warp == kTfDequantWarps + 1) {
     // ------------------------------------------------------------ MMA issuer
