@@ -16,7 +16,7 @@
 // ~1e-6 * rms.  With fp16-ENCODED scales (MLLMB200_SCALE_FP16: 11 significant bits) the product needs up
 // to 14 bits and the HMUL2 below rounds it to 11: a relative error of at most 2^-12 per weight, which
 // shows up as about 1.5e-4 * rms(y) per output; stated bound for that mode 2e-3 * rms(y) (the exact
-// kernels 1-3 remain available for it).  Scales more than 2^25 below the matrix maximum fall into fp16
+// kernels 1-3 remain available for it).  Scales more than 2^24 below the matrix maximum fall into fp16
 // subnormals and lose low bits (contribution < 2^-25 of the largest group's).
 //
 //   y[m,n] = lhs_scale[m] * 2^-E * sum_k A[n,k] B[m,k] + bias[n]
@@ -48,10 +48,36 @@
 #ifndef MLLMB200_TF_WEIGHT_HINT
 #define MLLMB200_TF_WEIGHT_HINT 1
 #endif
+#ifndef MLLMB200_TF_FUSED_DEQUANT
+#define MLLMB200_TF_FUSED_DEQUANT 1
+#endif
+#ifndef MLLMB200_TF_ATM  // dequantized weight operand in tensor memory (128-row tiles)
+#define MLLMB200_TF_ATM 1
+#endif
+#ifndef MLLMB200_TF_WIDE  // 256-row tiles (two accumulators, operand in shared memory) where tf_tile_for picks them
+#define MLLMB200_TF_WIDE 1
+#endif
 
 namespace mllmb200 {
 
-constexpr int kTfDequantWarps = 8;  // warps w and w + 4 share the weight rows 32 (w % 4)..; each takes one K-group of a stage
+#ifdef MLLMB200_TF_TRACE
+extern __device__ unsigned long long* g_gs_trace;  // development build only: clock stamps of one CTA per K-tile
+// MLLMB200_TF_TRACE = 1: every stamp; 2: only the MMA warp's (slots 4-6) and the top of the dequant loop (7)
+#define TF_STAMP(it, slot) do { if ((MLLMB200_TF_TRACE == 1 || (slot) >= 4) && traced && (it) < 100) g_gs_trace[17 + (it) * 8 + (slot)] = (unsigned long long)clock64(); } while (0)
+#define TF_STAMP0(slot) do { if (traced) g_gs_trace[1 + (slot)] = (unsigned long long)clock64(); } while (0)
+#else
+#define TF_STAMP(it, slot) do { } while (0)
+#define TF_STAMP0(slot) do { } while (0)
+#endif
+
+#ifndef MLLMB200_TF_DQ_WARPS
+#define MLLMB200_TF_DQ_WARPS 16
+#endif
+// Dequant warps (a multiple of 8).  The warps that share a set of 32 weight rows take turns over the K-groups; one
+// K-group costs a warp a chain of waits, loads, ~80 ALU instructions and a tensor-memory store of several hundred
+// cycles, so it takes several warps per row set to keep that chain off the critical path (measured with 8 warps:
+// ~900 cycles per K-tile of 2 groups against 512 cycles of tensor-core time).
+constexpr int kTfDequantWarps = MLLMB200_TF_DQ_WARPS;
 constexpr int kTfThreads = (kTfDequantWarps + 2) * 32;
 constexpr int kTfTileRows = 128;   // weight rows per MMA (tensor-memory lanes); a CTA tile is ROWS = 128 or 256 of them
 
@@ -79,27 +105,37 @@ struct TfParams {
 // A16 = the W4A16 sibling format (layout_a16.h): 768-byte cells with an fp32 scale and an fp32 zero term per
 // row and K-group, A = fp16( ((u - 8) * s + z) * 2^E ) (one rounding), B = fp16( a_q * a_s ) per 32-element
 // block (one rounding), fp16 output.
-template <int NT, int ROWS, bool A16 = false>
+//
+// ATM = the dequantized weight operand lives in TENSOR memory, not in shared memory: the dequant warps write their
+// rows with tcgen05.st (thread = lane = weight row, two fp16 per 32-bit column) and the MMA takes A from there.
+// Shared memory then carries only the loaded data - per K-group of a 128 x 256 tile 16 KB of B read by the MMAs
+// plus 18.6 KB written by the copies, instead of 24 + 8 + 18.6 KB - and the room of the operand stages goes to a
+// deeper ring.  Columns: [0, NT) the accumulator, then kAStages x kGroups x 16 of operand (512 allocated).
+template <int NT, int ROWS, bool A16 = false, bool ATM = false>
 struct TfSmem {
+  static_assert(!ATM || ROWS == 128, "the tensor-memory operand is for single-accumulator tiles");
   static constexpr int kCell = A16 ? kCellBytesA16 : kCellBytes;
   // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
   // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
   static constexpr int kGroups = (NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
-  // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
-  // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
-  // the number of tiles in flight, so both rings are as deep as shared memory allows.
-  static constexpr int kStages = (NT >= 256 && ROWS == 128) ? 4 : 3;
-  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages); the 768-byte cells of the
-  // W4A16 format leave room for two operand stages of 4 K-groups
-  static constexpr int kAStages = (A16 && NT < 256) ? 2 : kStages;
   static constexpr int kPanels = ROWS / kPanelRows;
-  static constexpr int kGroupABytes = ROWS * kGroup * 2;  // one K-group of the A operand (8 or 16 KB)
   static constexpr int kRawBytes = kPanels * kGroups * kCell;
   static constexpr int kBBytes = kGroups * NT * 64;
   static constexpr int kStageBytes = kRawBytes + kBBytes;
-  static constexpr int kABytes = kGroups * kGroupABytes;
   static constexpr int kBarBytes = 256;
   static constexpr int kHdrBytes = NT * 8;  // {lhs_scale, a_off} of the tile's activation rows
+  static constexpr int kFitStages = (227 * 1024 - 1024 - kBarBytes - kHdrBytes) / kStageBytes;
+  // A K-tile passes through a chain of hand-offs (copy landed -> dequantized -> MMAs issued -> MMAs
+  // committed -> stage free) of well over a thousand cycles; its cost per tile is the chain divided by
+  // the number of tiles in flight, so both rings are as deep as shared memory allows.
+  static constexpr int kStages = ATM ? (kFitStages < 7 ? kFitStages : 7) : (NT >= 256 && ROWS == 128) ? 4 : 3;
+  // must not exceed kStages (the dequant warps wait on mma_done of tile it - kAStages); the 768-byte cells of the
+  // W4A16 format leave room for two operand stages of 4 K-groups
+  static constexpr int kAColsPerStage = kGroups * 16;  // tensor-memory columns of one operand stage (ATM)
+  static constexpr int kATmemStages = (512 - NT) / kAColsPerStage;
+  static constexpr int kAStages = ATM ? (kATmemStages < kStages ? kATmemStages : kStages) : (A16 && NT < 256) ? 2 : kStages;
+  static constexpr int kGroupABytes = ROWS * kGroup * 2;  // one K-group of the A operand (8 or 16 KB)
+  static constexpr int kABytes = ATM ? 0 : kGroups * kGroupABytes;
   static constexpr int kAOffset = kBarBytes + kHdrBytes + kStages * kStageBytes;
   static constexpr int kTotal = kAOffset + kAStages * kABytes + 1024;
   static_assert(kTotal <= 227 * 1024, "shared memory");
@@ -108,9 +144,9 @@ struct TfSmem {
 // ROWS = 256: two 128-row accumulators side by side in tensor memory share every activation block
 // that is loaded - the activation (B) operand is re-read from L2 once per weight tile, which bounds
 // the 128-row tile on large grids.
-template <int NT, int ROWS, bool A16>
+template <int NT, int ROWS, bool A16, bool ATM>
 __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const TfParams p) {
-  using S = TfSmem<NT, ROWS, A16>;
+  using S = TfSmem<NT, ROWS, A16, ATM>;
   constexpr int kCell = S::kCell;
   static_assert(sizeof(TiledHeader) == sizeof(TiledHeaderA16), "both formats keep their cells 256 bytes in");
   constexpr int kPanels = S::kPanels, kHalves = ROWS / kTfTileRows, kTfGroupABytes = S::kGroupABytes;
@@ -127,7 +163,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   uint8_t* stages = smem + S::kBarBytes + S::kHdrBytes;
   uint8_t* a_stages = smem + S::kAOffset;
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // (warp-uniform for the compiler)
   if (p.use_pdl) pdl_launch_dependents();  // the next kernel waits for this whole grid before it touches anything we use
   // CTAs are dispatched in order of blockIdx.x, then y.  Renumbered so that the tiles that share a weight tile (same
   // columns of W, different rows of x) are neighbours in that order: they run in the same wave, the weight tile comes
@@ -138,6 +174,10 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   const int bx = linear / (int)gridDim.y, tile_m = linear % (int)gridDim.y;
 #else
   const int bx = blockIdx.x, tile_m = blockIdx.y;
+#endif
+#ifdef MLLMB200_TF_TRACE
+  const bool traced = linear == (int)(gridDim.x * gridDim.y) / 2 && lane == 0 && (warp == 0 || warp >= kTfDequantWarps) && g_gs_trace != nullptr;
+  if (warp == 0) TF_STAMP0(0);
 #endif
   int pi = 0;
 #pragma unroll
@@ -150,14 +190,20 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   const int tile_n = bx - pr.tile_begin;
   const int panel0 = tile_n * kPanels, m0 = tile_m * NT;
   const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
-  constexpr uint32_t kTmemCols = (uint32_t)(kHalves * NT) < 32u ? 32u : (uint32_t)(kHalves * NT);
+  constexpr uint32_t kTmemCols = ATM ? 512u : (uint32_t)(kHalves * NT) < 32u ? 32u : (uint32_t)(kHalves * NT);
+  constexpr uint32_t kAColBase = (uint32_t)NT;  // first operand column (ATM)
+  // Dequant work: kRowSets sets of 32 weight rows, kDqShare warps per set; K-group g of K-tile it goes to the warp
+  // number (it * groups per tile + g) mod kDqShare of its row set.
+  constexpr int kRowSets = ROWS / 32, kDqShare = kTfDequantWarps / kRowSets;
+  static_assert(kDqShare >= 1 && (kDqShare % kTfGroupsPerStage == 0 || kTfGroupsPerStage % kDqShare == 0), "turn-taking");
+  constexpr int kDqArrivals = kRowSets * (kDqShare < kTfGroupsPerStage ? kDqShare : kTfGroupsPerStage);
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&raw_full[s], 1);
       mbar_init(&mma_done[s], 1);
     }
-    for (int s = 0; s < kTfAStages; ++s) mbar_init(&a_full[s], kTfDequantWarps);  // one arrival per dequant warp
+    for (int s = 0; s < kTfAStages; ++s) mbar_init(&a_full[s], kDqArrivals);  // one arrival per warp that has a K-group in the tile
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
@@ -168,7 +214,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_base_any = *tmem_base_slot;
   const TiledHeader* hdr = reinterpret_cast<const TiledHeader*>(pr.tiled);
 
   if (warp == kTfDequantWarps) {
@@ -218,11 +264,16 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       const int s = it % kStages;
       const uint32_t ph = (uint32_t)(it / kStages) & 1u;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(&mma_done[s], ph ^ 1u))) break;
+      TF_STAMP(it, 0);
       request(it, 3);
     }
   } else if (warp == kTfDequantWarps + 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop (same waits, same addresses in every lane) and one elected lane issues: the
+    // operands of tcgen05.mma are then warp-uniform values, not the private registers of a diverged lane.
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_any, 0);
+    const bool issuer = elect_one_sync();
+    {
       // instruction descriptor: D = f32, A = B = f16, both K-major, N = NT, M = 128
       const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((128u >> 4) << 24);
       bool ok = true;
@@ -231,9 +282,12 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
         const int s = it % kStages, sa = it % kTfAStages;
         // a_full[sa] is arrived on by the dequant warps AFTER they saw raw_full[s] complete, so it also
         // orders this stage's bulk copies (the B operand) before the MMAs: one wait instead of two
-        ok = mbar_wait_bounded(&a_full[sa], (uint32_t)(it / kTfAStages) & 1u);
+        TF_STAMP(it, 4);
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&a_full[sa], (uint32_t)(it / kTfAStages) & 1u));
         if (!ok) break;
+        TF_STAMP(it, 5);
         tc_fence_after();
+        if (issuer) {
         const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
         uint8_t* st = stages + (size_t)s * S::kStageBytes;
         const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(a_stages + (size_t)sa * S::kABytes);
@@ -244,33 +298,43 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
           if (g >= ng) break;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {  // K = 16 per instruction: two chunks of 8; the start address counts 16-byte units
+            if constexpr (ATM) {
+              tc_mma_f16_ts(tmem_base, tmem_base + kAColBase + (uint32_t)(sa * S::kAColsPerStage + g * 16 + h * 8),
+                            b_desc + (uint64_t)((g * NT * 64 + h * 256) >> 4), idesc, accumulate);
+            } else {
 #pragma unroll
-            for (int rh = 0; rh < kHalves; ++rh)  // 128-row halves of the tile: own accumulator (NT columns each), same B
-              tc_mma_f16(tmem_base + (uint32_t)(rh * NT),
-                         a_desc + (uint64_t)((g * kTfGroupABytes + rh * (kTfTileRows * 64) + h * 256) >> 4),
-                         b_desc + (uint64_t)((g * NT * 64 + h * 256) >> 4), idesc, accumulate);
+              for (int rh = 0; rh < kHalves; ++rh)  // 128-row halves of the tile: own accumulator (NT columns each), same B
+                tc_mma_f16(tmem_base + (uint32_t)(rh * NT),
+                           a_desc + (uint64_t)((g * kTfGroupABytes + rh * (kTfTileRows * 64) + h * 256) >> 4),
+                           b_desc + (uint64_t)((g * NT * 64 + h * 256) >> 4), idesc, accumulate);
+            }
             accumulate = 1;
           }
         }
         tc_commit(&mma_done[s]);  // frees the loaded stage (producer) and the A stage (dequant)
+        }
+        __syncwarp();
+        TF_STAMP(it, 6);
       }
-      if (ok) tc_commit(acc_done);
+      if (ok && issuer) tc_commit(acc_done);
     }
   } else {
+    const uint32_t tmem_base = tmem_base_any;
     // ------------------------------------------------------------ dequant: thread j = weight row j of the tile.
     // ROWS = 128: rows are shared by warps w and w + 4, which alternate over the K-groups of a stage;
     // ROWS = 256: one row per thread, every group.
-    const int j = ROWS == 128 ? (tid & 127) : tid;
-    const int gsel = ROWS == 128 ? (warp >> 2) : 0, gstep = ROWS == 128 ? kTfDequantWarps / 4 : 1;
+    const int j = (warp % kRowSets) * 32 + lane;
+    const int turn = warp / kRowSets;
     const int q = j >> 5, r = j & 31;  // panel of the tile, row in the panel
     const bool have_panel = panel0 + q < pr.num_panels;
     const uint32_t scale_mode = hdr->scale_mode;
-    // 2^E maps the largest |scale| of the matrix into [2^11, 2^12): (u - 8) * s * 2^E < 2^15.
+    // 2^E maps the largest |scale| of the matrix into [2^10, 2^11): (u - 8) * s * 2^E < 2^14, 24 * s * 2^E < 2^16 * 0.75.
     // (Read here, not before the role split: the producer must not wait for this load.)
     // W4A16: the header word at the same offset holds the bits of max (8 |s| + |z|) >= max |weight|,
     // mapped into [2^14, 2^15).
     const int emax = (int)(((A16 ? reinterpret_cast<const TiledHeaderA16*>(pr.tiled)->max_weight_bits : hdr->max_scale_bits) >> 23) & 0xFFu);
-    const int E = emax == 0 ? 0 : (A16 ? 14 : 11) - (emax - 127);
+    const int E = emax == 0 ? 0 : (A16 ? 14 : 10) - (emax - 127);
+    const bool fused_dequant = MLLMB200_TF_FUSED_DEQUANT && scale_mode != 2u;
     const float up = exp2f((float)E), down = exp2f((float)-E);
     if constexpr (!A16) {
       // the rows' {scale, offset} pairs, written by the quantization kernel in front of this one; read by these
@@ -282,20 +346,28 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
       const int s = it % kStages, sa = it % kTfAStages;
+      const int gsel = (turn + kDqShare - (it * kTfGroupsPerStage) % kDqShare) % kDqShare;  // this warp's first K-group of the tile
+      if (gsel >= kTfGroupsPerStage) continue;                                              // none: not its turn
+      TF_STAMP(it, 7);
       ok = mbar_wait_bounded(&raw_full[s], (uint32_t)(it / kStages) & 1u);
+      TF_STAMP(it, 1);
       if (ok && it >= kTfAStages) {  // the A stage is free once the MMAs of K-tile it - kTfAStages are done
         const int prev = it - kTfAStages;
         ok = mbar_wait_bounded(&mma_done[prev % kStages], (uint32_t)(prev / kStages) & 1u);
       }
       if (!ok) break;
+      TF_STAMP(it, 2);
       const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
       const uint8_t* raw = stages + (size_t)s * S::kStageBytes + q * kTfGroupsPerStage * kCell;
       uint8_t* a_out = a_stages + (size_t)sa * S::kABytes + (j >> 3) * 512 + (j & 7) * 16;
+      // ATM: this warp's lanes of tensor memory (32 (warp % 4)..), first column of the operand stage
+      const uint32_t a_tm = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + kAColBase + (uint32_t)(sa * S::kAColsPerStage);
 #pragma unroll
-      for (int g = gsel; g < kTfGroupsPerStage; g += gstep) {
+      for (int g = gsel; g < kTfGroupsPerStage; g += kDqShare) {
         if (g < ng) {
         uint4 w = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
         float sc = 0.0f;
+        uint32_t areg[16];  // ATM: the row's 32 fp16 of this K-group, column c * 4 + t = chunk c, pair t
         if constexpr (A16) {
           // fp32 all the way to one rounding: ((u - 8) * s + z) * 2^E; 0x4B000000 | u = 2^23 + u as a float
           float zr = 0.0f;
@@ -318,40 +390,76 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
               const __half2 v = __floats2half2_rn(f[t], f[t + 4]);
               o[t] = *reinterpret_cast<const uint32_t*>(&v);
             }
-            *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+            if constexpr (ATM) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) areg[c * 4 + t] = o[t];
+            } else {
+              *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
           }
         } else {
         if (have_panel) {
           w = *reinterpret_cast<const uint4*>(raw + g * kCellBytes + r * 16);
           sc = decode_scale(*reinterpret_cast<const uint16_t*>(raw + g * kCellBytes + kCellNibbleBytes + r * 2), scale_mode);
         }
-        const __half2 s2 = __float2half2_rn(sc * up);           // exact: a power-of-two multiple of a bf16 / fp16 value
+        const float s_up = sc * up;                              // exact: a power-of-two multiple of a bf16 / fp16 value
+        const __half2 s2 = __float2half2_rn(s_up);
         // (u - 8) * s2 below is exact for a bf16-encoded scale (3 + 8 bits); for an fp16-encoded one HMUL2 rounds it once
         const __half2 off = __floats2half2_rn(1032.0f, 1032.0f);  // 0x6400 | nibble = 1024 + nibble; weight = nibble - 8
+        // bf16-encoded scales, one instruction less per pair: the nibble in mantissa bits 6..9 of 0x4400 reads
+        // x = 4 + u / 4, and (u - 8) s = x (4 s) - 24 s as ONE fused multiply-add - 4 s and 24 s = 3 * 8 * s
+        // (8 + 2 significant bits) are exact in fp16, and so is the result, so nothing is rounded
+        const __half2 s4 = __float2half2_rn(4.0f * s_up), c24 = __float2half2_rn(-24.0f * s_up);
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {  // word c = k 8c..8c+7; half2 t = nibbles t and t + 4 (16 bits apart)
           uint32_t o[4];
+          if (fused_dequant) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const uint32_t moved = t == 0 ? ws[c] << 6 : t == 1 ? ws[c] << 2 : t == 2 ? ws[c] >> 2 : ws[c] >> 6;
+              const uint32_t bits = (moved & 0x03C003C0u) | 0x44004400u;
+              const __half2 v = __hfma2(*reinterpret_cast<const __half2*>(&bits), s4, c24);
+              o[t] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+          } else {
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const uint32_t bits = ((ws[c] >> (4 * t)) & 0x000F000Fu) | 0x64006400u;
             const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&bits), off), s2);
             o[t] = *reinterpret_cast<const uint32_t*>(&v);
           }
-          *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          if constexpr (ATM) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) areg[c * 4 + t] = o[t];
+          } else {
+            *reinterpret_cast<uint4*>(a_out + g * kTfGroupABytes + c * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
         }
         }
+        if constexpr (ATM) tmem_st16(a_tm + (uint32_t)(g * 16), areg);
         }
       }
-      fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
+      if constexpr (ATM) {
+        tmem_st_wait();     // the stores have landed ...
+        tc_fence_before();  // ... and are ordered before the MMAs of the thread that sees the arrival below
+      } else {
+        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
+      }
       __syncwarp();
+      TF_STAMP(it, 3);
       if (lane == 0) mbar_arrive(&a_full[sa]);
     }
     // ------------------------------------------------------------ epilogue (same four warps)
     // tensor-memory loads are warp-wide: every lane takes part, only the stores are guarded
     ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(acc_done, 0));
     tc_fence_after();
-    const int col_begin = (warp >> 2) * (NT / 2), col_end = col_begin + NT / 2;  // warps w and w + 4 split the columns
+    TF_STAMP0(1);
+    // warps w, w + 4, .. share tensor-memory lanes 32 (w % 4).. and split the columns
+    constexpr int kColSplit = kTfDequantWarps / 4, kColsPerWarp = NT / kColSplit, kChunk = kColsPerWarp >= 32 ? 32 : 16;
+    static_assert(kColsPerWarp % kChunk == 0, "column split");
+    const int col_begin = (warp >> 2) * kColsPerWarp, col_end = col_begin + kColsPerWarp;
 #pragma unroll 1
     for (int rh = 0; rh < kHalves; ++rh) {  // the 128-row halves of the tile: accumulators NT columns apart
       const int n = tile_n * ROWS + rh * kTfTileRows + (warp & 3) * 32 + lane;
@@ -360,48 +468,66 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(rh * NT);
       if (ok) {
 #pragma unroll 1
-        for (int c0 = col_begin; c0 < col_end && m0 + c0 < p.m; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld16(lane_addr + (uint32_t)c0, v);
-          tmem_ld_wait();
+        for (int c0 = col_begin; c0 < col_end && m0 + c0 < p.m; c0 += kChunk) {
+          // all loads of the chunk first (tensor memory, the rows' scales), then the arithmetic, then the stores
+          // back to back: lanes = consecutive n, one 128-byte line per store instruction
+          uint32_t v[kChunk];
+          tmem_ld16(lane_addr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[16]>(v[0]));
+          if constexpr (kChunk == 32) tmem_ld16(lane_addr + (uint32_t)(c0 + 16), reinterpret_cast<uint32_t(&)[16]>(v[16]));
+          float sc[kChunk];
+          if constexpr (!A16) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = m0 + c0 + i;
-            if (live && m < p.m) {
-              if constexpr (A16) {
-                const float val = fmaf(__uint_as_float(v[i]), down, bs);
-                static_cast<__half*>(pr.y)[(size_t)m * pr.ldy + n] = __float2half_rn(fminf(fmaxf(val, -65504.0f), 65504.0f));
-              } else {
-                const float2 h = s_hdr[c0 + i];
-                const float val = fmaf(__uint_as_float(v[i]) * down, h.x, bs);
-                const float out = clamp_flt_max(val);
-                const size_t at = (size_t)m * pr.ldy + n;
-                static_cast<float*>(pr.y)[at] = out;  // lanes = consecutive n: coalesced per m
-                for (int pe = 0; pe < pr.num_peers; ++pe) pr.y_peer[pe][at] = out;
-              }
+            for (int i = 0; i < kChunk; i += 2) {
+              const float4 h = *reinterpret_cast<const float4*>(&s_hdr[c0 + i]);  // {scale, offset} of two rows
+              sc[i] = h.x, sc[i + 1] = h.z;
+            }
+          }
+          tmem_ld_wait();
+          const int m_left = p.m - (m0 + c0);
+          if constexpr (A16) {
+            __half* yp = static_cast<__half*>(pr.y) + (size_t)(m0 + c0) * pr.ldy + n;
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+              const float val = fmaf(__uint_as_float(v[i]), down, bs);
+              if (live && i < m_left) yp[(size_t)i * pr.ldy] = __float2half_rn(fminf(fmaxf(val, -65504.0f), 65504.0f));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) v[i] = __float_as_uint(clamp_flt_max(fmaf(__uint_as_float(v[i]) * down, sc[i], bs)));
+            const size_t at0 = (size_t)(m0 + c0) * pr.ldy + n;
+            float* yp = static_cast<float*>(pr.y) + at0;
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i)
+              if (live && i < m_left) yp[(size_t)i * pr.ldy] = __uint_as_float(v[i]);
+            for (int pe = 0; pe < pr.num_peers; ++pe) {  // tensor parallelism: the same tile into every peer's y
+              float* yq = pr.y_peer[pe] + at0;
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i)
+                if (live && i < m_left) yq[(size_t)i * pr.ldy] = __uint_as_float(v[i]);
             }
           }
         }
       }
     }
     tc_fence_before();
+    TF_STAMP0(2);
   }
   __syncthreads();
   if (warp == kTfDequantWarps + 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base_any, kTmemCols);
   }
 }
 
-template <int NT, int ROWS, bool A16 = false>
+template <int NT, int ROWS, bool A16 = false, bool ATM = false>
 static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_t stream) {
-  using S = TfSmem<NT, ROWS, A16>;
+  using S = TfSmem<NT, ROWS, A16, ATM>;
   static bool configured[64] = {};  // function attributes are per device
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (!(dev >= 0 && dev < 64 && configured[dev])) {
-    e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS, A16>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    e = cudaFuncSetAttribute(w4a32_gemm_tcf16_kernel<NT, ROWS, A16, ATM>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
@@ -417,7 +543,7 @@ static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  return cudaLaunchKernelEx(&cfg, w4a32_gemm_tcf16_kernel<NT, ROWS, A16>, prm);
+  return cudaLaunchKernelEx(&cfg, w4a32_gemm_tcf16_kernel<NT, ROWS, A16, ATM>, prm);
 }
 
 // Tile shape for a launch: weight rows per CTA (128, or 256 = two accumulators sharing every loaded
@@ -439,7 +565,7 @@ static TfTile tf_tile_for(int m, int count, const int* n) {
     wide = wide && n[i] >= 4096;
   }
   TfTile t;
-  if (wide && m >= 256 && t256 * ((m + 255) / 256) >= 100) {  // (256 rows x 128: measured slower than 128 x 256, 31 vs 24 us)
+  if (MLLMB200_TF_WIDE && wide && m >= 256 && t256 * ((m + 255) / 256) >= 100) {  // (256 rows x 128: measured slower than 128 x 256, 31 vs 24 us)
     t.rows = 256;
     t.nt = 256;
     return t;
@@ -493,10 +619,11 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
     tiles += (n[i] + tile.rows - 1) / tile.rows;
   }
   if (tile.rows == 256) return launch_tf_t<256, 256>(prm, tiles, stream);
+  constexpr bool kAtm = MLLMB200_TF_ATM != 0;
   switch (nt) {
-    case 256: return launch_tf_t<256, 128>(prm, tiles, stream);
-    case 128: return launch_tf_t<128, 128>(prm, tiles, stream);
-    default: return launch_tf_t<64, 128>(prm, tiles, stream);
+    case 256: return launch_tf_t<256, 128, false, kAtm>(prm, tiles, stream);
+    case 128: return launch_tf_t<128, 128, false, kAtm>(prm, tiles, stream);
+    default: return launch_tf_t<64, 128, false, kAtm>(prm, tiles, stream);
   }
 }
 
