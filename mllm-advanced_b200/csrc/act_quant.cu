@@ -254,7 +254,7 @@ constexpr int kF16RowsPerCta = 4;   // rows 4i .. 4i+3 sit side by side in a blo
 constexpr int kF16WarpsPerRow = 8;
 __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_quant_blocks_f16_kernel(
     const float* __restrict__ x, int m_total, int k, int ldx, int num_groups, int m8_pad, uint8_t* __restrict__ blocks,
-    float2* __restrict__ hdr, int use_pdl) {
+    float2* __restrict__ hdr, int use_pdl, int* __restrict__ clear_ints, int clear_count) {
   __shared__ float s_mm[kF16RowsPerCta][kF16WarpsPerRow][2];
   if (use_pdl) {
     // x may be the previous kernel's output, and that kernel may still be reading the blocks this one overwrites:
@@ -262,6 +262,9 @@ __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_qua
     pdl_launch_dependents();
     pdl_wait_prior();
   }
+  // the K-split counters of the GEMM behind this kernel (it reads them only after this grid has finished)
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < clear_count; i += blockDim.x) clear_ints[i] = 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = warp & (kF16RowsPerCta - 1), part = warp / kF16RowsPerCta;
   const int m = blockIdx.x * kF16RowsPerCta + r;
@@ -335,7 +338,7 @@ __global__ void __launch_bounds__(kF16RowsPerCta * kF16WarpsPerRow * 32) act_qua
 }
 
 cudaError_t launch_act_quant_blocks_f16(const float* x, int m, int m_pad, int k, int ldx, uint8_t* blocks, float2* hdr,
-                                        cudaStream_t stream, int use_pdl) {
+                                        cudaStream_t stream, int use_pdl, int* clear_ints, int clear_count) {
   const int num_groups = (k + kGroup - 1) / kGroup;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(m_pad / kF16RowsPerCta), 1, 1);
@@ -348,7 +351,8 @@ cudaError_t launch_act_quant_blocks_f16(const float* x, int m, int m_pad, int k,
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  return cudaLaunchKernelEx(&cfg, act_quant_blocks_f16_kernel, x, m, k, ldx, num_groups, m_pad / 8, blocks, hdr, use_pdl);
+  return cudaLaunchKernelEx(&cfg, act_quant_blocks_f16_kernel, x, m, k, ldx, num_groups, m_pad / 8, blocks, hdr, use_pdl,
+                            clear_ints, clear_ints != nullptr ? clear_count : 0);
 }
 
 // m8_pad == 0: 48-byte records; m8_pad > 0: canonical 256-byte blocks with m8_pad blocks per K-group.

@@ -36,12 +36,16 @@ bool w4a32_gemm_tcf16_supported(int m, int k, int n);
 bool w4a32_gemm_tcf16_preferred(int m, int k, int n);
 int w4a32_gemm_tcf16_m_pad(int m, int n);
 int w4a32_gemm_tcf16_m_pad_max(int m);
-cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t, int use_pdl);
-cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t, int use_pdl = 0);
+cudaError_t launch_w4a32_gemm_tcf16(const uint8_t*, const float2*, const void*, float*, int, int, int, int, cudaStream_t, int use_pdl,
+                                    int* split_sync, int split_sync_ints);
+cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t, int use_pdl = 0,
+                                        int* clear_ints = nullptr, int clear_count = 0);
 int w4a32_gemm_tcf16_tile_grouped(int m, int count, const int* n);
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
                                             const int*, const int*, cudaStream_t, int num_peers = 0,
-                                            float* const* y_peers = nullptr, int use_pdl = 0);
+                                            float* const* y_peers = nullptr, int use_pdl = 0, int* split_sync = nullptr,
+                                            int split_sync_ints = 0);
+constexpr int kSplitSyncInts = 1024;  // K-split counters of the fp16 tile GEMM at the end of the workspace (two per output tile)
 
 bool w4a32_gemm_stream_supported(int m, int k, int count, const int* n);
 size_t w4a32_gemm_stream_act_bytes(int m, int k);
@@ -164,6 +168,7 @@ int mllmb200_w4a32_unpack_device(const void* tiled_dev, int row_count, int K, vo
 int mllmb200_w4a32_workspace_size(int M, int K, size_t* bytes) {
   if (!bytes || M <= 0 || K <= 0) return MLLMB200_INVALID_ARG;
   *bytes = ws_rec_bytes(M, K) + align_up((size_t)M * sizeof(float2), 256);
+  if (w4a32_gemm_tcf16_supported(M, K, 1)) *bytes += kSplitSyncInts * sizeof(int);
   return MLLMB200_OK;
 }
 
@@ -227,8 +232,11 @@ int mllmb200_w4a32_linear_forward_ex(const float* x_dev, const void* tiled_dev, 
     if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
     uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
     float2* hdr16 = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
-    cudaError_t e16 = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N), K, ldx, blocks, hdr16, st, use_pdl);
-    if (e16 == cudaSuccess) e16 = launch_w4a32_gemm_tcf16(blocks, hdr16, tiled_dev, y_dev, M, K, N, ldy, st, use_pdl);
+    int* sync16 = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(hdr16) + align_up((size_t)M * sizeof(float2), 256));
+    cudaError_t e16 = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, N), K, ldx, blocks, hdr16, st, use_pdl,
+                                                  sync16, kSplitSyncInts);
+    if (e16 == cudaSuccess)
+      e16 = launch_w4a32_gemm_tcf16(blocks, hdr16, tiled_dev, y_dev, M, K, N, ldy, st, use_pdl, sync16, kSplitSyncInts);
     return e16 == cudaSuccess ? MLLMB200_OK : cuda_fail(e16);
   }
   uint8_t* a_rec;
@@ -304,9 +312,11 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
       float2* hdr = reinterpret_cast<float2*>(blocks + ws_rec_bytes(M, K));
       const int nt = w4a32_gemm_tcf16_tile_grouped(M, count, N);
       const int pdl = (flags >> 8) & 1;
-      cudaError_t e = launch_act_quant_blocks_f16(x_dev, M, (M + nt - 1) / nt * nt, K, ldx, blocks, hdr, st_grp, pdl);
+      int* sync = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(hdr) + align_up((size_t)M * sizeof(float2), 256));
+      cudaError_t e = launch_act_quant_blocks_f16(x_dev, M, (M + nt - 1) / nt * nt, K, ldx, blocks, hdr, st_grp, pdl, sync, kSplitSyncInts);
       if (e == cudaSuccess)
-        e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, count, tiled_dev, y_dev, N, ldy, st_grp, 0, nullptr, pdl);
+        e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, count, tiled_dev, y_dev, N, ldy, st_grp, 0, nullptr, pdl, sync,
+                                            kSplitSyncInts);
       return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
     }
   }

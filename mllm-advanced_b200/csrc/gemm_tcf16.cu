@@ -51,6 +51,9 @@
 #ifndef MLLMB200_TF_FUSED_DEQUANT
 #define MLLMB200_TF_FUSED_DEQUANT 1
 #endif
+#ifndef MLLMB200_TF_SPLIT_K
+#define MLLMB200_TF_SPLIT_K 1
+#endif
 #ifndef MLLMB200_TF_ATM  // dequantized weight operand in tensor memory (128-row tiles)
 #define MLLMB200_TF_ATM 1
 #endif
@@ -99,6 +102,11 @@ struct TfParams {
   const float2* a_hdr;      // [m] {lhs_scale, a_off bits}; unused (may be null) on the W4A16 path
   int m, k, num_groups, m8_pad, num_problems;
   int use_pdl;  // programmatic dependent launch: everything up to the first read of the activations overlaps the previous kernel
+  // K split in two (grids that would leave most SMs idle): the two CTAs of an output tile each take half of the
+  // K-tiles; whichever finishes its half first parks its raw accumulators in the tile's place in y, the other one
+  // adds them to its own and runs the epilogue.  split_sync: two zeroed ints per output tile {arrivals, parked}.
+  int splits;
+  int* split_sync;
   TfProblem prob[kTfMaxProblems];
 };
 
@@ -171,10 +179,11 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   // stay resident.
 #if MLLMB200_TF_RASTER_M
   const int linear = (int)(blockIdx.y * gridDim.x + blockIdx.x);
-  const int bx = linear / (int)gridDim.y, tile_m = linear % (int)gridDim.y;
+  const int bx = linear / (int)gridDim.y, tile_ms = linear % (int)gridDim.y;
 #else
-  const int bx = blockIdx.x, tile_m = blockIdx.y;
+  const int bx = blockIdx.x, tile_ms = blockIdx.y;
 #endif
+  const int tile_m = tile_ms / p.splits, split = tile_ms % p.splits;  // the halves of a tile: neighbours in dispatch order
 #ifdef MLLMB200_TF_TRACE
   const bool traced = linear == (int)(gridDim.x * gridDim.y) / 2 && lane == 0 && (warp == 0 || warp >= kTfDequantWarps) && g_gs_trace != nullptr;
   if (warp == 0) TF_STAMP0(0);
@@ -189,7 +198,10 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   }
   const int tile_n = bx - pr.tile_begin;
   const int panel0 = tile_n * kPanels, m0 = tile_m * NT;
-  const int k_tiles = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
+  const int k_tiles_all = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
+  // this CTA's K-tiles: [it0, it0 + k_tiles) of the matrix; `it` below counts from 0 within them
+  const int it0 = split == 0 ? 0 : k_tiles_all / 2;
+  const int k_tiles = p.splits == 1 ? k_tiles_all : (split == 0 ? k_tiles_all / 2 : k_tiles_all - k_tiles_all / 2);
   constexpr uint32_t kTmemCols = ATM ? 512u : (uint32_t)(kHalves * NT) < 32u ? 32u : (uint32_t)(kHalves * NT);
   constexpr uint32_t kAColBase = (uint32_t)NT;  // first operand column (ATM)
   // Dequant work: kRowSets sets of 32 weight rows, kDqShare warps per set; K-group g of K-tile it goes to the warp
@@ -227,7 +239,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     // for both together, with the first part that is requested.
     auto request = [&](int it, int parts) {
       const int s = it % kStages;
-      const int g0 = it * kTfGroupsPerStage;
+      const int g0 = (it0 + it) * kTfGroupsPerStage;
       const int ng = min(kTfGroupsPerStage, p.num_groups - g0);
       uint8_t* st = stages + (size_t)s * S::kStageBytes;
       if ((parts & 1) && lane == 0) mbar_arrive_expect_tx(&raw_full[s], (uint32_t)(np * ng * kCell + ng * NT * 64));
@@ -288,7 +300,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
         TF_STAMP(it, 5);
         tc_fence_after();
         if (issuer) {
-        const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
+        const int ng = min(kTfGroupsPerStage, p.num_groups - (it0 + it) * kTfGroupsPerStage);
         uint8_t* st = stages + (size_t)s * S::kStageBytes;
         const uint32_t b_addr = smem_u32(st + S::kRawBytes), a_addr = smem_u32(a_stages + (size_t)sa * S::kABytes);
         // K-major, no swizzle: 16-byte K chunks of a row 128 bytes apart, 8-row groups 512 bytes apart
@@ -346,7 +358,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     bool ok = true;
     for (int it = 0; it < k_tiles && ok; ++it) {
       const int s = it % kStages, sa = it % kTfAStages;
-      const int gsel = (turn + kDqShare - (it * kTfGroupsPerStage) % kDqShare) % kDqShare;  // this warp's first K-group of the tile
+      const int gsel = (turn + kDqShare - (it * kTfGroupsPerStage) % kDqShare) % kDqShare;  // (turns count from this CTA's first tile)  // this warp's first K-group of the tile
       if (gsel >= kTfGroupsPerStage) continue;                                              // none: not its turn
       TF_STAMP(it, 7);
       ok = mbar_wait_bounded(&raw_full[s], (uint32_t)(it / kStages) & 1u);
@@ -357,7 +369,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
       }
       if (!ok) break;
       TF_STAMP(it, 2);
-      const int ng = min(kTfGroupsPerStage, p.num_groups - it * kTfGroupsPerStage);
+      const int ng = min(kTfGroupsPerStage, p.num_groups - (it0 + it) * kTfGroupsPerStage);
       const uint8_t* raw = stages + (size_t)s * S::kStageBytes + q * kTfGroupsPerStage * kCell;
       uint8_t* a_out = a_stages + (size_t)sa * S::kABytes + (j >> 3) * 512 + (j & 7) * 16;
       // ATM: this warp's lanes of tensor memory (32 (warp % 4)..), first column of the operand stage
@@ -456,6 +468,33 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(acc_done, 0));
     tc_fence_after();
     TF_STAMP0(1);
+    // K split: 0 = whole K here; 1 = first of the tile's two CTAs to finish (parks its accumulators in y);
+    // 2 = second (adds the parked ones).  The second waits - bounded - only for a CTA that is already in its epilogue.
+    int role = 0;
+    int* tile_sync = nullptr;
+    if constexpr (!A16) {
+      if (p.splits > 1) {
+        tile_sync = p.split_sync + 2 * (bx * (int)(gridDim.y / p.splits) + tile_m);
+        int* s_role = reinterpret_cast<int*>(tmem_base_slot + 1);
+        if (tid == 0) {
+          int r = atomicAdd(tile_sync, 1) == 0 ? 1 : 2;
+          if (r == 2) {
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(tile_sync + 1) == 0) {
+              if (clock64() - t0 > (1ll << 31)) {
+                atomicOr(&g_device_status, kDevStatusTimeout);
+                r = 3;  // gave up: no result for this tile, the status word says so
+                break;
+              }
+            }
+          }
+          *s_role = r;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kTfDequantWarps * 32) : "memory");
+        role = *s_role;
+        if (role == 3) ok = false;
+      }
+    }
     // warps w, w + 4, .. share tensor-memory lanes 32 (w % 4).. and split the columns
     constexpr int kColSplit = kTfDequantWarps / 4, kColsPerWarp = NT / kColSplit, kChunk = kColsPerWarp >= 32 ? 32 : 16;
     static_assert(kColsPerWarp % kChunk == 0, "column split");
@@ -492,10 +531,23 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
               if (live && i < m_left) yp[(size_t)i * pr.ldy] = __float2half_rn(fminf(fmaxf(val, -65504.0f), 65504.0f));
             }
           } else {
-#pragma unroll
-            for (int i = 0; i < kChunk; ++i) v[i] = __float_as_uint(clamp_flt_max(fmaf(__uint_as_float(v[i]) * down, sc[i], bs)));
             const size_t at0 = (size_t)(m0 + c0) * pr.ldy + n;
             float* yp = static_cast<float*>(pr.y) + at0;
+            if (role == 1) {  // park the raw sums
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i)
+                if (live && i < m_left) __stcg(yp + (size_t)i * pr.ldy, __uint_as_float(v[i]));
+              continue;
+            }
+            if (role == 2) {  // a + b = b + a: the result does not depend on which half finished first
+              float parked[kChunk];
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i) parked[i] = (live && i < m_left) ? __ldcg(yp + (size_t)i * pr.ldy) : 0.0f;
+#pragma unroll
+              for (int i = 0; i < kChunk; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + parked[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) v[i] = __float_as_uint(clamp_flt_max(fmaf(__uint_as_float(v[i]) * down, sc[i], bs)));
 #pragma unroll
             for (int i = 0; i < kChunk; ++i)
               if (live && i < m_left) yp[(size_t)i * pr.ldy] = __uint_as_float(v[i]);
@@ -508,6 +560,11 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
           }
         }
       }
+    }
+    if (role == 1) {  // every parked value is visible before the flag is
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kTfDequantWarps * 32) : "memory");
+      if (tid == 0) st_release_gpu(tile_sync + 1, 1);
     }
     tc_fence_before();
     TF_STAMP0(2);
@@ -532,7 +589,7 @@ static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT));
+  cfg.gridDim = dim3((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT * prm.splits));
   cfg.blockDim = dim3(kTfThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = stream;
@@ -556,6 +613,13 @@ static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_
 struct TfTile {
   int rows, nt;
 };
+static int tf_sm_count() {
+  static int sms[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 148;
+  return sms[dev];
+}
 static TfTile tf_tile_for(int m, int count, const int* n) {
   long long t128 = 0, t256 = 0;
   bool wide = true;  // 256-row tiles only for matrices with at least 4096 rows
@@ -589,9 +653,12 @@ bool w4a32_gemm_tcf16_preferred(int m, int k, int n) { return w4a32_gemm_tcf16_s
 // Up to four matrices that share x in ONE launch (their weight tiles side by side in the grid):
 // the activation blocks must be padded to m_pad = a multiple of the tile width chosen by
 // w4a32_gemm_tcf16_tile_grouped for the same arguments.
+// split_sync (optional): split_sync_ints ints that are ZERO when the kernel starts (the quantization kernel in front of
+// it clears them); with them, launches that would fill less than half of the GPU split K in two.
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float2* a_hdr, int m, int k, int count,
                                             const void* const* tiled, float* const* y, const int* n, const int* ldy,
-                                            cudaStream_t stream, int num_peers, float* const* y_peers, int use_pdl) {
+                                            cudaStream_t stream, int num_peers, float* const* y_peers, int use_pdl,
+                                            int* split_sync, int split_sync_ints) {
   if (count < 1 || count > kTfMaxProblems) return cudaErrorInvalidValue;
   if (num_peers > 0 && (count != 1 || num_peers > kTfMaxPeers || y_peers == nullptr)) return cudaErrorInvalidValue;
   const TfTile tile = tf_tile_for(m, count, n);
@@ -618,7 +685,16 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
     for (int j = 0; j < prm.prob[i].num_peers; ++j) prm.prob[i].y_peer[j] = y_peers[j];
     tiles += (n[i] + tile.rows - 1) / tile.rows;
   }
+  prm.splits = 1;
+  prm.split_sync = split_sync;
   if (tile.rows == 256) return launch_tf_t<256, 256>(prm, tiles, stream);
+  {
+    const int m_tiles = (m + nt - 1) / nt, ctas = tiles * m_tiles;
+    const int groups_per_tile = nt >= 256 ? 2 : 4;  // (TfSmem::kGroups of the 128-row tiles)
+    const int k_tiles = (prm.num_groups + groups_per_tile - 1) / groups_per_tile;
+    if (MLLMB200_TF_SPLIT_K && split_sync != nullptr && 2 * ctas <= tf_sm_count() && k_tiles >= 8 && 2 * ctas <= split_sync_ints)
+      prm.splits = 2;
+  }
   constexpr bool kAtm = MLLMB200_TF_ATM != 0;
   switch (nt) {
     case 256: return launch_tf_t<256, 128, false, kAtm>(prm, tiles, stream);
@@ -646,6 +722,7 @@ cudaError_t launch_w4a16_gemm_tcf16_grouped(const uint8_t* a_blocks, int m, int 
   prm.num_groups = (k + kGroup - 1) / kGroup;
   prm.m8_pad = (m + nt - 1) / nt * nt / 8;
   prm.num_problems = count;
+  prm.splits = 1;
   int tiles = 0;
   for (int i = 0; i < count; ++i) {
     prm.prob[i].tiled = static_cast<const uint8_t*>(tiled[i]);
@@ -669,8 +746,9 @@ cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, 
 }
 
 cudaError_t launch_w4a32_gemm_tcf16(const uint8_t* a_blocks, const float2* a_hdr, const void* tiled, float* y, int m, int k,
-                                    int n, int ldy, cudaStream_t stream, int use_pdl) {
-  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream, 0, nullptr, use_pdl);
+                                    int n, int ldy, cudaStream_t stream, int use_pdl, int* split_sync, int split_sync_ints) {
+  return launch_w4a32_gemm_tcf16_grouped(a_blocks, a_hdr, m, k, 1, &tiled, &y, &n, &ldy, stream, 0, nullptr, use_pdl,
+                                         split_sync, split_sync_ints);
 }
 
 }  // namespace mllmb200

@@ -37,10 +37,11 @@ cudaError_t launch_w4a32_gemv_stream(int count, const float* const* x, const int
 bool w4a32_gemv_stream_supported(int m, int count, const int* k, const int* n);
 bool w4a32_gemm_tcf16_preferred(int m, int k, int n);
 int w4a32_gemm_tcf16_m_pad(int m, int n);
-cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t, int use_pdl = 0);
+cudaError_t launch_act_quant_blocks_f16(const float*, int, int, int, int, uint8_t*, float2*, cudaStream_t, int use_pdl = 0,
+                                        int* clear_ints = nullptr, int clear_count = 0);
 cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t*, const float2*, int, int, int, const void* const*, float* const*,
                                             const int*, const int*, cudaStream_t, int num_peers, float* const* y_peers,
-                                            int use_pdl = 0);
+                                            int use_pdl = 0, int* split_sync = nullptr, int split_sync_ints = 0);
 
 constexpr int kTpMaxRanks = 8;
 constexpr long long kTpWaitTicks = 1ll << 32;  // ~2 s: ranks reach a collective call milliseconds apart at worst

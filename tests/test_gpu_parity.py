@@ -367,6 +367,35 @@ def test_tcgen05_fp16_gemm_vs_oracle(orc, m, k, n):
     print(f"tcgen05 fp16 m={m} k={k} n={n}: max|diff| / rms = {float(np.max(np.abs(y - ref))) / rms:.2e}")
 
 
+@pytest.mark.parametrize("m,k,n", [(128, 1056, 200), (512, 8960, 1536), (260, 2080, 384), (64, 4128, 96), (128, 1024, 256)])
+def test_tcgen05_fp16_gemm_k_split(orc, m, k, n):
+    """Launches that would leave most SMs idle split K between two CTAs per output tile; the half that finishes
+    first parks its sums in the tile's place in y.  Odd and ragged K-tile counts, an output buffer that starts as NaN
+    (nothing may depend on what y held), a row stride wider than N, and the same bits on every repeat whichever
+    half finishes first."""
+    rng = np.random.default_rng(m + 3 * k + n)
+    x, w, b = make_case(rng, m, n, k, x_scale=rng.uniform(0.3, 2.0))
+    blob = mb.quant_prepack(w, b)
+    q, s, _ = mb.blob_sections(blob)
+    ref = orc.linear(x, np.ascontiguousarray(q), np.ascontiguousarray(s), b)
+    wt = mb.W4A32Weights.from_blob(blob)
+    xd = torch.from_numpy(x).cuda()
+    buf = torch.full((m, n + 24), float("nan"), device="cuda")
+    y = buf[:, :n]
+    first = None
+    for _ in range(6):
+        buf.fill_(float("nan"))
+        mb.linear_forward(xd, wt, out=y, kernel=mb.KERNEL_TC_F16)
+        torch.cuda.synchronize()
+        mb.check_device_status()
+        if first is None:
+            first = y.clone()
+            assert_close(first.cpu().numpy(), ref, f"k-split m={m} k={k} n={n}")
+        else:
+            assert torch.equal(y, first)
+        assert bool(torch.isnan(buf[:, n:]).all()), "wrote outside the N columns"
+
+
 @pytest.mark.parametrize("mode", [mb.SCALE_BF16_RNE, mb.SCALE_FP16])
 @pytest.mark.parametrize("m,k,n", [(128, 1536, 256), (512, 1536, 8960), (256, 8960, 1536), (200, 1176, 1280)])
 def test_tcgen05_fp16_gemm_other_scale_encodings(orc, m, k, n, mode):
