@@ -320,6 +320,12 @@ def run_gpu(args):
         xp = {k: torch.randn((PREFILL_M, k), device="cuda", generator=gen) for k in (1536, 8960)}
         kern = mb.KERNEL_TC_F16 if args.prefill_f16 else mb.KERNEL_AUTO
         for _ in range(max(1, args.steps)):
+            if args.prefill_grouped:  # the call structure of prefill_fastest_grouped: 4 quantizations + 4 GEMM launches
+                mb.linear_forward_grouped(xp[1536], lw[0:3], workspace=ws, policy=mb.KERNEL_FASTEST)
+                mb.linear_forward(xp[1536], lw[3], workspace=ws, kernel=mb.KERNEL_FASTEST)
+                mb.linear_forward_grouped(xp[1536], lw[4:6], workspace=ws, policy=mb.KERNEL_FASTEST)
+                mb.linear_forward(xp[8960], lw[6], workspace=ws, kernel=mb.KERNEL_FASTEST)
+                continue
             for w in lw:
                 mb.linear_forward(xp[w.k], w, workspace=ws, kernel=kern)
         torch.cuda.synchronize()
@@ -1243,6 +1249,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline number only (used under ncu)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="run one decoder layer's seven linears at M=512 once and exit (small target for ncu)")
+    ap.add_argument("--prefill-grouped", action="store_true",
+                    help="with --prefill-only: (q,k,v) and (gate,up) as grouped calls, fastest policy")
     ap.add_argument("--prefill-f16", action="store_true", help="with --prefill-only: use the fp16 tensor-core path (kernel 4)")
     ap.add_argument("--fast-prefill", action="store_true", help="time the prefill linears on 2 layers instead of 28")
     args = ap.parse_args()

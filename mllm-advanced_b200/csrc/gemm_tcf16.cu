@@ -17,25 +17,30 @@
 // to 14 bits and the HMUL2 below rounds it to 11: a relative error of at most 2^-12 per weight, which
 // shows up as about 1.5e-4 * rms(y) per output; stated bound for that mode 2e-3 * rms(y) (the exact
 // kernels 1-3 remain available for it).  Scales more than 2^24 below the matrix maximum fall into fp16
-// subnormals and lose low bits (contribution < 2^-25 of the largest group's).
+// subnormals and lose low bits (contribution < 2^-24 of the largest group's).
 //
 //   y[m,n] = lhs_scale[m] * 2^-E * sum_k A[n,k] B[m,k] + bias[n]
 //
 // Tile: 128 weight rows (MMA M, tensor-memory lanes) x NT activation rows (MMA N, columns), one
-// accumulator for the whole K loop, one CTA per SM.  Warp roles (320 threads):
-//   warps 0-7  dequant: thread j (mod 128) expands weight row j of the tile, warps 0-3 the first and
-//              warps 4-7 the second K-group of a stage (16 bytes of nibbles -> 64 bytes of
-//              fp16 per K-group: mask / or / HSUB2 / HMUL2 on pairs of nibbles 16 bits apart) into the
-//              canonical K-major core-matrix layout; after the loop the same warps run the epilogue
-//              (warp w owns tensor-memory lanes 32 (w % 4).. and half of the columns)
-//   warp 8     producer: bulk copies (cp.async.bulk) of the raw weight cells and of the activation
-//              blocks, which act_quant_blocks_f16_kernel already wrote in operand layout
-//   warp 9     MMA issuer (one lane; two K=16 instructions per K-group) and tensor-memory owner
-// Stages of 2 K-groups: kStages (4-7) loaded-data stages {raw cells 4.5 KB, B operand NT*128 B} and as
-// many stages of the dequantized A operand (16 KB).  Every mbarrier wait is bounded.
-// Measured on the Qwen2-1.5B layer shapes at M = 512: gate/up (N = 8960, NT = 256, 140 CTAs) 22.5 us =
-// 0.63 PFLOP/s; the K loop is bound by the issuing thread (one K-tile = 4 MMAs + 2 waits + 1 commit
-// ~ 700-900 cycles) and, for N = 1536 (48 CTAs), by the unfilled GPU.
+// accumulator for the whole K loop, one CTA per SM.  Warp roles (576 threads):
+//   warps 0-15 dequant: thread = weight row 32 (w % 4) + lane of the tile; the four warps of a row set take turns
+//              over the K-groups (16 bytes of nibbles -> 64 bytes of fp16 per K-group: shift / mask-or / one
+//              fused multiply-add on pairs of nibbles 16 bits apart) and write the row's 16 columns of the
+//              A operand into TENSOR memory with tcgen05.st (256-row tiles: two warps per row set, operand in
+//              shared memory in the canonical K-major core-matrix layout); after the loop the same warps run
+//              the epilogue (warp w owns tensor-memory lanes 32 (w % 4).. and a quarter of the columns)
+//   warp 16    producer: bulk copies (cp.async.bulk) of the raw weight cells (evict-first: each is read once
+//              per wave) and of the activation blocks, which act_quant_blocks_f16_kernel already wrote in
+//              operand layout
+//   warp 17    MMA issuer and tensor-memory owner: the whole warp runs the loop, one elected lane issues
+//              (two K=16 instructions per K-group, A from tensor memory, B through a shared-memory descriptor)
+// Stages of 2 (NT = 256) or 4 K-groups: a ring of 5-7 loaded-data stages {raw cells, B operand NT*64 B per
+// group} in shared memory and up to as many operand stages in tensor-memory columns [NT, 512).  Every wait
+// (mbarrier, split-K flag) is bounded.  CTAs are renumbered so that the row tiles of one weight tile are
+// dispatched side by side; launches that would fill less than half of the SMs split K between two CTAs per
+// output tile.
+// Measured at M = 512 on the Qwen2-1.5B layer shapes (cold caches, one launch each): q,k,v grouped 17 us,
+// o 17 us, gate+up grouped 36 us, down 34 us; config 4 (28672 x 8192, M = 2048): 0.84 ms = 1145 TFLOP/s.
 #include <cuda_fp16.h>
 
 #include "device_common.cuh"
@@ -604,12 +609,10 @@ static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_
 }
 
 // Tile shape for a launch: weight rows per CTA (128, or 256 = two accumulators sharing every loaded
-// activation block) and activation rows per tile.  A tcgen05.mma costs its issuing thread ~100
-// cycles whatever its size and 128 x NT x 16 takes NT / 2 cycles of tensor-core time, so narrow
-// activation tiles are issue-bound (measured: K = 8960, N = 1536, M = 512: 74 us at NT = 64 as at 128);
-// on grids that fill the GPU the 128-row tile is bound by L2 traffic for the activation operand,
-// which every weight tile re-reads - the 256-row tile halves it (config 4, M = 2048: 974 -> 1014 TFLOP/s;
-// with 8 MMAs per K-tile the issuing thread is then the limit).
+// activation block) and activation rows per tile.  128 x NT x 16 takes NT / 2 cycles of tensor-core time
+// and the dequantization of a K-group costs the same whatever NT, so narrow activation tiles are bound by
+// the dequant warps; on grids that fill the GPU the 128-row tile moves twice the bytes per FLOP through L2
+// (the activation operand, which every weight tile re-reads) - config 4, M = 2048: 0.84 ms with either.
 struct TfTile {
   int rows, nt;
 };
