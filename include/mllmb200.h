@@ -131,7 +131,10 @@ MLLMB200_API int mllmb200_w4a32_linear_forward(const float* x_dev, const void* t
  * 3 tcgen05 kind::i8 GEMM (exact int32 group sums, as the reference), 4 tcgen05 fp16 GEMM (M >= 64: group
  * scales folded into an fp16 weight operand - exact for bf16-encoded scales, rounded to fp16's 11 bits
  * (relative error <= 2^-11 per weight) for MLLMB200_SCALE_FP16 - fp32 accumulation over all of K in
- * tensor memory; same 1e-3*rms bound; auto never picks it), 5 fastest: kernel 4 for M >= 128, else auto,
+ * tensor memory; same 1e-3*rms bound; auto never picks it; launches that would fill less than half of the SMs
+ * split K between two CTAs per output tile, and y holds one half's partial sums for a moment during the
+ * call - deterministic, but y is scratch until the call's work on the stream has finished), 5 fastest: kernel 4
+ * for M >= 128, else auto,
  * 6 the two-launch GEMV (activation-quantization kernel + one-shot GEMV), kept for comparison,
  * 7 streaming tensor-core GEMM for small batches (M <= 64; what auto picks for 5 <= M <= 64): the weight cells are
  * spread over all SMs as in the GEMV, the per-group integer products run as mma.sync u8 x s8 (exact int32 group

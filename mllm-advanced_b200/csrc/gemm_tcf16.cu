@@ -128,9 +128,8 @@ template <int NT, int ROWS, bool A16 = false, bool ATM = false>
 struct TfSmem {
   static_assert(!ATM || ROWS == 128, "the tensor-memory operand is for single-accumulator tiles");
   static constexpr int kCell = A16 ? kCellBytesA16 : kCellBytes;
-  // K-groups per stage.  Every stage costs the MMA-issuing thread two barrier waits and a commit
-  // (~300 cycles) on top of ~100 cycles per tcgen05.mma issue (measured with clock64).
-  static constexpr int kGroups = (NT >= 256 || ROWS > 128) ? 2 : 4;  // (NT = 256 has room for only 2 stages of 4 groups: measured slower, 25 vs 22 us)
+  // K-groups per stage.  Every stage costs the MMA-issuing warp a barrier wait and a commit.
+  static constexpr int kGroups = (NT >= 256 || ROWS > 128) ? 2 : 4;
   static constexpr int kPanels = ROWS / kPanelRows;
   static constexpr int kRawBytes = kPanels * kGroups * kCell;
   static constexpr int kBBytes = kGroups * NT * 64;
