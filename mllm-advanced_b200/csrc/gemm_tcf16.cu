@@ -62,6 +62,9 @@
 #ifndef MLLMB200_TF_ATM  // dequantized weight operand in tensor memory (128-row tiles)
 #define MLLMB200_TF_ATM 1
 #endif
+#ifndef MLLMB200_TF_ATM_A16  // the same for the W4A16 instantiation (measured: no faster - its fp32 dequant is the bound)
+#define MLLMB200_TF_ATM_A16 0
+#endif
 #ifndef MLLMB200_TF_WIDE  // 256-row tiles (two accumulators, operand in shared memory) where tf_tile_for picks them
 #define MLLMB200_TF_WIDE 1
 #endif
@@ -736,10 +739,11 @@ cudaError_t launch_w4a16_gemm_tcf16_grouped(const uint8_t* a_blocks, int m, int 
     prm.prob[i].bias_off = make_tiled_header_a16(n[i], k, 0).bias_off;
     tiles += (n[i] + 127) / 128;
   }
+  constexpr bool kAtm = MLLMB200_TF_ATM != 0 && MLLMB200_TF_ATM_A16 != 0;
   switch (nt) {
-    case 256: return launch_tf_t<256, 128, true>(prm, tiles, stream);
-    case 128: return launch_tf_t<128, 128, true>(prm, tiles, stream);
-    default: return launch_tf_t<64, 128, true>(prm, tiles, stream);
+    case 256: return launch_tf_t<256, 128, true, kAtm>(prm, tiles, stream);
+    case 128: return launch_tf_t<128, 128, true, kAtm>(prm, tiles, stream);
+    default: return launch_tf_t<64, 128, true, kAtm>(prm, tiles, stream);
   }
 }
 cudaError_t launch_w4a16_gemm_tcf16(const uint8_t* a_blocks, const void* tiled, void* y_f16, int m, int k, int n, int ldy,
