@@ -1189,8 +1189,10 @@ def run_tp(args, torch, mb, dist, rank, world, gen):
         res["nvlink_bound_ms"] = recv_bytes / 770e9 * 1e3  # every rank receives the other ranks' blocks; 770 GB/s measured peer copy
         res["tflops" if m > 1 else "GBs_weights_alg"] = (2.0 * m * k * n / (res["tp_fused_ms"] * 1e-3) / 1e12 if m > 1 else
                                                          algorithmic_bytes(m, k, n, False) / (res["tp_fused_ms"] * 1e-3) / 1e9)
-        # the gathered result against the unsharded one computed here: the GEMM bit for bit (a tile's sum does not depend
-        # on how the rows are sharded), the GEMV within 1e-5 * rms (the shard splits K over its CTAs differently)
+        # the gathered result against the unsharded one computed here, within 1e-5 * rms (GEMV; the shard splits K over
+        # its CTAs differently) or 1e-4 * rms (GEMM, K = 8192: either launch splits K in two on the tiles left over after
+        # its own last full wave - other orders of the same fp32 additions; measured 1.2e-5), and bit for bit between
+        # the ranks and between the two gather modes
         mb.linear_forward(x, full, out=y1, workspace=ws_full, kernel=kern)
         ok = True
         for mode in (tp.GATHER_PEER_STORES, tp.GATHER_NCCL):
@@ -1200,11 +1202,19 @@ def run_tp(args, torch, mb, dist, rank, world, gen):
             y = tpl.forward(x, gather=mode, kernel=kern)
             torch.cuda.synchronize()
             mb.check_device_status()
-            if m > 1:
-                ok = ok and bool(torch.equal(y, y1))
-            else:
-                rms = float(y1.pow(2).mean().sqrt())
-                ok = ok and float((y - y1).abs().max()) <= 1e-5 * rms
+            rms = float(y1.pow(2).mean().sqrt())
+            rel = float((y - y1).abs().max()) / rms
+            res["max_diff_over_rms"] = max(res.get("max_diff_over_rms", 0.0), rel)
+            digest = y.view(torch.int32).to(torch.int64).sum().reshape(1)  # same bits on every rank <=> same digest
+            lo, hi = digest.clone(), digest.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            res["ranks_agree"] = res.get("ranks_agree", True) and int(lo.item()) == int(hi.item())
+            if mode == tp.GATHER_PEER_STORES:
+                y_fused = y.clone()
+            elif m > 1:
+                res["modes_agree"] = bool(torch.equal(y, y_fused))
+            ok = ok and rel <= (1e-5 if m == 1 else 1e-4) and res["ranks_agree"] and res.get("modes_agree", True)
             dist.barrier()
         flag = torch.tensor([1.0 if ok else 0.0], device="cuda")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)

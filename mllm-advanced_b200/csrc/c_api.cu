@@ -76,6 +76,11 @@ static inline size_t ws_rec_bytes(int m, int k) {
   return align_up(big > blk16 ? big : blk16, 256);
 }
 size_t w4a32_ws_rec_bytes(int m, int k) { return ws_rec_bytes(m, k); }  // for tp.cu
+// the K-split counters of the fp16 tile GEMM: behind the row headers of a workspace of workspace_size(m, k) bytes
+int* w4a32_ws_split_sync(void* ws_dev, int m, int k) {
+  return reinterpret_cast<int*>(static_cast<uint8_t*>(ws_dev) + ws_rec_bytes(m, k) + align_up((size_t)m * sizeof(float2), 256));
+}
+int w4a32_ws_split_sync_ints() { return kSplitSyncInts; }
 }  // namespace mllmb200
 
 using namespace mllmb200;

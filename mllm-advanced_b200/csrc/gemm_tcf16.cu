@@ -47,9 +47,6 @@
 #include "layout_a16.h"
 #include "tcgen05_common.cuh"
 
-#ifndef MLLMB200_TF_RASTER_M
-#define MLLMB200_TF_RASTER_M 1
-#endif
 #ifndef MLLMB200_TF_WEIGHT_HINT
 #define MLLMB200_TF_WEIGHT_HINT 1
 #endif
@@ -110,10 +107,12 @@ struct TfParams {
   const float2* a_hdr;      // [m] {lhs_scale, a_off bits}; unused (may be null) on the W4A16 path
   int m, k, num_groups, m8_pad, num_problems;
   int use_pdl;  // programmatic dependent launch: everything up to the first read of the activations overlaps the previous kernel
-  // K split in two (grids that would leave most SMs idle): the two CTAs of an output tile each take half of the
-  // K-tiles; whichever finishes its half first parks its raw accumulators in the tile's place in y, the other one
-  // adds them to its own and runs the epilogue.  split_sync: two zeroed ints per output tile {arrivals, parked}.
-  int splits;
+  // Grid: one CTA per output tile for tiles [0, split_begin), two per tile from there on (m_tiles = tiles along M).
+  // K split in two (grids that would leave most SMs idle, and the tiles left over after the last full wave): the
+  // two CTAs of an output tile each take half of the K-tiles; whichever finishes its half first parks its raw
+  // accumulators in the tile's place in y, the other one adds them to its own and runs the epilogue.
+  // split_sync: two zeroed ints per split output tile {arrivals, parked}.
+  int m_tiles, split_begin;
   int* split_sync;
   TfProblem prob[kTfMaxProblems];
 };
@@ -180,19 +179,17 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
 
   const int tid = threadIdx.x, lane = tid & 31, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // (warp-uniform for the compiler)
   if (p.use_pdl) pdl_launch_dependents();  // the next kernel waits for this whole grid before it touches anything we use
-  // CTAs are dispatched in order of blockIdx.x, then y.  Renumbered so that the tiles that share a weight tile (same
-  // columns of W, different rows of x) are neighbours in that order: they run in the same wave, the weight tile comes
-  // from DRAM once and the rest of them find it in L2, while the activation blocks, which every wave reads in full,
-  // stay resident.
-#if MLLMB200_TF_RASTER_M
-  const int linear = (int)(blockIdx.y * gridDim.x + blockIdx.x);
-  const int bx = linear / (int)gridDim.y, tile_ms = linear % (int)gridDim.y;
-#else
-  const int bx = blockIdx.x, tile_ms = blockIdx.y;
-#endif
-  const int tile_m = tile_ms / p.splits, split = tile_ms % p.splits;  // the halves of a tile: neighbours in dispatch order
+  // CTAs are dispatched in order of blockIdx.x.  Output tiles are numbered so that the tiles that share a weight tile
+  // (same columns of W, different rows of x) are neighbours in that order: they run in the same wave, the weight tile
+  // comes from DRAM once and the rest of them find it in L2, while the activation blocks, which every wave reads in
+  // full, stay resident.  The two halves of a split tile are neighbours too.
+  const int linear = (int)blockIdx.x;
+  const bool split_k = linear >= p.split_begin;
+  const int tile_lin = split_k ? p.split_begin + ((linear - p.split_begin) >> 1) : linear;
+  const int split = split_k ? ((linear - p.split_begin) & 1) : 0;
+  const int bx = tile_lin / p.m_tiles, tile_m = tile_lin % p.m_tiles;
 #ifdef MLLMB200_TF_TRACE
-  const bool traced = linear == (int)(gridDim.x * gridDim.y) / 2 && lane == 0 && (warp == 0 || warp >= kTfDequantWarps) && g_gs_trace != nullptr;
+  const bool traced = linear == (int)gridDim.x / 2 && lane == 0 && (warp == 0 || warp >= kTfDequantWarps) && g_gs_trace != nullptr;
   if (warp == 0) TF_STAMP0(0);
 #endif
   int pi = 0;
@@ -208,7 +205,7 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
   const int k_tiles_all = (p.num_groups + kTfGroupsPerStage - 1) / kTfGroupsPerStage;
   // this CTA's K-tiles: [it0, it0 + k_tiles) of the matrix; `it` below counts from 0 within them
   const int it0 = split == 0 ? 0 : k_tiles_all / 2;
-  const int k_tiles = p.splits == 1 ? k_tiles_all : (split == 0 ? k_tiles_all / 2 : k_tiles_all - k_tiles_all / 2);
+  const int k_tiles = !split_k ? k_tiles_all : (split == 0 ? k_tiles_all / 2 : k_tiles_all - k_tiles_all / 2);
   constexpr uint32_t kTmemCols = ATM ? 512u : (uint32_t)(kHalves * NT) < 32u ? 32u : (uint32_t)(kHalves * NT);
   constexpr uint32_t kAColBase = (uint32_t)NT;  // first operand column (ATM)
   // Dequant work: kRowSets sets of 32 weight rows, kDqShare warps per set; K-group g of K-tile it goes to the warp
@@ -480,8 +477,8 @@ __global__ void __launch_bounds__(kTfThreads, 1) w4a32_gemm_tcf16_kernel(const T
     int role = 0;
     int* tile_sync = nullptr;
     if constexpr (!A16) {
-      if (p.splits > 1) {
-        tile_sync = p.split_sync + 2 * (bx * (int)(gridDim.y / p.splits) + tile_m);
+      if (split_k) {
+        tile_sync = p.split_sync + 2 * (tile_lin - p.split_begin);
         int* s_role = reinterpret_cast<int*>(tmem_base_slot + 1);
         if (tid == 0) {
           int r = atomicAdd(tile_sync, 1) == 0 ? 1 : 2;
@@ -596,7 +593,7 @@ static cudaError_t launch_tf_t(const TfParams& prm, int total_tiles, cudaStream_
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)total_tiles, (unsigned)((prm.m + NT - 1) / NT * prm.splits));
+  cfg.gridDim = dim3((unsigned)(2 * total_tiles * prm.m_tiles - prm.split_begin), 1, 1);  // (split_begin = all tiles: no split)
   cfg.blockDim = dim3(kTfThreads, 1, 1);
   cfg.dynamicSmemBytes = S::kTotal;
   cfg.stream = stream;
@@ -690,16 +687,25 @@ cudaError_t launch_w4a32_gemm_tcf16_grouped(const uint8_t* a_blocks, const float
     for (int j = 0; j < prm.prob[i].num_peers; ++j) prm.prob[i].y_peer[j] = y_peers[j];
     tiles += (n[i] + tile.rows - 1) / tile.rows;
   }
-  prm.splits = 1;
   prm.split_sync = split_sync;
-  if (tile.rows == 256) return launch_tf_t<256, 256>(prm, tiles, stream);
+  prm.m_tiles = (m + nt - 1) / nt;
   {
-    const int m_tiles = (m + nt - 1) / nt, ctas = tiles * m_tiles;
-    const int groups_per_tile = nt >= 256 ? 2 : 4;  // (TfSmem::kGroups of the 128-row tiles)
+    // Which output tiles split K: all of them when two CTAs per tile still fit one wave; else the tiles left over
+    // after the last full wave, when they are fewer than half a wave (config 4: 896 tiles = 6 waves + 8: a seventh
+    // wave of 8 CTAs would cost as much as a full one).
+    const int out_tiles = tiles * prm.m_tiles, sms = tf_sm_count();
+    const int groups_per_tile = (nt >= 256 || tile.rows == 256) ? 2 : 4;  // (TfSmem::kGroups)
     const int k_tiles = (prm.num_groups + groups_per_tile - 1) / groups_per_tile;
-    if (MLLMB200_TF_SPLIT_K && split_sync != nullptr && 2 * ctas <= tf_sm_count() && k_tiles >= 8 && 2 * ctas <= split_sync_ints)
-      prm.splits = 2;
+    const int left_over = out_tiles % sms;
+    int split_tiles = 0;
+    if (MLLMB200_TF_SPLIT_K && split_sync != nullptr && k_tiles >= 8) {
+      if (2 * out_tiles <= sms) split_tiles = out_tiles;
+      else if (out_tiles > sms && 2 * left_over <= sms) split_tiles = left_over;
+    }
+    if (2 * split_tiles > split_sync_ints) split_tiles = 0;
+    prm.split_begin = out_tiles - split_tiles;
   }
+  if (tile.rows == 256) return launch_tf_t<256, 256>(prm, tiles, stream);
   constexpr bool kAtm = MLLMB200_TF_ATM != 0;
   switch (nt) {
     case 256: return launch_tf_t<256, 128, false, kAtm>(prm, tiles, stream);
@@ -727,7 +733,7 @@ cudaError_t launch_w4a16_gemm_tcf16_grouped(const uint8_t* a_blocks, int m, int 
   prm.num_groups = (k + kGroup - 1) / kGroup;
   prm.m8_pad = (m + nt - 1) / nt * nt / 8;
   prm.num_problems = count;
-  prm.splits = 1;
+  prm.m_tiles = (m + nt - 1) / nt;
   int tiles = 0;
   for (int i = 0; i < count; ++i) {
     prm.prob[i].tiled = static_cast<const uint8_t*>(tiled[i]);
@@ -739,6 +745,7 @@ cudaError_t launch_w4a16_gemm_tcf16_grouped(const uint8_t* a_blocks, int m, int 
     prm.prob[i].bias_off = make_tiled_header_a16(n[i], k, 0).bias_off;
     tiles += (n[i] + 127) / 128;
   }
+  prm.split_begin = tiles * prm.m_tiles;  // (no K split: fp16 output cannot hold parked sums)
   constexpr bool kAtm = MLLMB200_TF_ATM != 0 && MLLMB200_TF_ATM_A16 != 0;
   switch (nt) {
     case 256: return launch_tf_t<256, 128, true, kAtm>(prm, tiles, stream);

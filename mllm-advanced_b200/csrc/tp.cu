@@ -30,6 +30,8 @@
 namespace mllmb200 {
 int record_cuda_failure(cudaError_t e);
 size_t w4a32_ws_rec_bytes(int m, int k);
+int* w4a32_ws_split_sync(void* ws_dev, int m, int k);
+int w4a32_ws_split_sync_ints();
 cudaError_t launch_w4a32_gemv_stream(int count, const float* const* x, const int* ldx, const uint8_t* const* a_rec,
                                      const float2* const* a_hdr, int m, const int* k, const void* const* tiled,
                                      float* const* y, const int* n, const int* ldy, int use_pdl, cudaStream_t stream,
@@ -262,8 +264,12 @@ int mllmb200_w4a32_linear_forward_tp(void* handle, const float* x_dev, const voi
     if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
     uint8_t* blocks = static_cast<uint8_t*>(ws_dev);
     float2* hdr = reinterpret_cast<float2*>(blocks + w4a32_ws_rec_bytes(M, K));
-    e = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, nl), K, ldx, blocks, hdr, s);
-    if (e == cudaSuccess) e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, 1, &tiled, &y_blk, &nl, &ldy, s, np, peers);
+    // with the K-split counters, as the public forward: every gather mode computes a shard with the same launch
+    int* sync = w4a32_ws_split_sync(ws_dev, M, K);
+    const int sync_ints = w4a32_ws_split_sync_ints();
+    e = launch_act_quant_blocks_f16(x_dev, M, w4a32_gemm_tcf16_m_pad(M, nl), K, ldx, blocks, hdr, s, 0, sync, sync_ints);
+    if (e == cudaSuccess)
+      e = launch_w4a32_gemm_tcf16_grouped(blocks, hdr, M, K, 1, &tiled, &y_blk, &nl, &ldy, s, np, peers, 0, sync, sync_ints);
   } else {
     // kernels without a peer epilogue: compute the block, then push it to every peer with strided device copies
     const int st = mllmb200_w4a32_linear_forward_ex(x_dev, tiled_shard_dev, y_blk, ws_dev, M, K, nl, ldx, N_total, kernel, stream);

@@ -367,10 +367,12 @@ def test_tcgen05_fp16_gemm_vs_oracle(orc, m, k, n):
     print(f"tcgen05 fp16 m={m} k={k} n={n}: max|diff| / rms = {float(np.max(np.abs(y - ref))) / rms:.2e}")
 
 
-@pytest.mark.parametrize("m,k,n", [(128, 1056, 200), (512, 8960, 1536), (260, 2080, 384), (64, 4128, 96), (128, 1024, 256)])
+@pytest.mark.parametrize("m,k,n", [(128, 1056, 200), (512, 8960, 1536), (260, 2080, 384), (64, 4128, 96), (128, 1024, 256),
+                                   (256, 1056, 9600)])
 def test_tcgen05_fp16_gemm_k_split(orc, m, k, n):
-    """Launches that would leave most SMs idle split K between two CTAs per output tile; the half that finishes
-    first parks its sums in the tile's place in y.  Odd and ragged K-tile counts, an output buffer that starts as NaN
+    """Launches that would leave most SMs idle split K between two CTAs per output tile (and so do the tiles left over
+    after the last full wave - the last case: 150 tiles on 148 SMs); the half that finishes first parks its sums in
+    the tile's place in y.  Odd and ragged K-tile counts, an output buffer that starts as NaN
     (nothing may depend on what y held), a row stride wider than N, and the same bits on every repeat whichever
     half finishes first."""
     rng = np.random.default_rng(m + 3 * k + n)
