@@ -28,6 +28,13 @@
 #include "decoder_state.h"
 #include "device_common.cuh"
 
+#ifndef MLLMB200_BATCH_ATTN_CTAS_PER_SM
+#define MLLMB200_BATCH_ATTN_CTAS_PER_SM 4
+#endif
+#ifndef MLLMB200_BATCH_ATTN_V2  // 0: the batch-1 attention body for every sequence (the earlier form)
+#define MLLMB200_BATCH_ATTN_V2 1
+#endif
+
 namespace mllmb200 {
 
 __global__ void add_rmsnorm_quant_kernel(const float*, const float*, const float*, float, int, float*, float*, uint8_t*,
@@ -57,6 +64,202 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_partial_batched_kern
                        cache_k + (size_t)seq * cache_seq_stride + (size_t)kvh * max_ctx * D,
                        cache_v + (size_t)seq * cache_seq_stride + (size_t)kvh * max_ctx * D, part_o + head0 * splits * D,
                        part_ml + head0 * splits * 2, splits, split);
+}
+
+// The same partial attention laid out for THROUGHPUT (head_dim 128): with 64 sequences x 2 KV heads x splits CTAs
+// in flight the GPU does not wait for any one of them, and what bounds the batch-1 body above - one shuffle
+// reduction per (position, head) over a full warp and one shared-memory load per multiply-add of P.V - is all
+// that is left.  Here, per block of 32 cache positions:
+//   scores  warp w takes positions 4w..4w+3, 8 lanes per position, 16 elements of the head dimension per lane:
+//           4 16-byte loads of K per lane (128 contiguous bytes per position and instruction), the rotated queries
+//           as broadcast 16-byte shared-memory loads, a 3-step shuffle reduction per (position, head);
+//   softmax warp h owns head h (running maximum and sum, as in the body above);
+//   P.V     warp w takes the same four positions, lane = 4 consecutive elements of the head dimension: 4 16-byte
+//           loads of V per lane, the probabilities as two broadcast 16-byte loads per position, 4 x group
+//           accumulators per thread; the eight warps' accumulators are added in warp order at the end.
+// The next block's K and V are requested before the current block's arithmetic.  The new token's key (rotated)
+// and value are appended to the cache by the CTA whose range holds `pos`, before its loop.
+constexpr int kBa2Threads = 256, kBa2Block = 32, kBa2D = 128, kBa2G = kAttnMaxGroup;
+struct Ba2Smem {
+  float q[kBa2G * kBa2D];        // rotated queries
+  float sc[kBa2Block][kBa2G];    // scores of the block, position-major
+  float pr[kBa2Block][kBa2G];    // probabilities exp(score - running max)
+  float alpha[kBa2G], mrun[kBa2G], lrun[kBa2G];
+  float red[kBa2Threads / 32][kBa2G * kBa2D / 2];  // final sum over the warps, half of the heads at a time
+};
+__global__ void __launch_bounds__(kBa2Threads) attn_decode_partial_batched_v2_kernel(
+    const float* __restrict__ q, int ldq, const float* __restrict__ k_new, const float* __restrict__ v_new, int ldkv,
+    const float* __restrict__ sin_t, const float* __restrict__ cos_t, const int* __restrict__ pos_ptr, int max_ctx, int chunk,
+    int group, int q_heads, float* __restrict__ cache_k, float* __restrict__ cache_v, size_t cache_seq_stride,
+    float* __restrict__ part_o, float* __restrict__ part_ml, int splits) {
+  constexpr int D = kBa2D, HALF = D / 2;
+  __shared__ __align__(16) Ba2Smem sm;
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int pos = min(pos_ptr[seq], max_ctx - 1);
+  if (split * chunk > pos) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c0 = split * chunk, c1 = min((split + 1) * chunk, pos + 1);
+  const size_t head0 = (size_t)seq * q_heads + (size_t)kvh * group;
+  const float* qh = q + (size_t)seq * ldq + (size_t)kvh * group * D;
+  const float* kn = k_new + (size_t)seq * ldkv + kvh * D;
+  const float* vn = v_new + (size_t)seq * ldkv + kvh * D;
+  const float* sin_row = sin_t + (size_t)pos * HALF;
+  const float* cos_row = cos_t + (size_t)pos * HALF;
+  float* kc = cache_k + (size_t)seq * cache_seq_stride + (size_t)kvh * max_ctx * D;
+  float* vc = cache_v + (size_t)seq * cache_seq_stride + (size_t)kvh * max_ctx * D;
+  part_o += head0 * splits * D;
+  part_ml += head0 * splits * 2;
+  const float scale = 1.0f / sqrtf((float)D);
+
+  // rotated queries; the new token's key and value into the cache (RoPE as mllm/Backends/Arm/Kernels/rope.cpp:20-87
+  // of the reference project: element d pairs with d +- D/2)
+  for (int idx = tid; idx < group * D; idx += kBa2Threads) {
+    const int h = idx / D, d = idx - h * D, dd = d < HALF ? d : d - HALF;
+    const float sn = sin_row[dd], cs = cos_row[dd];
+    const float x0 = qh[(size_t)h * D + dd], x1 = qh[(size_t)h * D + dd + HALF];
+    sm.q[idx] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
+  }
+  if (pos >= c0 && pos < c1 && tid < D) {
+    const int d = tid, dd = d < HALF ? d : d - HALF;
+    const float sn = sin_row[dd], cs = cos_row[dd];
+    const float x0 = kn[dd], x1 = kn[dd + HALF];
+    kc[(size_t)pos * D + d] = d < HALF ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs);
+    vc[(size_t)pos * D + d] = vn[d];
+  }
+  if (tid < kBa2G) {
+    sm.mrun[tid] = -3.402823466e+38f;
+    sm.lrun[tid] = 0.0f;
+  }
+  __threadfence();
+  __syncthreads();  // (the appended row is read back below through L2, by this CTA only)
+
+  const int tp = warp * 4 + (lane >> 3), l8 = lane & 7;  // scores: position of the block, slice of the head dimension
+  float4 kreg[4], vreg[4];
+  auto load_k = [&](int b0) {
+    const int t = b0 + tp;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      kreg[i] = t < c1 ? __ldcg(reinterpret_cast<const float4*>(kc + (size_t)t * D + 32 * i + 4 * l8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  auto load_v = [&](int b0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = b0 + warp * 4 + j;
+      vreg[j] = t < c1 ? __ldcg(reinterpret_cast<const float4*>(vc + (size_t)t * D + 4 * lane)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  float4 acc[kBa2G];
+#pragma unroll
+  for (int h = 0; h < kBa2G; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+  load_k(c0);
+  load_v(c0);
+
+  for (int b0 = c0; b0 < c1; b0 += kBa2Block) {
+    // ---- scores
+    {
+      float part[kBa2G];
+#pragma unroll
+      for (int h = 0; h < kBa2G; ++h) {
+        part[h] = 0.0f;
+        if (h < group) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 qv = *reinterpret_cast<const float4*>(&sm.q[h * D + 32 * i + 4 * l8]);
+            part[h] = fmaf(qv.x, kreg[i].x, part[h]);
+            part[h] = fmaf(qv.y, kreg[i].y, part[h]);
+            part[h] = fmaf(qv.z, kreg[i].z, part[h]);
+            part[h] = fmaf(qv.w, kreg[i].w, part[h]);
+          }
+        }
+      }
+      if (b0 + kBa2Block < c1) load_k(b0 + kBa2Block);  // the next block's keys, on their way during the rest
+#pragma unroll
+      for (int h = 0; h < kBa2G; ++h) {
+        if (h < group) {
+          float v = part[h];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          if (l8 == 0) sm.sc[tp][h] = (b0 + tp < c1) ? v * scale : -3.402823466e+38f;
+        }
+      }
+    }
+    __syncthreads();
+    // ---- online softmax bookkeeping: warp h owns head h, lane = position of the block
+    if (warp < group) {
+      const float sc = sm.sc[lane][warp];
+      float mx = sc;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_old = sm.mrun[warp], m_new = fmaxf(m_old, mx);
+      const float p = (b0 + lane < c1) ? expf(sc - m_new) : 0.0f;
+      float sum = p;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      sm.pr[lane][warp] = p;
+      if (lane == 0) {
+        const float al = expf(m_old - m_new);  // 0 on the first block (m_old = -FLT_MAX)
+        sm.alpha[warp] = al;
+        sm.mrun[warp] = m_new;
+        sm.lrun[warp] = sm.lrun[warp] * al + sum;
+      }
+    }
+    __syncthreads();
+    // ---- P.V: this warp's four positions, lane = elements 4 lane .. 4 lane + 3
+    {
+      const float4 a0 = *reinterpret_cast<const float4*>(&sm.alpha[0]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&sm.alpha[4]);
+      const float al[kBa2G] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+      for (int h = 0; h < kBa2G; ++h) {
+        if (h < group) {
+          acc[h].x *= al[h], acc[h].y *= al[h], acc[h].z *= al[h], acc[h].w *= al[h];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 p0 = *reinterpret_cast<const float4*>(&sm.pr[warp * 4 + j][0]);
+        const float4 p1 = *reinterpret_cast<const float4*>(&sm.pr[warp * 4 + j][4]);
+        const float pj[kBa2G] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int h = 0; h < kBa2G; ++h) {
+          if (h < group) {
+            acc[h].x = fmaf(pj[h], vreg[j].x, acc[h].x);
+            acc[h].y = fmaf(pj[h], vreg[j].y, acc[h].y);
+            acc[h].z = fmaf(pj[h], vreg[j].z, acc[h].z);
+            acc[h].w = fmaf(pj[h], vreg[j].w, acc[h].w);
+          }
+        }
+      }
+      if (b0 + kBa2Block < c1) load_v(b0 + kBa2Block);
+    }
+    // (the next block's scores go to sm.sc, which nobody reads any more; sm.pr and sm.alpha are rewritten only
+    // after the next __syncthreads, which every warp reaches after its P.V)
+  }
+  // ---- the eight warps' accumulators, added in warp order; half of the heads at a time through shared memory
+  for (int half = 0; half < 2; ++half) {
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < kBa2G / 2; ++hh) {
+      const int h = half * (kBa2G / 2) + hh;
+      if (h < group) *reinterpret_cast<float4*>(&sm.red[warp][hh * D + 4 * lane]) = acc[h];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < (kBa2G / 2) * D; idx += kBa2Threads) {
+      const int h = half * (kBa2G / 2) + idx / D, d = idx % D;
+      if (h < group) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kBa2Threads / 32; ++w) sum += sm.red[w][idx];
+        part_o[((size_t)h * splits + split) * D + d] = sum;
+      }
+    }
+  }
+  if (tid < group) {
+    float* ml = part_ml + ((size_t)tid * splits + split) * 2;
+    ml[0] = sm.mrun[tid];
+    ml[1] = sm.lrun[tid];
+  }
 }
 
 // Merge of the context splits of one sequence per CTA (the arithmetic of attn_combine_quant_kernel, fp32 output):
@@ -333,7 +536,11 @@ int enqueue_batched_step(BatchDecoder* b) {
     }
     {
       const dim3 grid(b->attn_splits, c.kv_heads, B);
-      if (c.head_dim == 128)
+      if (c.head_dim == 128 && MLLMB200_BATCH_ATTN_V2)
+        attn_decode_partial_batched_v2_kernel<<<grid, kBa2Threads, 0, s>>>(
+            b->q, QD, b->k, b->v, KD, d->sin_t, d->cos_t, b->pos, c.max_ctx, b->attn_chunk, group, c.q_heads, b->cache_k[l],
+            b->cache_v[l], b->cache_seq_stride, b->part_o, b->part_ml, b->attn_splits);
+      else if (c.head_dim == 128)
         attn_decode_partial_batched_kernel<128><<<grid, kAttnThreads, 0, s>>>(
             b->q, QD, b->k, b->v, KD, d->sin_t, d->cos_t, b->pos, c.max_ctx, b->attn_chunk, group, c.q_heads, b->cache_k[l],
             b->cache_v[l], b->cache_seq_stride, b->part_o, b->part_ml, b->attn_splits);
@@ -391,8 +598,8 @@ int mllmb200_qwen2_batch_create(void* decoder, int batch, void** handle) {
   const int QD = c.q_heads * c.head_dim, KD = c.kv_heads * c.head_dim;
   b->cache_seq_stride = (size_t)c.kv_heads * c.max_ctx * c.head_dim;
   {
-    // aim at about 8 CTAs per SM over the (split, kv head, sequence) grid, chunks a multiple of 32 and at least the batch-1 chunk
-    const long long want_splits = std::max<long long>(1, (8LL * 148) / ((long long)batch * c.kv_heads));
+    // aim at about 4 CTAs per SM (two resident at a time; measured against 2, 8 and 16) over the (split, kv head, sequence) grid, chunks a multiple of 32 and at least the batch-1 chunk
+    const long long want_splits = std::max<long long>(1, ((long long)MLLMB200_BATCH_ATTN_CTAS_PER_SM * 148) / ((long long)batch * c.kv_heads));
     int chunk = (int)((c.max_ctx + want_splits - 1) / want_splits);
     chunk = std::max(d->attn_chunk, (chunk + 31) / 32 * 32);
     b->attn_chunk = chunk;
