@@ -8,7 +8,7 @@ kernels than the batch-1 path, which changes the order of fp32 additions only) -
 The reference's dynamic int8 activation quantization is discontinuous: an activation within rounding distance of a
 quantization boundary moves by one level when the additions in front of it are reordered, and one such flip moves the
 logits of these small models by 1e-2..7e-2 * rms from there on.  Measured between the two decode modes of the batch-1
-decoder itself (graph and persistent, same prompts): 2 % of the steps; the numpy oracle sides with either.  So a
+decoder itself (graph and persistent, same prompts): 2 % of the steps (on the prompt followed up, the numpy oracle sided with the persistent mode).  So a
 sequence may exceed the bar, up to 0.1 * rms, as long as its tokens are the same."""
 import os
 import sys
