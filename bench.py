@@ -1002,6 +1002,8 @@ def run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind)
     B, ctx_end, steps_t = args.batch_sequences, cfg["max_ctx"], args.batch_timed_steps
     n_vis, n_txt = 256, 256
     bd = mb.Qwen2BatchDecoder(dec, B)
+    if args.batch_policy:
+        bd.set_policy(args.batch_policy)
     ds = dec.stream()
     rng = np.random.default_rng(11)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -1049,7 +1051,9 @@ def run_batched_decode(args, torch, mb, dec, cfg, emb, gen, hbm_peak, peak_kind)
                 "GBs": by / (ms * 1e-3) / 1e9, "frac_hbm": by / (ms * 1e-3) / 1e9 / hbm_peak}
 
     out = {"config": f"BASELINE config 3: {B} sequences x {ctx_end}-token context on the Qwen2-1.5B language tower, prefill of "
-                     f"{n_vis} vision-patch embeddings + {n_txt} text tokens per sequence, fp32 KV cache, every linear at M = {B}",
+                     f"{n_vis} vision-patch embeddings + {n_txt} text tokens per sequence, fp32 KV cache, every linear at M = {B}, "
+                     f"kernel policy {args.batch_policy} (5: gate / up on the fp16 tile GEMM, the other linears on the exact streaming GEMM; 0: all exact)",
+           "policy": args.batch_policy,
            "prefill_ms_all_sequences": prefill_ms, "prefill_tokens_per_s": B * n0 / (prefill_ms * 1e-3),
            "at_start": entry(ms_start, n0 + 2 + steps_t / 2), "at_end": entry(ms_end, ctx_late + steps_t / 2),
            "timed_steps": steps_t, "peak_kind": f"of {peak_kind}",
@@ -1349,6 +1353,9 @@ def main():
     ap.add_argument("--no-batched-decode", action="store_true", help="skip the 64-sequence batched decode of the decoder section")
     ap.add_argument("--batched-only", action="store_true", help="only the batched decode section, on --decoder-layers layers")
     ap.add_argument("--decoder-layers", type=int, default=LAYERS, help="layers of the model of --batched-only (small values for profiler captures)")
+    ap.add_argument("--batch-policy", type=int, default=5,
+                    help="kernel policy of the batched decoder's linears: 5 fastest (gate / up on the fp16 tile GEMM: exact "
+                         "products, fp32 accumulation; the rest exact int32 group sums), 0 exact int32 group sums everywhere")
     ap.add_argument("--batch-context", type=int, default=0, help="with --batched-only: stop the untimed walk at this context (0 = the full 1024)")
     ap.add_argument("--batch-sequences", type=int, default=64, help="sequences of the batched decode section (BASELINE config 3: 64)")
     ap.add_argument("--batch-timed-steps", type=int, default=16, help="timed greedy steps at either end of the batched decode")

@@ -134,7 +134,7 @@ MLLMB200_API int mllmb200_w4a32_linear_forward(const float* x_dev, const void* t
  * tensor memory; same 1e-3*rms bound; auto never picks it; launches that would fill less than half of the SMs
  * split K between two CTAs per output tile, and y holds one half's partial sums for a moment during the
  * call - deterministic, but y is scratch until the call's work on the stream has finished), 5 fastest: kernel 4
- * for M >= 128, else auto,
+ * for M >= 128 and, at 64 <= M < 128, for matrices (or groups) of at least 8192 rows with K <= 4096; else auto,
  * 6 the two-launch GEMV (activation-quantization kernel + one-shot GEMV), kept for comparison,
  * 7 streaming tensor-core GEMM for small batches (M <= 64; what auto picks for 5 <= M <= 64): the weight cells are
  * spread over all SMs as in the GEMV, the per-group integer products run as mma.sync u8 x s8 (exact int32 group

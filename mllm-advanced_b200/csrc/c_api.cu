@@ -279,7 +279,11 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
                                                    (flags >> 8) & 1, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? MLLMB200_OK : cuda_fail(e);
   }
-  if (((flags & 0xFF) == 0 || (flags & 0xFF) == 5) && M >= kStreamGemmMinM && M <= kStreamGemmMaxM &&
+  int n_group = 0;
+  for (int i = 0; i < count; ++i) n_group += N[i];
+  // ("fastest" at 64 <= M: wide groups with a short K go to the fp16 tile GEMM further down)
+  const bool tile16_first = (flags & 0xFF) == 5 && count > 1 && w4a32_gemm_tcf16_preferred(M, K, n_group);
+  if (((flags & 0xFF) == 0 || (flags & 0xFF) == 5) && !tile16_first && M >= kStreamGemmMinM && M <= kStreamGemmMaxM &&
       w4a32_gemm_stream_supported(M, K, count, N)) {  // small batch: one quantization, ONE streaming tensor-core launch
     if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
     cudaStream_t st7 = static_cast<cudaStream_t>(stream);
@@ -308,9 +312,14 @@ int mllmb200_w4a32_linear_forward_grouped(const float* x_dev, int M, int K, int 
   const int policy = flags & 0xFF;  // 0 auto, 5 fastest (as the kernel argument of linear_forward_ex)
   if (policy != 0 && policy != 5) return MLLMB200_INVALID_ARG;
   cudaStream_t st_grp = static_cast<cudaStream_t>(stream);
-  if (count > 1 && policy == 5 && M >= 128) {
+  if (count > 1 && policy == 5 && M >= 64) {
     bool all16 = true;
-    for (int i = 0; i < count; ++i) all16 = all16 && w4a32_gemm_tcf16_supported(M, K, N[i]);
+    int n_sum = 0;
+    for (int i = 0; i < count; ++i) {
+      all16 = all16 && w4a32_gemm_tcf16_supported(M, K, N[i]);
+      n_sum += N[i];
+    }
+    all16 = all16 && w4a32_gemm_tcf16_preferred(M, K, n_sum);  // (the group's weight tiles ride in one grid)
     if (all16) {
       if (!ws_dev || (reinterpret_cast<uintptr_t>(ws_dev) & 255u)) return MLLMB200_INVALID_ARG;
       uint8_t* blocks = static_cast<uint8_t*>(ws_dev);

@@ -53,6 +53,9 @@
 #ifndef MLLMB200_TF_FUSED_DEQUANT
 #define MLLMB200_TF_FUSED_DEQUANT 1
 #endif
+#ifndef MLLMB200_TF_SMALL_M
+#define MLLMB200_TF_SMALL_M 1
+#endif
 #ifndef MLLMB200_TF_SPLIT_K
 #define MLLMB200_TF_SPLIT_K 1
 #endif
@@ -650,7 +653,12 @@ int w4a32_gemm_tcf16_m_pad_max(int m) { return (m + 255) / 256 * 256; }
 bool w4a32_gemm_tcf16_supported(int m, int k, int n) { return m >= 64 && k >= 1 && n >= 1 && (m + 63) / 64 <= 65535; }
 // Shapes on which this path is at least as fast as the int8 path (measured on the Qwen2-1.5B layer
 // shapes at M = 512: 17 vs 18 us for N = 1536 / 256, 24 vs 60 us for N = 8960, 59 vs 68 us for K = 8960).
-bool w4a32_gemm_tcf16_preferred(int m, int k, int n) { return w4a32_gemm_tcf16_supported(m, k, n) && m >= 128; }
+// At 64 <= M < 128 only where the weight tiles alone fill the GPU and K is short (gate / up of the 1.5B model, alone or
+// grouped: 17 vs 30 us at M = 64 against the streaming small-batch GEMM); narrow or long-K matrices stay there.
+bool w4a32_gemm_tcf16_preferred(int m, int k, int n) {
+  if (!w4a32_gemm_tcf16_supported(m, k, n)) return false;
+  return m >= 128 || (MLLMB200_TF_SMALL_M && n >= 8192 && k <= 4096);
+}
 
 // Up to four matrices that share x in ONE launch (their weight tiles side by side in the grid):
 // the activation blocks must be padded to m_pad = a multiple of the tile width chosen by

@@ -78,6 +78,45 @@ def test_batched_decode_equals_independent_runs(cfg, batch, steps, lo, hi):
 
 
 @pytest.mark.gpu
+def test_batched_decode_fastest_policy_at_full_width():
+    """Policy 5 at 64 sequences on the 1.5B widths (two layers, small vocabulary): gate / up take the fp16 tile GEMM
+    (exact products, fp32 accumulation over all of K), the other linears the exact streaming GEMM.  Same bars against
+    64 independent batch-1 runs as above."""
+    import mllm_b200 as mb
+    from test_decoder import FULL
+    cfg = dict(FULL, layers=2, vocab=2000)
+    batch, steps = 64, 3
+    rng = np.random.default_rng(5)
+    w, raw = make_model(cfg, 9)
+    dec = _gpu_decoder(cfg, w, raw)
+    prompts = [rng.integers(0, cfg["vocab"], size=int(rng.integers(4, 40))).tolist() for _ in range(batch)]
+    singles = [_run_single(dec, p, steps) for p in prompts]
+    bd = mb.Qwen2BatchDecoder(dec, batch)
+    bd.set_policy(mb.KERNEL_FASTEST)
+    for b, p in enumerate(prompts):
+        bd.prefill(b, tokens=p)
+    bd.decode(steps)
+    flipped, worst = 0, 0.0
+    for b, p in enumerate(prompts):
+        _, pos, logits = bd.read(b, 0, 0, want_logits=True)
+        ref_toks, ref_pos, ref_logits = singles[b]
+        assert pos == ref_pos
+        err = float(np.max(np.abs(logits - ref_logits))) / _rms(ref_logits)
+        worst = max(worst, err)
+        assert err <= FLIP_TOL, (b, err)
+        flipped += err > LOGIT_TOL
+        toks = bd.generated(b, steps)
+        if not np.array_equal(toks, ref_toks):
+            i = int(np.argmax(toks != ref_toks))
+            gap = abs(float(ref_logits[ref_toks[i]]) - float(ref_logits[toks[i]])) / _rms(ref_logits)
+            assert i == steps and gap <= 2 * err, (b, i, gap, err)
+    assert flipped <= max(1, int(FLIP_FRACTION * batch)), (flipped, worst)
+    mb.check_device_status()
+    bd.close()
+    dec.close()
+
+
+@pytest.mark.gpu
 def test_batched_decode_against_numpy_oracle():
     """Two sequences of the small configuration against the numpy restatement itself."""
     import mllm_b200 as mb
