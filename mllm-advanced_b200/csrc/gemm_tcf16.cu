@@ -37,26 +37,27 @@
 // Stages of 2 (NT = 256) or 4 K-groups: a ring of 5-7 loaded-data stages {raw cells, B operand NT*64 B per
 // group} in shared memory and up to as many operand stages in tensor-memory columns [NT, 512).  Every wait
 // (mbarrier, split-K flag) is bounded.  CTAs are renumbered so that the row tiles of one weight tile are
-// dispatched side by side; launches that would fill less than half of the SMs split K between two CTAs per
-// output tile.
+// dispatched side by side; launches that would fill less than half of the SMs, and the tiles left over after a
+// launch's last full wave, split K between two CTAs per output tile.
 // Measured at M = 512 on the Qwen2-1.5B layer shapes (cold caches, one launch each): q,k,v grouped 17 us,
-// o 17 us, gate+up grouped 36 us, down 34 us; config 4 (28672 x 8192, M = 2048): 0.84 ms = 1145 TFLOP/s.
+// o 17 us, gate+up grouped 36 us, down 34 us; config 4 (28672 x 8192, M = 2048): 0.80 ms = 1202 TFLOP/s.
 #include <cuda_fp16.h>
 
 #include "device_common.cuh"
 #include "layout_a16.h"
 #include "tcgen05_common.cuh"
 
-#ifndef MLLMB200_TF_WEIGHT_HINT
+// Build-time switches (each 1 = the measured choice; 0 restores the form it replaced, for comparisons):
+#ifndef MLLMB200_TF_WEIGHT_HINT  // evict-first L2 hint on the weight-cell copies
 #define MLLMB200_TF_WEIGHT_HINT 1
 #endif
-#ifndef MLLMB200_TF_FUSED_DEQUANT
+#ifndef MLLMB200_TF_FUSED_DEQUANT  // one fused multiply-add per pair of nibbles (bf16-encoded scales)
 #define MLLMB200_TF_FUSED_DEQUANT 1
 #endif
-#ifndef MLLMB200_TF_SMALL_M
+#ifndef MLLMB200_TF_SMALL_M  // "fastest" picks this kernel from M = 64 for wide matrices with a short K
 #define MLLMB200_TF_SMALL_M 1
 #endif
-#ifndef MLLMB200_TF_SPLIT_K
+#ifndef MLLMB200_TF_SPLIT_K  // K split in two on short grids and left-over tiles
 #define MLLMB200_TF_SPLIT_K 1
 #endif
 #ifndef MLLMB200_TF_ATM  // dequantized weight operand in tensor memory (128-row tiles)
