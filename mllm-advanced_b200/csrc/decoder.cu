@@ -43,6 +43,8 @@ template <int D>
 __global__ void attention_prefill_kernel(const float*, int, int, const float*, const float*, const int*, int, int, const float*,
                                          const float*, float*, int);
 size_t attention_prefill_smem_bytes(int head_dim);
+int attention_prefill_rows();
+int attention_prefill_threads();
 __global__ void lm_head_f16_kernel(const float*, const __half*, int, int, float*, float2*);
 __global__ void sample_advance_kernel(const float2*, int, int*, int*, int*, int*, int);
 __global__ void act_quant_records_kernel(const float*, int, int, int, uint8_t*, float2*, int, int);
@@ -199,13 +201,14 @@ int prefill_into(Decoder* d, const int* tokens_dev, const float* embeds_dev, int
     rope_kv_append_kernel<<<dim3(c.kv_heads, n), c.head_dim, 0, s>>>(d->k, d->v, KD, d->sin_t, d->cos_t, d->zero, c.max_ctx,
                                                                     cache_k[l], cache_v[l]);
     {
-      const dim3 grid((n + 7) / 8, c.kv_heads);
+      const int rows = attention_prefill_rows();  // query rows per CTA, one warp each
+      const dim3 grid((n + rows - 1) / rows, c.kv_heads);
       const size_t smem = attention_prefill_smem_bytes(c.head_dim);
       if (c.head_dim == 128)
-        attention_prefill_kernel<128><<<grid, 256, smem, s>>>(d->q, QD, n, d->sin_t, d->cos_t, d->zero, c.max_ctx,
+        attention_prefill_kernel<128><<<grid, attention_prefill_threads(), smem, s>>>(d->q, QD, n, d->sin_t, d->cos_t, d->zero, c.max_ctx,
                                                                c.q_heads / c.kv_heads, cache_k[l], cache_v[l], d->attn, QD);
       else
-        attention_prefill_kernel<64><<<grid, 256, smem, s>>>(d->q, QD, n, d->sin_t, d->cos_t, d->zero, c.max_ctx,
+        attention_prefill_kernel<64><<<grid, attention_prefill_threads(), smem, s>>>(d->q, QD, n, d->sin_t, d->cos_t, d->zero, c.max_ctx,
                                                               c.q_heads / c.kv_heads, cache_k[l], cache_v[l], d->attn, QD);
     }
     DEC_ST(mllmb200_w4a32_linear_forward_ex(d->attn, L.w[kO], d->o, d->ws, n, QD, H, QD, H, 5, s));
