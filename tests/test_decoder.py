@@ -214,7 +214,8 @@ def test_decoder_rejects_bad_arguments():
 
 
 @pytest.mark.gpu
-def test_full_width_decode_agrees_with_prefill():
+@pytest.mark.parametrize("prompt_len", [64, 400])
+def test_full_width_decode_agrees_with_prefill(prompt_len):
     """Size-independent property at the full Qwen2-1.5B widths (4 layers): tokens produced by decode
     steps (GEMV kernels, fused quantizing producers, graph replay) and the token a from-scratch
     prefill of prompt + those tokens samples (tcgen05 kernels, separate quantization) come from the
@@ -223,7 +224,7 @@ def test_full_width_decode_agrees_with_prefill():
     import mllm_b200 as mb
     import bench
     gen = torch.Generator(device="cuda").manual_seed(5)
-    cfg = dict(mb.QWEN2_1P5B, layers=4, max_ctx=256)
+    cfg = dict(mb.QWEN2_1P5B, layers=4, max_ctx=512)  # (400 positions: 13 key blocks per attention tile at the end of the prompt)
     layers = [[bench.make_random_weights(mb, torch, n, k, hb, gen) for _, k, n, hb in bench.LINEARS] for _ in range(4)]
     dec = mb.Qwen2Decoder(cfg)
     for l, lw in enumerate(layers):
@@ -235,16 +236,16 @@ def test_full_width_decode_agrees_with_prefill():
     emb = torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen)
     head = (torch.randn((cfg["vocab"], cfg["hidden"]), device="cuda", generator=gen) * 0.02).to(torch.float16)
     dec.set_tables(emb, head)
-    prompt = np.random.default_rng(3).integers(0, cfg["vocab"], 64).tolist()
+    prompt = np.random.default_rng(3).integers(0, cfg["vocab"], prompt_len).tolist()
     steps = 8
     dec.prefill(prompt)
     dec.decode(steps)
     toks = dec.generated(steps).tolist()
     _, pos, lg_decode = dec.read(0, 0, want_logits=True)
-    assert pos == 64 + steps
+    assert pos == prompt_len + steps
     dec.prefill(prompt + toks[:steps])
-    t2, pos2, lg_prefill = dec.read(64 + steps - 1, 1, want_logits=True)
-    assert pos2 == 64 + steps
+    t2, pos2, lg_prefill = dec.read(prompt_len + steps - 1, 1, want_logits=True)
+    assert pos2 == prompt_len + steps
     rms = float(np.sqrt(np.mean(lg_prefill.astype(np.float64) ** 2)))
     err = float(np.max(np.abs(lg_decode - lg_prefill))) / rms
     print(f"full-width decode vs prefill: rel logit err {err:.3e}")
